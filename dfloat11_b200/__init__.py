@@ -1,0 +1,13 @@
+"""B200-native implementation of DFloat11's on-the-fly BF16 weight decompression path.
+
+Importing the package loads ``libdf11.so`` (built in-tree by ``python -m dfloat11_b200.build``);
+a missing or stale library is an ImportError -- there is no CPU or pure-PyTorch fallback.
+"""
+from . import _lib  # noqa: F401  (fails loudly when the native library is absent)
+from .codec import UnrepresentableError, encode_weights, get_codec, get_luts, split_bf16, validate_unit
+from .ops import aux_bytes, decode, decode_prepared, prepare
+
+__all__ = [
+    "UnrepresentableError", "encode_weights", "get_codec", "get_luts", "split_bf16", "validate_unit",
+    "aux_bytes", "decode", "decode_prepared", "prepare",
+]

@@ -1,0 +1,99 @@
+"""Torch-facing launchers of the libdf11 decode entry points.
+
+These stand where the reference calls its cupy kernel object
+(``_decode(grid=..., block=..., shared_mem=..., args=[...])``, dfloat11/dfloat11.py:142-151
+and :576-585): same tensors, same meaning, but the launch goes through the C ABI of
+``libdf11.so`` onto torch's current CUDA stream of the tensors' device.  There is no
+CPU or pure-PyTorch fallback: tensors that are not on a CUDA device raise.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+def _require_cuda(**tensors: torch.Tensor) -> torch.device:
+    device = None
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(f"df11 decode needs CUDA tensors; `{name}` is on {t.device}")
+        if not t.is_contiguous():
+            raise RuntimeError(f"`{name}` must be contiguous")
+        if device is None:
+            device = t.device
+        elif t.device != device:
+            raise RuntimeError(f"`{name}` is on {t.device}, expected {device}")
+    return device
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def decode(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_mantissa: torch.Tensor,
+           output_positions: torch.Tensor, gaps: torch.Tensor, out: Optional[torch.Tensor] = None,
+           max_block_elems: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decompress one DF11 unit into ``out`` (BF16, ``sign_mantissa.numel()`` elements).
+
+    ``output_positions`` may be the uint8 byte view stored on disk or a uint32/int32 tensor.
+    ``status`` is an optional int32 tensor of one element that receives DF11_STATUS_* bits.
+    Asynchronous: returns right after the launch on the current stream.
+    """
+    device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, sign_mantissa=sign_mantissa,
+                           output_positions=output_positions, gaps=gaps, out=out, status=status)
+    n_elements = sign_mantissa.numel()
+    if out is None:
+        out = torch.empty(n_elements, dtype=torch.bfloat16, device=device)
+    if out.dtype != torch.bfloat16 or out.numel() < n_elements:
+        raise RuntimeError("`out` must be a bfloat16 tensor with at least n_elements elements")
+    _lib.check(_lib.lib.df11_decode(
+        luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(),
+        output_positions.data_ptr(), gaps.data_ptr(), out.data_ptr(),
+        luts.shape[0], encoded_exponent.numel(), n_elements, int(max_block_elems),
+        status.data_ptr() if status is not None else None, device.index, _stream(device)))
+    return out
+
+
+def aux_bytes(n_bytes: int) -> int:
+    return _lib.check(_lib.lib.df11_aux_bytes(int(n_bytes)))
+
+
+def prepare(luts: torch.Tensor, encoded_exponent: torch.Tensor, output_positions: torch.Tensor,
+            gaps: torch.Tensor, n_elements: int, aux: Optional[torch.Tensor] = None,
+            status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fill (allocating if needed) the auxiliary buffer that ``decode_prepared`` reads."""
+    device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, output_positions=output_positions,
+                           gaps=gaps, aux=aux, status=status)
+    need = aux_bytes(encoded_exponent.numel())
+    if aux is None:
+        aux = torch.empty(need, dtype=torch.uint8, device=device)
+    _lib.check(_lib.lib.df11_prepare(
+        luts.data_ptr(), encoded_exponent.data_ptr(), output_positions.data_ptr(), gaps.data_ptr(),
+        aux.data_ptr(), aux.numel() * aux.element_size(), luts.shape[0], encoded_exponent.numel(),
+        int(n_elements), status.data_ptr() if status is not None else None, device.index, _stream(device)))
+    return aux
+
+
+def decode_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_mantissa: torch.Tensor,
+                    output_positions: torch.Tensor, gaps: torch.Tensor, aux: torch.Tensor,
+                    out: Optional[torch.Tensor] = None, max_block_elems: int = 0,
+                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Single-pass decode using the buffer made by ``prepare`` for the same unit."""
+    device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, sign_mantissa=sign_mantissa,
+                           output_positions=output_positions, gaps=gaps, aux=aux, out=out, status=status)
+    n_elements = sign_mantissa.numel()
+    if out is None:
+        out = torch.empty(n_elements, dtype=torch.bfloat16, device=device)
+    if out.dtype != torch.bfloat16 or out.numel() < n_elements:
+        raise RuntimeError("`out` must be a bfloat16 tensor with at least n_elements elements")
+    _lib.check(_lib.lib.df11_decode_prepared(
+        luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(),
+        output_positions.data_ptr(), gaps.data_ptr(), aux.data_ptr(), out.data_ptr(),
+        luts.shape[0], encoded_exponent.numel(), n_elements, int(max_block_elems),
+        status.data_ptr() if status is not None else None, device.index, _stream(device)))
+    return out

@@ -1,0 +1,146 @@
+/*
+ * libdf11 -- C ABI of the DFloat11 on-the-fly weight decompression path for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The reference project has no C interface: its Python package loads a PTX file
+ * with cupy (`cp.RawModule(path=ptx_path).get_function('decode')`,
+ * dfloat11/dfloat11.py:38-40) and launches it from two places
+ * (dfloat11/dfloat11.py:142-151 in the forward pre-hook and :576-585 in the
+ * compressor's self-check).  The entry points below are what a binding for that
+ * path needs instead; each comment names the reference code it replaces.
+ *
+ * Conventions
+ *   - Plain pointers and sizes only.  Pointers documented "device" must be valid
+ *     on CUDA device `device`; "host" pointers are ordinary memory.
+ *   - Nothing here allocates or frees device memory, synchronises the device or
+ *     the stream, or keeps a pointer after returning.  Launches go to the given
+ *     stream of the given device (the reference launches on cupy's current
+ *     stream, dfloat11.py:142).
+ *   - Every function returns DF11_OK (0) or a negative DF11_ERR_* code;
+ *     df11_last_error() gives the message for the calling thread's last failure.
+ *   - Functions are re-entrant and may be called from several threads.
+ */
+#ifndef DF11_H
+#define DF11_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DF11_OK 0
+#define DF11_ERR_BADARG (-1)  /* null pointer, negative size, unsupported table count ... */
+#define DF11_ERR_CUDA (-2)    /* a CUDA runtime call failed (message has the CUDA error)   */
+#define DF11_ERR_CORRUPT (-3) /* the DF11 tensors are inconsistent                         */
+#define DF11_ERR_NOSPACE (-4) /* an output buffer given by the caller is too small         */
+
+/* Bits a decode kernel ORs into the optional device status word. */
+#define DF11_STATUS_BAD_TABLE 1    /* pointer outside `luts`, or a code length of 0 or > 32 */
+#define DF11_STATUS_BAD_POSITIONS 2 /* output_positions not monotone / beyond n_elements    */
+#define DF11_STATUS_TRUNCATED 4    /* a format block holds more elements than max_block_elems */
+
+/* Library version, major*10000 + minor*100 + patch.  (The reference keeps a format
+ * version string, dfloat11.py:44; this number versions the ABI below.) */
+int df11_version(void);
+
+/* Message of the last error on the calling thread ("" if none). */
+const char *df11_last_error(void);
+
+/*
+ * Decompress one DF11 unit to BF16.  Replaces the reference's kernel launch
+ *   _decode(grid, block, shared_mem, args=[luts, encoded_exponent, sign_mantissa,
+ *           output_positions, gaps, out, n_luts, n_bytes, n_elements])
+ * (dfloat11/dfloat11.py:142-151, kernel signature dfloat11/decode.cu:25-34).
+ *
+ *   luts              device, uint8  [n_luts * 256]
+ *   codes             device, uint8  [n_bytes]           ("encoded_exponent")
+ *   sign_mantissa     device, uint8  [n_elements]
+ *   output_positions  device, uint32 [ceil(n_bytes/4096) + 1]
+ *   gaps              device, uint8  [ceil(n_bytes/4096) * 320]
+ *   out_bf16          device, uint16 [n_elements]        receives the BF16 bit patterns
+ *   max_block_elems   largest output_positions[b+1] - output_positions[b]; it sizes the
+ *                     kernel's shared-memory staging the way the reference's
+ *                     `shared_mem_size` does (dfloat11.py:299-306).  <= 0: assume the
+ *                     format's worst case (32768).
+ *   status            device, int32, optional (may be NULL): DF11_STATUS_* bits are
+ *                     ORed in when the kernel meets inconsistent tensors.  The kernel
+ *                     never traps, reads out of bounds or loops without bound on bad
+ *                     input; it only produces unspecified element values.
+ *   stream            a cudaStream_t (NULL = the legacy default stream)
+ *
+ * 64-bit sizes: units above 2^31 elements are fine (the reference's `int`
+ * arguments, decode.cu:33, overflow there).  Fast paths need `codes` 8-byte aligned,
+ * `sign_mantissa` 8-byte and `out_bf16` 16-byte aligned (any torch allocation is);
+ * other alignments work but decode slower.
+ */
+int df11_decode(const void *luts, const void *codes, const void *sign_mantissa,
+                const void *output_positions, const void *gaps, void *out_bf16,
+                int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                int32_t max_block_elems, void *status, int32_t device, void *stream);
+
+/*
+ * Optional two-step form for units that are decoded many times (every forward
+ * pass, dfloat11.py:119-151).  df11_prepare() runs once per unit and device: it
+ * fills a caller-owned auxiliary device buffer with (a) the multi-symbol decode
+ * table derived from `luts` and (b) the output offset of every 8-byte window
+ * inside its format block -- the result of the counting pass and block scan that
+ * the reference kernel redoes on every launch (decode.cu:104-178).
+ * df11_decode_prepared() then decodes in a single pass.  The DF11 tensors on disk
+ * are unchanged; the auxiliary buffer is derived data and can be rebuilt at any time.
+ *
+ * df11_aux_bytes(n_bytes) is the size of that buffer (about n_bytes/4 + 16 KiB).
+ * The buffer must be 16-byte aligned.  It has no counterpart in the reference.
+ */
+int64_t df11_aux_bytes(int64_t n_bytes);
+
+int df11_prepare(const void *luts, const void *codes, const void *output_positions,
+                 const void *gaps, void *aux, int64_t aux_bytes, int32_t n_luts,
+                 int64_t n_bytes, int64_t n_elements, void *status, int32_t device,
+                 void *stream);
+
+int df11_decode_prepared(const void *luts, const void *codes, const void *sign_mantissa,
+                         const void *output_positions, const void *gaps, const void *aux,
+                         void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                         int32_t max_block_elems, void *status, int32_t device, void *stream);
+
+/*
+ * Host-side check of one unit before its first launch (all pointers HOST memory).
+ * The reference performs no validation: a zero entry in the length row makes its
+ * kernel spin forever (decode.cu:116-118).  Checks: table count, pointers stay
+ * inside `luts`, every symbol reachable from the root has a length in 1..32,
+ * output_positions is monotone and ends at n_elements, tensor sizes agree.
+ * On success *max_block_elems (optional) receives the value df11_decode wants.
+ */
+int df11_validate_host(const void *luts, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                       const void *output_positions, int64_t n_positions, int64_t n_gap_bytes,
+                       int32_t *max_block_elems);
+
+/*
+ * Host-side bit packer for one unit; byte-identical to the reference's `encode`
+ * (dfloat11/dfloat11_utils.py:118-170) for the same code table, but linear-time
+ * native code instead of a per-symbol Python loop.  All pointers HOST memory.
+ *
+ *   exponents   uint8 [n_elements]        (W >> 7) & 0xFF of every BF16 weight
+ *   code_len    uint8 [256], code_val uint32 [256]   code of each exponent value
+ *               (length 0 = value does not occur)
+ *   pad_len / pad_val   code whose leading bits complete the last byte when the
+ *               stream does not end on a byte boundary (the reference uses its
+ *               end-of-stream code, dfloat11_utils.py:153-160); pad_len 0 = zero bits
+ * df11_encode_size() returns the stream length in bytes (or a negative error).
+ * df11_encode_host() fills
+ *   codes  [n_bytes], gaps [ceil(n_bytes/4096)*320], output_positions [ceil(n_bytes/4096)+1]
+ * using up to n_threads host threads.
+ */
+int64_t df11_encode_size(const void *exponents, int64_t n_elements, const void *code_len);
+
+int df11_encode_host(const void *exponents, int64_t n_elements, const void *code_len,
+                     const void *code_val, int32_t pad_len, uint32_t pad_val, void *codes,
+                     int64_t n_bytes, void *gaps, int64_t n_gap_bytes, void *output_positions,
+                     int64_t n_positions, int32_t n_threads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DF11_H */

@@ -1,0 +1,267 @@
+"""GPU parity tests of the decode kernels, called through the C ABI of libdf11.so.
+
+Bar: bit-exact.  Checked against (1) the original BF16 tensors, (2) the CPU oracle,
+(3) tensors produced by the reference's own encoder (tests/golden), and (4) the reference's
+own kernel run on the same GPU on identical inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from dfloat11_b200 import _lib, codec, ops
+from oracle import df11_oracle as oracle
+from oracle import ref_kernel
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _to_dev(g):
+    return dict(
+        luts=torch.from_numpy(np.ascontiguousarray(g["luts"])).to(DEV),
+        enc=torch.from_numpy(np.ascontiguousarray(g["encoded"])).to(DEV),
+        sm=torch.from_numpy(np.ascontiguousarray(g["sign_mantissa"])).to(DEV),
+        pos=torch.from_numpy(np.ascontiguousarray(g["output_positions"]).view(np.uint8).copy()).to(DEV),
+        gaps=torch.from_numpy(np.ascontiguousarray(g["gaps"])).to(DEV),
+    )
+
+
+def _bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def _widest(pos_u32):
+    return int(np.diff(np.asarray(pos_u32).astype(np.int64)).max())
+
+
+def _unit_from_weights(weights, n_threads=None):
+    t = codec.encode_weights(weights, n_threads=n_threads)
+    d = dict(luts=t["luts"].to(DEV), enc=t["encoded_exponent"].to(DEV), sm=t["sign_mantissa"].to(DEV),
+             pos=t["output_positions"].to(DEV), gaps=t["gaps"].to(DEV))
+    widest = _widest(t["output_positions"].numpy().view(np.uint32))
+    return t, d, widest
+
+
+@pytest.mark.parametrize("exact_cap", [False, True])
+def test_golden_two_pass(golden, exact_cap):
+    d = _to_dev(golden)
+    st = _status()
+    cap = _widest(golden["output_positions"]) if exact_cap else 0
+    out = torch.full((golden["w"].size,), -1.0, dtype=torch.bfloat16, device=DEV)
+    ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], out=out, max_block_elems=cap, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert np.array_equal(_bits(out), golden["w"])
+    want = oracle.decode_c(golden["luts"], golden["encoded"], golden["sign_mantissa"],
+                           golden["output_positions"], golden["gaps"])
+    assert np.array_equal(_bits(out), want)
+
+
+def test_golden_prepared(golden):
+    d = _to_dev(golden)
+    st = _status()
+    aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], golden["w"].size, status=st)
+    assert aux.numel() == ops.aux_bytes(d["enc"].numel())
+    for _ in range(2):   # the auxiliary buffer is reusable
+        out = torch.full((golden["w"].size,), -1.0, dtype=torch.bfloat16, device=DEV)
+        ops.decode_prepared(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], aux, out=out,
+                            max_block_elems=_widest(golden["output_positions"]), status=st)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        assert np.array_equal(_bits(out), golden["w"])
+
+
+@pytest.mark.parametrize("variant", ["shipped_ptx", "recompiled_sm100a"])
+def test_same_bits_as_reference_kernel(golden, variant):
+    if not ref_kernel.available(variant):
+        pytest.skip("reference kernel artefact not built (make -C oracle ref)")
+    d = _to_dev(golden)
+    smem = ref_kernel.shared_mem_size(golden["output_positions"])
+    ref_out = torch.zeros(golden["w"].size, dtype=torch.bfloat16, device=DEV)
+    ref_kernel.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], ref_out, smem, variant=variant)
+    out = ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"])
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(ref_out), golden["w"])
+    assert torch.equal(out.view(torch.int16), ref_out.view(torch.int16))
+
+
+def _scaled_llama_block(hidden, inter, kv, seed):
+    g = torch.Generator().manual_seed(seed)
+    shapes = [(hidden, hidden), (kv, hidden), (kv, hidden), (hidden, hidden),
+              (inter, hidden), (inter, hidden), (hidden, inter)]
+    return [(torch.randn(s, generator=g) * 0.02).to(torch.bfloat16) for s in shapes]
+
+
+def test_llama_block_small_vs_oracle_and_reference():
+    weights = _scaled_llama_block(512, 1792, 128, seed=0)       # 3.8 M elements, ~300 format blocks
+    t, d, widest = _unit_from_weights(weights)
+    want = torch.cat([w.reshape(-1) for w in weights])
+    st = _status()
+    out = ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], max_block_elems=widest, status=st)
+    aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], want.numel(), status=st)
+    out2 = ops.decode_prepared(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], aux,
+                               max_block_elems=widest, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16))
+    assert torch.equal(out2.cpu().view(torch.int16), want.view(torch.int16))
+    cpu = oracle.decode_c(t["luts"].numpy(), t["encoded_exponent"].numpy(), t["sign_mantissa"].numpy(),
+                          t["output_positions"].numpy(), t["gaps"].numpy(), n_threads=4)
+    assert np.array_equal(_bits(out), cpu)
+    if ref_kernel.available():
+        ref_out = torch.zeros_like(out)
+        ref_kernel.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], ref_out,
+                          512 * 4 + 4 + 2 * widest)
+        torch.cuda.synchronize()
+        assert torch.equal(ref_out.view(torch.int16), out.view(torch.int16))
+
+
+def test_llama_block_full_size_round_trip():
+    """BASELINE config 1: one Llama-3.1-8B block, 218 103 808 elements, N(0, 0.02), seed 0."""
+    weights = _scaled_llama_block(4096, 14336, 1024, seed=0)
+    t, d, widest = _unit_from_weights(weights)
+    want = torch.cat([w.reshape(-1) for w in weights]).to(DEV)
+    assert want.numel() == 218_103_808
+    st = _status()
+    out = ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], max_block_elems=widest, status=st)
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    out.zero_()
+    aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], want.numel(), status=st)
+    ops.decode_prepared(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], aux, out=out,
+                        max_block_elems=widest, status=st)
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    assert st.item() == 0
+    # the views the hook hands to the Linear layers are plain slices of the decoded buffer
+    parts = torch.tensor_split(out, t["split_positions"].tolist())
+    for p, w in zip(parts, weights):
+        assert p.numel() == w.numel()
+    # checksum-of-checksums against the original (size-independent property)
+    assert int(out.view(torch.int16).to(torch.int64).sum().item()) == \
+        int(want.view(torch.int16).to(torch.int64).sum().item())
+
+
+def test_misaligned_pointers_take_the_slow_paths(golden):
+    if golden["w"].size < 64:
+        pytest.skip("tiny case")
+    d = _to_dev(golden)
+
+    def shifted(t, k):
+        buf = torch.empty(t.numel() + 32, dtype=torch.uint8, device=DEV)
+        view = buf[k:k + t.numel()]
+        view.copy_(t)
+        return view
+
+    enc = shifted(d["enc"], 3)
+    sm = shifted(d["sm"], 5)
+    out_buf = torch.zeros(golden["w"].size + 8, dtype=torch.bfloat16, device=DEV)
+    out = out_buf[1:1 + golden["w"].size]          # 2-byte aligned only
+    st = _status()
+    ops.decode(d["luts"], enc, sm, d["pos"], d["gaps"], out=out, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert np.array_equal(_bits(out.contiguous()), golden["w"])
+    assert out_buf[0].item() == 0 and out_buf[1 + golden["w"].size].item() == 0
+
+
+def test_output_is_written_only_inside_the_unit(golden):
+    d = _to_dev(golden)
+    n = golden["w"].size
+    buf = torch.full((n + 64,), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], out=buf[:n])
+    torch.cuda.synchronize()
+    assert torch.all(buf[n:] == 7.0)
+    assert np.array_equal(_bits(buf[:n].contiguous()), golden["w"])
+
+
+def test_runs_on_a_side_stream(golden):
+    d = _to_dev(golden)
+    s = torch.cuda.Stream(device=DEV)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        out = ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"])
+    s.synchronize()
+    assert np.array_equal(_bits(out), golden["w"])
+
+
+def test_corrupt_units_set_status_and_return():
+    from tests.conftest import load_golden
+    g = load_golden("gauss_multi")
+    d = _to_dev(g)
+    n = g["w"].size
+    # 1. zero code lengths: the reference kernel would never terminate (decode.cu:116-118)
+    luts = d["luts"].clone()
+    luts[-1, :] = 0
+    st = _status()
+    ops.decode(luts, d["enc"], d["sm"], d["pos"], d["gaps"], status=st)
+    torch.cuda.synchronize()
+    assert st.item() & _lib.STATUS_BAD_TABLE
+    # 2. staging smaller than a block: flagged, no out-of-bounds write
+    st = _status()
+    buf = torch.full((n + 64,), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], out=buf[:n], max_block_elems=1000, status=st)
+    torch.cuda.synchronize()
+    assert st.item() & _lib.STATUS_TRUNCATED
+    assert torch.all(buf[n:] == 7.0)
+    # 3. output positions running backwards / past the end
+    pos = g["output_positions"].copy()
+    pos[1], pos[2] = pos[2], pos[1]
+    pos[-1] = n + 100000
+    st = _status()
+    buf = torch.full((n + 64,), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.decode(d["luts"], d["enc"], d["sm"], torch.from_numpy(pos.view(np.uint8).copy()).to(DEV), d["gaps"],
+               out=buf[:n], status=st)
+    torch.cuda.synchronize()
+    assert st.item() & _lib.STATUS_BAD_POSITIONS
+    assert torch.all(buf[n:] == 7.0)
+    # 4. random bytes as a stream: terminates, stays in bounds
+    st = _status()
+    noise = torch.randint(0, 256, (d["enc"].numel(),), dtype=torch.uint8, device=DEV)
+    buf = torch.full((n + 64,), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.decode(d["luts"], noise, d["sm"], d["pos"], d["gaps"], out=buf[:n], status=st)
+    torch.cuda.synchronize()
+    assert torch.all(buf[n:] == 7.0)
+
+
+def test_argument_errors_raise():
+    from tests.conftest import load_golden
+    d = _to_dev(load_golden("gauss_n3"))
+    with pytest.raises(RuntimeError):
+        ops.decode(d["luts"].cpu(), d["enc"], d["sm"], d["pos"], d["gaps"])
+    with pytest.raises(_lib.DF11Error):
+        ops.decode(d["luts"][:1], d["enc"], d["sm"], d["pos"], d["gaps"])       # n_luts = 1
+    with pytest.raises(RuntimeError):
+        ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"],
+                   out=torch.empty(1, dtype=torch.bfloat16, device=DEV))           # too small
+
+
+@pytest.mark.parametrize("case", ["one_bit_codes", "eight_bit_codes", "deep_codes", "single_symbol"])
+def test_synthetic_distributions(case):
+    rng = np.random.default_rng(17)
+    n = 700_000
+    if case == "one_bit_codes":
+        e = (rng.random(n) < 0.9).astype(np.uint16) * 3 + 100         # 90 % one symbol
+    elif case == "eight_bit_codes":
+        e = rng.integers(0, 240, size=n).astype(np.uint16)
+    elif case == "deep_codes":
+        p = 0.5 ** np.arange(1, 41)
+        e = rng.choice(np.arange(60, 100), size=n, p=p / p.sum()).astype(np.uint16)
+    else:
+        e = np.full(n, 127, dtype=np.uint16)
+    sm = rng.integers(0, 256, size=n).astype(np.uint16)
+    w = (((sm & 0x80) << 8) | (e << 7) | (sm & 0x7F)).astype(np.uint16)
+    weight = torch.from_numpy(w.view(np.int16)).view(torch.bfloat16)
+    t, d, widest = _unit_from_weights([weight])
+    st = _status()
+    out = ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], max_block_elems=widest, status=st)
+    aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], n, status=st)
+    out2 = ops.decode_prepared(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], aux, max_block_elems=widest,
+                               status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert np.array_equal(_bits(out), w)
+    assert np.array_equal(_bits(out2), w)
