@@ -45,7 +45,8 @@ sys.path.insert(0, ROOT)
 QWEN3_8B = dict(name="qwen3-8b-shape", layers=36, hidden=4096, kv=1024, inter=12288, vocab=151936)
 LLAMA_8B = dict(name="llama3.1-8b-shape", layers=32, hidden=4096, kv=1024, inter=14336, vocab=128256)
 SMALL = dict(name="small-smoke", layers=2, hidden=1024, kv=256, inter=3072, vocab=8192)
-WORKLOADS = {"qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "small": SMALL}
+ONE_BLOCK = dict(name="one-llama-block", layers=1, hidden=4096, kv=1024, inter=14336, vocab=0)
+WORKLOADS = {"qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "small": SMALL, "block": ONE_BLOCK}
 
 
 def block_shapes(cfg):
@@ -55,10 +56,11 @@ def block_shapes(cfg):
 
 def unit_plan(cfg):
     """(name, n_elements, std) of every compressed unit in forward order."""
-    plan = [("embed_tokens", cfg["vocab"] * cfg["hidden"], 1.0)]
     n_block = sum(a * b for a, b in block_shapes(cfg))
-    plan += [(f"layers.{i}", n_block, 0.02) for i in range(cfg["layers"])]
-    plan.append(("lm_head", cfg["vocab"] * cfg["hidden"], 0.02))
+    plan = [(f"layers.{i}", n_block, 0.02) for i in range(cfg["layers"])]
+    if cfg["vocab"]:
+        plan = [("embed_tokens", cfg["vocab"] * cfg["hidden"], 1.0)] + plan
+        plan.append(("lm_head", cfg["vocab"] * cfg["hidden"], 0.02))
     return plan
 
 
@@ -113,7 +115,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:  # noqa: BLE001 - clocks are advisory
             self.proc = None
@@ -310,7 +312,7 @@ def main():
     plan = unit_plan(cfg)
     units = []
     for i, (name, n, std) in enumerate(plan):
-        keep = (i == 1 and rank == 0)       # the first transformer block also feeds the CPU baseline
+        keep = (name == "layers.0" and rank == 0)   # the first transformer block also feeds the CPU baseline
         units.append(make_unit(n, std, seed=1000 * (1 + rank) + i, device=device, keep_host=keep))
     scratch = torch.empty(max(u["n_elements"] for u in units), dtype=torch.bfloat16, device=device)
     status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -401,7 +403,7 @@ def main():
         if e2e is not None:
             result["e2e"] = e2e
         if not args.skip_extras:
-            block = units[1]
+            block = next(u for u, (name, _, _) in zip(units, plan) if name == "layers.0")
             result["reference_gpu_kernel"] = time_reference_gpu_kernel(block, scratch)
             from oracle import df11_oracle as oracle
             oracle.build()

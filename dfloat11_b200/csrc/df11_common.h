@@ -26,27 +26,31 @@
 #define DF11_MAX_CODE_LEN 32                         // dfloat11_utils.py:49 keeps codes <= 32 bits
 
 // ---------------------------------------------------------------------------
-// Multi-symbol decode table.
+// Multi-symbol tables, both indexed by the next K bits of the stream.  An entry
+// covers up to four consecutive symbols that the reference's byte-wise LUT walk
+// (decode.cu:105-118) is certain to produce for EVERY stream starting with those
+// K bits; "escape" means the first symbol cannot be resolved from K bits and the
+// full walk must be done for it.
 //
-// Index: the next K bits of the stream.  Entry: up to four consecutive symbols
-// that the reference's byte-wise LUT walk (decode.cu:105-118) is certain to
-// produce for EVERY stream that starts with those K bits.
+//   decode entry (64 bit): .meta = bits consumed | symbols << 8   (escape: 1 << 24)
+//                          .syms = the symbols, first one in the lowest byte
+//   count entry  (32 bit): bits 0..7  bits consumed              (escape: 128)
+//                          bits 8..10 symbols                    (escape: 0)
+//                          bits 16..31 start offset of the 1st..4th symbol, 4 bits
+//                                     each, 15 when absent      (escape: all 15)
 //
-//   meta (32 bit):  bits 0..5   total bits consumed by the symbols in the entry
-//                   bits 8..10  number of symbols, 0 = "escape": the first symbol
-//                               cannot be resolved from K bits, do the full walk
-//                   bits 16..19 / 20..23 / 24..27  start offset (in bits) of the
-//                               2nd / 3rd / 4th symbol, 15 when absent
-//   syms (32 bit):  the symbols, first one in the lowest byte
+// The decoding loops keep "position in window" and "output slot" in ONE register
+//   acc = pos | slot << 8
+// so that `acc += meta` advances both; the escape value pushes the slot past any
+// legal end, which ends the loop without a test inside it.
 // ---------------------------------------------------------------------------
 struct Df11Entry {
     uint32_t meta;
     uint32_t syms;
 };
 
-#define DF11_META_NBITS(m) ((m) & 0x3Fu)
-#define DF11_META_NSYMS(m) (((m) >> 8) & 7u)
-#define DF11_META_ESCAPE 0x0FFF0000u
+#define DF11_DEC_ESCAPE (1u << 24)
+#define DF11_CNT_ESCAPE 0xFFFF0080u
 
 // Offset of level-u "all equal" flags in the 255-byte agreement table: flag
 // (u, blk) says that root-row entries [blk << u, (blk + 1) << u) are all equal.
@@ -63,87 +67,69 @@ DF11_HD uint8_t df11_agree_flag(const uint8_t *root, int u, int blk)
     return same;
 }
 
-// The exact per-symbol rule of the reference (decode.cu:105-116) applied to the 32
-// bits `x` (MSB first).  `luts` has n_luts rows of 256, the last row holds code
-// lengths.  Returns the symbol; *len receives its code length.  *bad is set when the
-// tables are unusable here (pointer outside the tensor, length 0 or > 32) -- the
-// reference would read out of bounds or never terminate in those cases.
-DF11_HD uint32_t df11_walk(const uint8_t *luts, int n_luts, uint32_t x, uint32_t *len, int *bad)
-{
-    uint32_t e = luts[x >> 24];
-#ifdef __CUDA_ARCH__
-#pragma unroll
-#endif
-    for (int shift = 16; shift >= 0; shift -= 8) {
-        if (e >= 240u) {
-            uint32_t row = 256u - e;
-            if (row >= (uint32_t)n_luts) {
-                *bad = 1;
-                row = 0;
-            }
-            e = luts[row * 256u + ((x >> shift) & 255u)];
-        }
-    }
-    uint32_t l = luts[(uint32_t)(n_luts - 1) * 256u + e];
-    if (l == 0u || l > (uint32_t)DF11_MAX_CODE_LEN) {
-        *bad = 1;
-        l = 64u;  // leave the window
-    }
-    *len = l;
-    return e;
-}
-
-// Builds the entry for K-bit index v.  `agree` is the 255-byte agreement table of the
-// root row.  A symbol is taken into the entry only when every completion of the
-// unknown trailing bits makes the reference's root lookup return the same non-pointer
-// byte, so the entry never differs from the reference's symbol-by-symbol result.
-DF11_HD Df11Entry df11_build_entry(const uint8_t *luts, int n_luts, const uint8_t *agree,
-                                   uint32_t v, int K)
+// Builds the entries for K-bit index v (K <= 14).  `agree` is the 255-byte agreement
+// table of the root row.  A symbol is taken into the entry only when every completion
+// of the unknown trailing bits makes the reference's walk (root row, and one second-level
+// row for codes of 9 bits and more) end on the same symbol, and every symbol of an entry
+// starts inside the K index bits, so an entry never differs from the reference's
+// symbol-by-symbol result.
+DF11_HD void df11_build_entry(const uint8_t *luts, int n_luts, const uint8_t *agree, uint32_t v, int K,
+                              Df11Entry *dec, uint32_t *cnt)
 {
     const uint8_t *lens = luts + (n_luts - 1) * 256;
     const uint32_t left = v << (32 - K);  // index bits, left-aligned
-    uint32_t c = 0, nsyms = 0, syms = 0, starts = 0x0FFF0000u;
+    uint32_t c = 0, nsyms = 0, syms = 0, starts = 0xFFFF0000u;
     for (int j = 0; j < 4; ++j) {
         const int r = K - (int)c;  // index bits still unread
         if (r <= 0)
-            break;  // every symbol of an entry starts inside the K index bits
+            break;
         const int u = r >= 8 ? 0 : 8 - r;  // unknown low bits of this symbol's root byte
-        const uint32_t idx = c < 32u ? ((left << c) >> 24) : 0u;
+        const uint32_t idx = (left << c) >> 24;
         if (u > 0 && !agree[df11_agree_offset(u) + (int)(idx >> u)])
             break;
-        const uint32_t e = luts[idx];
-        if (e >= 240u)
-            break;  // pointer to a deeper row: needs bits we may not have
+        uint32_t e = luts[idx];
+        if (e >= 240u) {
+            // pointer to a second-level row, indexed by the next stream byte: usable when the
+            // root byte is fully known and every completion of the second byte agrees
+            const uint32_t row = 256u - e;
+            const int r2 = r - 8;  // known bits of the second byte
+            if (u > 0 || r2 <= 0 || row >= (uint32_t)n_luts)
+                break;
+            const int u2 = r2 >= 8 ? 0 : 8 - r2;
+            const uint32_t idx2 = ((left << c) >> 16) & 255u & ~((1u << u2) - 1u);
+            const uint8_t *sub = luts + row * 256u;
+            e = sub[idx2];
+            bool same = true;
+            for (uint32_t k = 1; k < (1u << u2); ++k)
+                same = same && sub[idx2 + k] == e;
+            if (!same || e >= 240u)
+                break;  // ambiguous, or a third level: left to the full walk
+        }
         const uint32_t l = lens[e];
         if (l == 0u || l > (uint32_t)DF11_MAX_CODE_LEN)
             break;
-        if (j > 0) {
-            starts &= ~(0xFu << (12 + 4 * j));
-            starts |= c << (12 + 4 * j);
-        }
+        starts &= ~(0xFu << (16 + 4 * j));
+        starts |= c << (16 + 4 * j);
         syms |= e << (8 * j);
         ++nsyms;
         c += l;
-        if (c >= 15u)
-            break;  // start offsets are stored in 4 bits, 15 meaning "absent" (K <= 14)
     }
-    Df11Entry out;
     if (nsyms == 0) {
-        out.meta = DF11_META_ESCAPE;
-        out.syms = 0;
+        dec->meta = DF11_DEC_ESCAPE;
+        dec->syms = 0;
+        *cnt = DF11_CNT_ESCAPE;
     } else {
-        out.meta = c | (nsyms << 8) | starts;
-        out.syms = syms;
+        dec->meta = c | (nsyms << 8);
+        dec->syms = syms;
+        *cnt = c | (nsyms << 8) | starts;
     }
-    return out;
 }
 
-// Number of symbols of a non-escape entry that start before bit offset `lim`
-// (lim >= 1; the first symbol starts at 0).
-DF11_HD uint32_t df11_owned_syms(uint32_t meta, uint32_t lim)
+// Number of symbols of a count entry that start before bit offset `lim` (1 <= lim <= 15).
+DF11_HD uint32_t df11_owned_syms(uint32_t cmeta, uint32_t lim)
 {
-    return 1u + (uint32_t)(((meta >> 16) & 15u) < lim) + (uint32_t)(((meta >> 20) & 15u) < lim) +
-           (uint32_t)(((meta >> 24) & 15u) < lim);
+    return (uint32_t)(((cmeta >> 16) & 15u) < lim) + (uint32_t)(((cmeta >> 20) & 15u) < lim) +
+           (uint32_t)(((cmeta >> 24) & 15u) < lim) + (uint32_t)((cmeta >> 28) < lim);
 }
 
 // 5-bit gap of window t (decode.cu:85-87) without the reference's read past the end.
@@ -157,12 +143,35 @@ DF11_HD uint32_t df11_gap(const uint8_t *gaps, int64_t n_gap_bytes, int64_t t)
     return (((hi << 8) | lo) >> (11 - r)) & 31u;
 }
 
-// Two BF16 values from two exponent bytes and two sign/mantissa bytes packed as
-// (e1 : sm1 : e0 : sm0), i.e. each half is exponent<<8 | sign<<7 | mantissa.
-// decode.cu:207-209 per element:  hi = (sm & 0x80) | (e >> 1),  lo = (e << 7) | (sm & 0x7f).
-DF11_HD uint32_t df11_merge_pair(uint32_t w)
+// Byte permute with the semantics of CUDA's __byte_perm for selector nibbles 0..7.
+DF11_HD uint32_t df11_prmt(uint32_t x, uint32_t y, uint32_t sel)
 {
-    return ((w >> 1) & 0x7F807F80u) | ((w << 8) & 0x80008000u) | (w & 0x007F007Fu);
+#ifdef __CUDA_ARCH__
+    return __byte_perm(x, y, sel);
+#else
+    const uint64_t both = ((uint64_t)y << 32) | x;
+    uint32_t r = 0;
+    for (int i = 0; i < 4; ++i)
+        r |= (uint32_t)((both >> (8 * ((sel >> (4 * i)) & 7u))) & 0xFFu) << (8 * i);
+    return r;
+#endif
+}
+
+// Four BF16 values from four exponent bytes `e4` and four sign/mantissa bytes `m4`
+// (element k in byte k).  Per element, decode.cu:207-209:
+//   high byte = (sm & 0x80) | (e >> 1),   low byte = (e << 7) | (sm & 0x7f).
+// Both bytes are formed for all four elements at once, then interleaved.
+DF11_HD void df11_merge4(uint32_t e4, uint32_t m4, uint32_t *out01, uint32_t *out23)
+{
+    const uint32_t hi = ((e4 >> 1) & 0x7F7F7F7Fu) | (m4 & 0x80808080u);
+    const uint32_t lo = ((e4 << 7) & 0x80808080u) | (m4 & 0x7F7F7F7Fu);
+    *out01 = df11_prmt(lo, hi, 0x5140);
+    *out23 = df11_prmt(lo, hi, 0x7362);
+}
+
+DF11_HD uint16_t df11_merge1(uint32_t e, uint32_t m)
+{
+    return (uint16_t)(((m & 0x80u) << 8) | (e << 7) | (m & 0x7Fu));
 }
 
 // ---------------------------------------------------------------------------
@@ -191,71 +200,207 @@ DF11_HD uint32_t df11_peek(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t pos)
     return df11_funnel_l(b, a, pos);
 }
 
-// Counting pass: number of codes that START inside the window's 64 bits (the
-// ownership rule of decode.cu:104,129), beginning at bit `gap`.
-template <int K>
-DF11_HD uint32_t df11_count_window(const Df11Entry *table, const uint8_t *luts, int n_luts,
-                                   uint32_t w0, uint32_t w1, uint32_t w2, uint32_t gap, int *bad)
+// The two window routines are written against a memory policy `M` so that the CUDA
+// kernels (32-bit shared-memory addresses, explicit ld/st.shared) and the host
+// emulation used by the CPU tests (plain arrays) run the same algorithm:
+//   uint32_t  M::cnt(i)        count-table entry i
+//   Df11Entry M::dec(i)        decode-table entry i
+//   uint32_t  M::lut(i)        byte i of the `luts` tensor (for the escape walk)
+//   void      M::put<OFF>(slot, v)   stage byte (slot + OFF) = v & 0xFF
+//
+// df11_walk_m is the exact per-symbol rule of the reference (decode.cu:105-116) applied
+// to the 32 bits `x` (MSB first): row 0 is indexed by the first byte, an entry >= 240
+// points to row 256 - entry indexed by the next byte (at most four levels), the last row
+// holds code lengths.  *bad is set when the tables are unusable (pointer outside the
+// tensor, length 0 or > 32) -- the reference would read out of bounds or never terminate.
+template <class M>
+DF11_HD uint32_t df11_walk_m(const M &m, int n_luts, uint32_t x, uint32_t *len, int *bad)
 {
-    uint32_t pos = gap, cnt = 0;
-    // all K index bits inside the window: every symbol of the entry starts before bit 64
-    while (pos <= 64u - K) {
-        const uint32_t x = df11_peek(w0, w1, w2, pos);
-        const uint32_t meta = table[x >> (32 - K)].meta;
-        if (DF11_META_NSYMS(meta) == 0u) {
-            uint32_t len;
-            df11_walk(luts, n_luts, x, &len, bad);
-            cnt += 1u;
-            pos += len;
-        } else {
-            cnt += DF11_META_NSYMS(meta);
-            pos += DF11_META_NBITS(meta);
+    uint32_t e = m.lut(x >> 24);
+#ifdef __CUDA_ARCH__
+#pragma unroll
+#endif
+    for (int shift = 16; shift >= 0; shift -= 8) {
+        if (e >= 240u) {
+            uint32_t row = 256u - e;
+            if (row >= (uint32_t)n_luts) {
+                *bad = 1;
+                row = 0;
+            }
+            e = m.lut(row * 256u + ((x >> shift) & 255u));
         }
     }
-    // the last few bits: count only the symbols that start before bit 64
-    while (pos < 64u) {
-        const uint32_t x = df11_peek(w0, w1, w2, pos);
-        const uint32_t meta = table[x >> (32 - K)].meta;
-        if (DF11_META_NSYMS(meta) == 0u) {
-            uint32_t len;
-            df11_walk(luts, n_luts, x, &len, bad);
-            cnt += 1u;
-            pos += len;
-        } else {
-            cnt += df11_owned_syms(meta, 64u - pos);
-            pos += DF11_META_NBITS(meta);
-        }
+    uint32_t l = m.lut((uint32_t)(n_luts - 1) * 256u + e);
+    if (l == 0u || l > (uint32_t)DF11_MAX_CODE_LEN) {
+        *bad = 1;
+        l = 64u;  // leave the window
     }
-    return cnt;
+    *len = l;
+    return e;
 }
 
-// Decoding pass: writes the window's exponents to stage[o .. end).  Terminates after
-// at most end - o probes whatever the data is.
-template <int K>
-DF11_HD void df11_decode_window(const Df11Entry *table, const uint8_t *luts, int n_luts, uint32_t w0,
-                                uint32_t w1, uint32_t w2, uint32_t gap, uint8_t *stage, int o, int end,
-                                int *bad)
+// Counting pass: number of codes that START inside the window's 64 bits (the
+// ownership rule of decode.cu:104,129), beginning at bit `gap`.
+template <int K, class M>
+DF11_HD uint32_t df11_count_window(const M &m, int n_luts, uint32_t w0, uint32_t w1, uint32_t w2,
+                                   uint32_t gap, int *bad)
+{
+    uint32_t acc = gap;  // pos | count << 8   (a caller with nothing to count passes gap = 64)
+    for (;;) {
+        // all K index bits inside the window: every symbol of an entry starts before bit 64
+        while ((acc & 0xFFu) <= 64u - K) {
+            const uint32_t x = df11_peek(w0, w1, w2, acc);
+            acc += m.cnt(x >> (32 - K)) & 0xFFFFu;
+        }
+        // the last few bits: count only the symbols that start before bit 64
+        while ((acc & 0xFFu) < 64u) {
+            const uint32_t x = df11_peek(w0, w1, w2, acc);
+            const uint32_t c = m.cnt(x >> (32 - K));
+            acc += (c & 0xFFu) + (df11_owned_syms(c, 64u - (acc & 0xFFu)) << 8);
+        }
+        if ((acc & 0xFFu) < 128u)
+            break;
+        // an escape entry added 128 to the position: take that one symbol the long way
+        acc -= 128u;
+        uint32_t len;
+        df11_walk_m(m, n_luts, df11_peek(w0, w1, w2, acc), &len, bad);
+        acc += len + 256u;
+    }
+    return acc >> 8;
+}
+
+// Decoding pass: writes the window's exponents to stage slots [o, end).  Terminates
+// after at most end - o probes whatever the data is, and writes nothing outside.
+template <int K, class M>
+DF11_HD void df11_decode_window(const M &m, int n_luts, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t gap,
+                                uint32_t o, uint32_t end, int *bad)
+{
+    uint32_t acc = gap | (o << 8);  // pos | slot << 8
+    const uint32_t end_acc = end << 8;
+    for (;;) {
+        // at least four slots left: store all four bytes of an entry; the ones past its
+        // symbol count are rewritten by this thread's next probe
+        while (acc + (3u << 8) < end_acc) {
+            const Df11Entry e = m.dec(df11_peek(w0, w1, w2, acc) >> (32 - K));
+            const uint32_t slot = acc >> 8;
+            m.template put<0>(slot, e.syms);
+            m.template put<1>(slot, e.syms >> 8);
+            m.template put<2>(slot, e.syms >> 16);
+            m.template put<3>(slot, e.syms >> 24);
+            acc += e.meta;
+        }
+        // fewer than four left: bytes past `end` belong to the next window
+        while (acc < end_acc) {
+            const Df11Entry e = m.dec(df11_peek(w0, w1, w2, acc) >> (32 - K));
+            const uint32_t slot = acc >> 8, rem = end - slot;
+            m.template put<0>(slot, e.syms);
+            if (rem > 1u) m.template put<1>(slot, e.syms >> 8);
+            if (rem > 2u) m.template put<2>(slot, e.syms >> 16);
+            acc += e.meta;
+        }
+        if (!(acc & DF11_DEC_ESCAPE))
+            break;
+        // an escape entry ended the loop: decode that one symbol with the full walk
+        acc -= DF11_DEC_ESCAPE;
+        uint32_t len;
+        const uint32_t s = df11_walk_m(m, n_luts, df11_peek(w0, w1, w2, acc), &len, bad);
+        if (acc < end_acc) m.template put<0>(acc >> 8, s);
+        acc += len + 256u;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Seek points (prepared form).  A one-time pass records, for every group of EPT
+// consecutive output elements (EPT = 16 or 32, groups aligned to EPT in the element
+// index), the absolute bit position in the stream at which the group's first code
+// starts.  A decoding thread then needs nothing but its group number: it reads the
+// group's bit position, decodes exactly EPT codes from there and writes EPT BF16
+// values -- no shared staging, no scan, no barrier.
+//
+// Storage: bit position = (hi[g / 32] << 16 | lo[g]) (+ 65536 if lo[g] < lo[32*(g/32)]),
+// i.e. 16 bits per group plus 32 bits per 32 groups; the 32 groups of one entry of
+// `hi` span at most 31 * 32 * 32 < 65536 bits, so one wrap-around is unambiguous.
+// ---------------------------------------------------------------------------
+
+// Walks the codes owned by one window (as df11_count_window does) knowing the output
+// index of its first code, and reports every code whose index is a multiple of `ept`:
+// emit(group, bit offset inside the window).  Extra policy member: none.
+template <int K, class M, class Emit>
+DF11_HD void df11_mark_window(const M &m, int n_luts, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t gap,
+                              uint64_t first_index, uint32_t ept, Emit emit, int *bad)
 {
     uint32_t pos = gap;
-    while (o < end) {
+    uint64_t idx = first_index;
+    while (pos < 64u) {
         const uint32_t x = df11_peek(w0, w1, w2, pos);
-        const Df11Entry e = table[x >> (32 - K)];
-        if (DF11_META_NSYMS(e.meta) == 0u) {
-            uint32_t len;
-            const uint32_t s = df11_walk(luts, n_luts, x, &len, bad);
-            stage[o] = (uint8_t)s;
-            o += 1;
-            pos += len;
+        const uint32_t c = m.cnt(x >> (32 - K));
+        uint32_t n, nbits, starts;
+        if (c == DF11_CNT_ESCAPE) {
+            df11_walk_m(m, n_luts, x, &nbits, bad);
+            n = 1u;
+            starts = 0u;
         } else {
-            // Bytes past the entry's symbol count are rewritten by the same thread's next
-            // probe; bytes past `end` belong to the next window and are not touched.
-            const int rem = end - o;
-            stage[o] = (uint8_t)e.syms;
-            if (rem > 1) stage[o + 1] = (uint8_t)(e.syms >> 8);
-            if (rem > 2) stage[o + 2] = (uint8_t)(e.syms >> 16);
-            if (rem > 3) stage[o + 3] = (uint8_t)(e.syms >> 24);
-            o += (int)DF11_META_NSYMS(e.meta);
-            pos += DF11_META_NBITS(e.meta);
+            const uint32_t lim = 64u - pos;
+            n = lim >= 15u ? ((c >> 8) & 7u) : df11_owned_syms(c, lim);
+            nbits = c & 0xFFu;
+            starts = c >> 16;
+        }
+        const uint32_t k = (uint32_t)(0u - (uint32_t)idx) & (ept - 1u);  // distance to the next multiple
+        if (k < n)
+            emit((idx + k) / ept, pos + ((starts >> (4u * k)) & 15u));
+        idx += n;
+        pos += nbits;
+    }
+}
+
+// Decodes the EPT codes of one group and hands them over four at a time, packed lowest
+// byte first.  The group's first code starts `bit` (0..31) bits into stream word
+// `word_index` (32-bit big-endian words; streams up to 16 GiB).  A lane with no group to
+// decode passes active = false.  (The fast kernel runs this loop as hand-scheduled device
+// code, df11_decode.cu; this is the statement of the algorithm and the form the CPU tests run.)
+// Extra policy members:
+//   uint32_t M::word(i)            stream bytes [4i, 4i+4) as a big-endian word, 0 past the end
+//   void     M::flush(k, word)     exponents 4k .. 4k+3 of the group
+//
+// The 96-bit window is shifted so that the next code to decode is at position 0 whenever
+// it is (re)loaded; a group of 16 codes rarely needs more than the 64 positions that
+// gives, so the reload inside the loop is the exception, not the rule.
+template <int K, int EPT, class M>
+DF11_HD void df11_decode_group(const M &m, int n_luts, uint32_t word_index, uint32_t bit, bool active, int *bad)
+{
+    constexpr uint32_t kDone = (uint32_t)EPT << 8;
+    uint32_t w0 = 0, w1 = 0, w2 = 0;
+    uint32_t acc = active ? 64u : kDone;  // pos | codes done << 8; pos >= 64 asks for a (re)load
+    uint32_t q = 0;                       // fewer than four pending exponents, lowest byte first
+    word_index -= 2u;                     // the first load advances by the 64 positions pretended above
+    while (acc < kDone) {
+        {
+            if (acc & 64u) {
+                // (re)load: the window starts at the code the position has reached
+                const uint32_t at = bit + (acc & 0x7Fu);  // position 64..127 relative to the old window
+                word_index += at >> 5;
+                bit = at & 31u;
+                const uint32_t a = m.word(word_index), b = m.word(word_index + 1u);
+                const uint32_t c = m.word(word_index + 2u), d = m.word(word_index + 3u);
+                w0 = df11_funnel_l(b, a, bit);
+                w1 = df11_funnel_l(c, b, bit);
+                w2 = df11_funnel_l(d, c, bit);
+                acc &= ~0xFFu;
+            }
+            const uint32_t x = df11_peek(w0, w1, w2, acc);
+            Df11Entry e = m.dec(x >> (32 - K));
+            if (e.meta == DF11_DEC_ESCAPE) {
+                uint32_t len;
+                e.syms = df11_walk_m(m, n_luts, x, &len, bad);
+                e.meta = len | 256u;
+            }
+            const uint32_t sh = (acc >> 5) & 0x18u;  // 8 * (codes done mod 4)
+            const uint32_t lo = q | (e.syms << sh);
+            const uint32_t old = acc;
+            acc += e.meta;
+            const bool complete = ((acc ^ old) & 0xFC00u) != 0u;  // the count crossed a multiple of four
+            if (complete) m.flush((old >> 10) & 0x3Fu, lo);
+            q = complete ? df11_funnel_l(e.syms, 0u, sh) : lo;  // exponents that did not fit / all pending
         }
     }
 }

@@ -1,24 +1,35 @@
 // DF11 -> BF16 decompression kernels for B200 (sm_100a) and their C entry points.
 //
 // What one launch computes is fixed by the reference kernel dfloat11/decode.cu:25-253
-// (see df11_common.h for the format); how it is computed is not taken from it:
+// (see df11_common.h for the format); how it is computed is not taken from it.
 //
-//   * persistent CTAs: grid = SMs x resident CTAs, each CTA walks format blocks
-//     b, b + grid, ... and builds its lookup tables in shared memory once;
-//   * a 2^K-entry multi-symbol table (up to four exponents per probe, derived from
-//     `luts`) replaces the reference's 2-5 dependent global loads per symbol;
-//   * a window (8 stream bytes + 4 look-ahead) lives in three registers, loaded
-//     with one 8-byte and one 4-byte coalesced load;
-//   * output slots come from a warp-shuffle scan (2 barriers per block, not 18),
-//     or -- in the prepared form -- from per-window offsets computed once per unit;
-//   * decoded exponents are staged as bytes in shared memory and merged with the
-//     sign/mantissa bytes eight elements at a time: one 8-byte load, one 16-byte
-//     fully coalesced store per thread;
-//   * every loop is bounded and every index is clamped: inconsistent tensors set a
-//     status bit instead of hanging (decode.cu:116-118 can spin forever).
+// Two decoders live here.
+//
+// df11_fast_kernel (behind df11_decode_prepared): a one-time pass over a unit
+// (df11_sync_kernel, behind df11_prepare) records a seek point -- the stream bit position
+// -- for every group of 16 or 32 consecutive output elements.  Afterwards a thread needs
+// only its group number: it reads the seek point, pulls the stream words it needs through
+// L1 (neighbouring threads read neighbouring words), decodes exactly one group with a
+// 2^K-entry multi-symbol table held in shared memory (up to four exponents per probe), merges
+// the exponents with one 16-byte load of sign/mantissa bytes and writes 16-byte stores.  No
+// staging of exponents, no scan, no barrier in the steady state; all global accesses of a
+// warp are contiguous.
+//
+// df11_decode_kernel (behind df11_decode): needs nothing but the six DF11 tensors.
+// Persistent CTAs walk the format blocks; every global read is a TMA bulk copy
+// (cp.async.bulk with mbarrier completion, no multicast): the next block's bitstream and
+// gap bytes arrive in a double buffer while the current block is decoded, and the block's
+// sign/mantissa bytes arrive while its exponents are decoded.  One window per thread in
+// three registers; output slots from a counting pass and a warp-shuffle scan (2 barriers
+// per block instead of the reference's 18); exponents staged as bytes in shared memory and
+// merged eight elements at a time with 16-byte coalesced stores.
+//
+// In both, every loop and every wait is bounded and every index is clamped: inconsistent
+// tensors set a status bit instead of hanging (decode.cu:116-118 can spin forever).
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -31,9 +42,12 @@ namespace {
 
 constexpr int kThreads = 512;  // one window per thread, one format block per CTA pass
 constexpr int kWarps = kThreads / 32;
-constexpr int kTableBits = 11;  // K: index width of the multi-symbol table
+constexpr int kTableBits = 11;  // K: index width of the multi-symbol tables
 
-enum Mode { kTwoPass = 0, kCount = 1, kPrepared = 2 };
+constexpr int kCodesBufBytes = DF11_BLOCK_BYTES + 16;      // block + look-ahead, multiple of 16
+constexpr int kInBufBytes = kCodesBufBytes + DF11_GAP_BYTES_PER_BLOCK;  // stream bytes, then gap bytes
+constexpr uint32_t kWaitLimit = 1u << 16;                  // bounded mbarrier polling
+constexpr int kFastThreads = 256;
 
 struct Params {
     const uint8_t *luts;
@@ -42,181 +56,629 @@ struct Params {
     const uint32_t *pos;
     const uint8_t *gaps;
     uint16_t *out;
-    const Df11Entry *table_g;  // prebuilt table in global memory, or null: build it here
-    uint16_t *woff;            // per-window element offset inside its format block
+    const Df11Entry *table_g;  // prebuilt decode table in global memory (prepared form)
+    uint32_t *sync_hi;         // seek points: high part, one per 32 groups
+    uint16_t *sync_lo;         // seek points: low 16 bits, one per group
     int *status;
     int64_t n_bytes;
     int64_t n_elements;
     int64_t n_blocks;
-    int64_t n_gap_bytes;
+    int64_t n_chunks;          // ceil(number of groups / 32)
     int n_luts;
-    int stage_cap;  // elements the shared staging area can hold (including phase)
-    int codes_aligned;
-    int io_aligned;
+    int ept;          // elements per seek point (16 or 32)
+    int stage_bytes;  // shared staging area (and sign/mantissa tile), multiple of 16
+    int codes_aligned;  // bit 0: codes 16-byte aligned, bit 1: gaps 16-byte aligned (bulk copies allowed),
+                        // bit 2: codes 4-byte aligned (word loads allowed)
+    int sm_aligned;     // sign_mantissa 16-byte aligned: bulk copies / 16-byte loads allowed
+    int out_aligned;    // out 16-byte aligned: vector stores allowed
 };
 
-__device__ __forceinline__ void load_window(const Params &p, int64_t t, uint32_t &w0, uint32_t &w1,
-                                            uint32_t &w2)
+// ---- shared-memory accessors: explicit 32-bit shared addresses ---------------------------
+__device__ __forceinline__ uint32_t lds32(uint32_t a)
 {
-    const int64_t off = t * DF11_WINDOW_BYTES;
-    if (p.codes_aligned && off + 12 <= p.n_bytes) {
-        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p.codes + off));
-        const uint32_t x = __ldg(reinterpret_cast<const uint32_t *>(p.codes + off + 8));
-        w0 = __byte_perm(v.x, 0, 0x0123);
-        w1 = __byte_perm(v.y, 0, 0x0123);
-        w2 = __byte_perm(x, 0, 0x0123);
-    } else {
-        uint32_t w[3] = {0, 0, 0};
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ void sts8(uint32_t a, uint32_t v)
+{
+    asm volatile("st.shared.u8 [%0+%2], %1;" ::"r"(a), "r"(v), "n"(OFF) : "memory");
+}
+
+// ---- TMA bulk copy global -> shared with mbarrier completion (no multicast) ---------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// src and dst 16-byte aligned, bytes a non-zero multiple of 16
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Waits for the given phase of an mbarrier, giving up after `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit)
+{
+    for (uint32_t it = 0; it < limit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// Memory policy of the window routines (df11_common.h) for the kernels: every table probe is
+// one ld.shared, every staged exponent one st.shared.u8 with an immediate offset.
+struct SmemPolicy {
+    uint32_t dec_addr, cnt_addr, stage_addr, luts_addr;
+    __device__ __forceinline__ uint32_t cnt(uint32_t i) const { return lds32(cnt_addr + i * 4u); }
+    __device__ __forceinline__ Df11Entry dec(uint32_t i) const
+    {
+        const uint2 v = lds64(dec_addr + i * 8u);
+        Df11Entry e;
+        e.meta = v.x;
+        e.syms = v.y;
+        return e;
+    }
+    __device__ __forceinline__ uint32_t lut(uint32_t i) const { return lds8(luts_addr + i); }
+    template <int OFF>
+    __device__ __forceinline__ void put(uint32_t slot, uint32_t v) const
+    {
+        sts8<OFF>(stage_addr + slot, v);
+    }
+};
+
+// Window words read straight from global memory, for blocks at the end of the stream (bytes
+// past the end read as 0) and for streams that are not 16-byte aligned.
+__device__ __noinline__ uint3 load_window_slow(const uint8_t *codes, int64_t n_bytes, int64_t off)
+{
+    uint32_t w[3] = {0, 0, 0};
 #pragma unroll
-        for (int k = 0; k < 12; ++k) {
-            const int64_t i = off + k;
-            const uint32_t byte = i < p.n_bytes ? (uint32_t)__ldg(p.codes + i) : 0u;
-            w[k >> 2] |= byte << (24 - 8 * (k & 3));
-        }
-        w0 = w[0], w1 = w[1], w2 = w[2];
+    for (int k = 0; k < 12; ++k) {
+        const int64_t i = off + k;
+        const uint32_t byte = i < n_bytes ? (uint32_t)__ldg(codes + i) : 0u;
+        w[k >> 2] |= byte << (24 - 8 * (k & 3));
+    }
+    return make_uint3(w[0], w[1], w[2]);
+}
+
+// 5-bit gap of window `w` of a block from the block's 320 gap bytes (decode.cu:85-87); the
+// second byte is read only when the field straddles a byte boundary.
+template <class F>
+__device__ __forceinline__ uint32_t block_gap(F byte_at, uint32_t w)
+{
+    const uint32_t bit = 5u * w, j = bit >> 3, r = bit & 7u;
+    const uint32_t hi = byte_at(j);
+    const uint32_t lo = byte_at(r > 3u ? j + 1u : j);
+    return (((hi << 8) | lo) >> (11u - r)) & 31u;
+}
+
+__device__ __forceinline__ void build_tables_smem(const Params &p, uint8_t *luts_s, uint8_t *agree, Df11Entry *dec,
+                                                  uint32_t *cnt, int K, uint32_t tid)
+{
+    for (int task = tid; task < 255; task += kThreads) {
+        int u = 1;
+        while (task >= df11_agree_offset(u + 1) && u < 8) ++u;
+        agree[task] = df11_agree_flag(luts_s, u, task - df11_agree_offset(u));
+    }
+    __syncthreads();
+    for (int v = tid; v < (1 << K); v += kThreads) {
+        Df11Entry e;
+        uint32_t c;
+        df11_build_entry(luts_s, p.n_luts, agree, (uint32_t)v, K, &e, &c);
+        if (dec) dec[v] = e;
+        if (cnt) cnt[v] = c;
     }
 }
 
-__device__ __forceinline__ uint16_t merge_one(uint32_t e, uint32_t m)
+// Block-wide exclusive scan of one value per thread; returns the exclusive prefix.
+__device__ __forceinline__ uint32_t block_scan(uint32_t v, uint32_t *wsum, uint32_t lane, uint32_t warp)
 {
-    return (uint16_t)(((m & 0x80u) << 8) | (e << 7) | (m & 0x7Fu));
+    uint32_t incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    uint32_t ws = lane < kWarps ? wsum[lane] : 0u;
+#pragma unroll
+    for (int d = 1; d < kWarps; d <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xffffffffu, ws, d);
+        if (lane >= d) ws += n;
+    }
+    const uint32_t before = __shfl_sync(0xffffffffu, ws, warp > 0 ? warp - 1 : 0);
+    return (warp > 0 ? before : 0u) + incl - v;
 }
 
-template <int K, int MODE>
-__global__ void __launch_bounds__(kThreads, 4) df11_kernel(const Params p)
+// ---------------------------------------------------------------------------------------
+// Seek-point kernel (once per unit, behind df11_prepare).  One window per thread: count the
+// window's codes, scan the counts inside the format block, then walk the window again knowing
+// the output index of its first code and record the bit position of every code whose index
+// is a multiple of EPT.
+// ---------------------------------------------------------------------------------------
+template <int K>
+__global__ void __launch_bounds__(kThreads, 3) df11_sync_kernel(const Params p)
 {
     extern __shared__ __align__(16) uint8_t smem[];
-    Df11Entry *table = reinterpret_cast<Df11Entry *>(smem);
-    uint8_t *luts_s = smem + (sizeof(Df11Entry) << K);
+    const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
+    uint8_t *luts_s = smem + (4u << K);
     uint8_t *agree = luts_s + p.n_luts * 256;
     uint32_t *wsum = reinterpret_cast<uint32_t *>(agree + 256);
-    uint8_t *stage = reinterpret_cast<uint8_t *>(wsum + 32);
+    SmemPolicy mem;
+    mem.dec_addr = 0;
+    mem.cnt_addr = smem_addr;
+    mem.stage_addr = 0;
+    mem.luts_addr = smem_addr + (4u << K);
 
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     int bad = 0;
-
-    // ---- once per CTA: tables into shared memory -------------------------------------
     for (int i = tid; i < p.n_luts * 256; i += kThreads) luts_s[i] = __ldg(p.luts + i);
     __syncthreads();
-    if (p.table_g != nullptr) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(p.table_g);
-        uint4 *dst = reinterpret_cast<uint4 *>(table);
-        for (int i = tid; i < (1 << K) / 2; i += kThreads) dst[i] = __ldg(src + i);
-    } else {
-        for (int task = tid; task < 255; task += kThreads) {
-            int u = 1;
-            while (task >= df11_agree_offset(u + 1) && u < 8) ++u;
-            agree[task] = df11_agree_flag(luts_s, u, task - df11_agree_offset(u));
+    build_tables_smem(p, luts_s, agree, nullptr, reinterpret_cast<uint32_t *>(smem), K, tid);
+    __syncthreads();
+
+    const uint32_t ept = (uint32_t)p.ept;
+    const uint64_t n_groups = ((uint64_t)p.n_elements + ept - 1) / ept;
+    for (int64_t b = blockIdx.x; b < p.n_blocks; b += gridDim.x) {
+        const int64_t off = b * DF11_BLOCK_BYTES + (int64_t)tid * DF11_WINDOW_BYTES;
+        const uint8_t *g = p.gaps + b * DF11_GAP_BYTES_PER_BLOCK;
+        const uint32_t gap = block_gap([&](uint32_t j) { return (uint32_t)__ldg(g + j); }, tid);
+        const bool live = off < p.n_bytes;
+        uint3 w = make_uint3(0, 0, 0);
+        uint32_t cnt = 0;
+        int tbad = 0;
+        if (live) {
+            if ((p.codes_aligned & 1) && off + 12 <= p.n_bytes) {
+                const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p.codes + off));
+                const uint32_t x = __ldg(reinterpret_cast<const uint32_t *>(p.codes + off + 8));
+                w = make_uint3(__byte_perm(v.x, 0, 0x0123), __byte_perm(v.y, 0, 0x0123), __byte_perm(x, 0, 0x0123));
+            } else {
+                w = load_window_slow(p.codes, p.n_bytes, off);
+            }
         }
-        __syncthreads();
-        for (int v = tid; v < (1 << K); v += kThreads)
-            table[v] = df11_build_entry(luts_s, p.n_luts, agree, (uint32_t)v, K);
+        cnt = df11_count_window<K>(mem, p.n_luts, w.x, w.y, w.z, live ? gap : 64u, &tbad);
+        const uint32_t o = block_scan(cnt, wsum, lane, warp);
+        if (live) {
+            const uint64_t first = (uint64_t)__ldg(p.pos + b) + o;
+            const uint64_t window_bit = (uint64_t)off * 8u;
+            df11_mark_window<K>(
+                mem, p.n_luts, w.x, w.y, w.z, gap, first, ept,
+                [&](uint64_t group, uint32_t bit_in_window) {
+                    if (group >= n_groups) return;  // padding decoded past the last element
+                    const uint64_t bit = window_bit + bit_in_window;
+                    p.sync_lo[group] = (uint16_t)bit;
+                    if ((group & 31u) == 0) p.sync_hi[group >> 5] = (uint32_t)(bit >> 16);
+                },
+                &tbad);
+        }
+        if (tbad) bad |= DF11_STATUS_BAD_TABLE;
+        __syncthreads();  // wsum is reused by the next block
+    }
+    if (bad && p.status != nullptr) atomicOr(p.status, bad);
+}
+
+// ---------------------------------------------------------------------------------------
+// Fast decoder (behind df11_decode_prepared).  One group of EPT output elements per thread
+// and step; a warp handles 32 consecutive groups, i.e. one contiguous run of 32*EPT outputs.
+// Shared memory: the decode table, `luts` (for the rare full walk) and one private row per
+// thread through which the decoded exponents pass from the decode loop to the merge.
+// ---------------------------------------------------------------------------------------
+// Row of shared memory through which a thread's 16 decoded exponents pass from the probe
+// loop to the merge: four words in a 20-byte row, so that equal word slots of the 32 lanes
+// of a warp fall on 32 different banks.
+constexpr uint32_t kRowStride = 20;
+
+struct FastTables {
+    uint32_t dec_addr, luts_addr;
+    __device__ __forceinline__ uint32_t lut(uint32_t i) const { return lds8(luts_addr + i); }
+};
+
+// The probe loop of the fast decoder (the device form of df11_decode_group's inner loop,
+// df11_common.h, for 16 codes).  State: acc = pos | codes done << 8, q = pending exponents,
+// fa = address of the next row word.  One pass: take the 32 stream bits at `pos`, probe the
+// table, append up to four exponents to q, store q when a fourth exponent completes a word.
+// Leaves when 16 codes are done, when the position passes 63 (window exhausted) or when an
+// escape entry was met (its value sets bit 24); the caller looks at acc to tell which.
+template <int K>
+__device__ __forceinline__ void probe_loop(uint32_t &acc, uint32_t &q, uint32_t &fa, uint32_t w0, uint32_t w1,
+                                           uint32_t w2, uint32_t dec_addr)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pc, pl;\n\t"
+        ".reg .b32 t, a, b, x, i, m, s, sh, t2, lo, hi, nacc, c;\n\t"
+        "DF11_PROBE:\n\t"
+        "and.b32 t, %0, 32;\n\t"
+        "setp.ne.u32 p, t, 0;\n\t"
+        "selp.b32 a, %4, %3, p;\n\t"
+        "selp.b32 b, %5, %4, p;\n\t"
+        "shf.l.wrap.b32 x, b, a, %0;\n\t"
+        "shr.u32 i, x, %7;\n\t"
+        "mad.lo.u32 i, i, 8, %6;\n\t"
+        "ld.shared.v2.u32 {m, s}, [i];\n\t"
+        "shr.u32 sh, %0, 5;\n\t"
+        "and.b32 sh, sh, 24;\n\t"
+        "shl.b32 t2, s, sh;\n\t"
+        "or.b32 lo, %1, t2;\n\t"
+        "shf.l.wrap.b32 hi, s, 0, sh;\n\t"
+        "add.u32 nacc, %0, m;\n\t"
+        "xor.b32 c, nacc, %0;\n\t"
+        "and.b32 c, c, 0xFC00;\n\t"
+        "setp.ne.u32 pc, c, 0;\n\t"
+        "@pc st.shared.u32 [%2], lo;\n\t"
+        "@pc add.u32 %2, %2, 4;\n\t"
+        "selp.b32 %1, hi, lo, pc;\n\t"
+        "mov.u32 %0, nacc;\n\t"
+        "and.b32 t, nacc, 0xFFFFF040;\n\t"
+        "setp.eq.u32 pl, t, 0;\n\t"
+        "@pl bra DF11_PROBE;\n\t"
+        "}"
+        : "+r"(acc), "+r"(q), "+r"(fa)
+        : "r"(w0), "r"(w1), "r"(w2), "r"(dec_addr), "n"(32 - K)
+        : "memory");
+}
+
+// ---------------------------------------------------------------------------------------
+// Fast decoder (behind df11_decode_prepared).  A warp handles 32 consecutive groups, i.e. one
+// contiguous run of 32*EPT outputs; a thread decodes its group 16 codes at a time.
+// Shared memory: the decode table, `luts` (for the rare full walk) and one private row per
+// thread.
+// ---------------------------------------------------------------------------------------
+template <int K, int EPT>
+__global__ void __launch_bounds__(kFastThreads) df11_fast_kernel(const Params p)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
+    constexpr uint32_t rows_off = 8u << K;
+    constexpr uint32_t luts_off = rows_off + kFastThreads * kRowStride;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u;
+
+    {   // once per CTA: decode table (built by df11_prepare) and luts into shared memory
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.table_g);
+        uint4 *dst = reinterpret_cast<uint4 *>(smem);
+        for (int i = tid; i < (1 << K) / 2; i += kFastThreads) dst[i] = __ldg(src + i);
+        for (int i = tid; i < p.n_luts * 256; i += kFastThreads) smem[luts_off + i] = __ldg(p.luts + i);
     }
     __syncthreads();
 
-    // ---- format blocks -----------------------------------------------------------------
-    for (int64_t b = blockIdx.x; b < p.n_blocks; b += gridDim.x) {
-        const int64_t t = b * DF11_WINDOWS_PER_BLOCK + tid;  // my window
-        const bool live = t * DF11_WINDOW_BYTES < p.n_bytes;
+    FastTables tab;
+    tab.dec_addr = smem_addr;
+    tab.luts_addr = smem_addr + luts_off;
+    const uint32_t row_addr = smem_addr + rows_off + tid * kRowStride;
+    const uint32_t *codes32 = reinterpret_cast<const uint32_t *>(p.codes);
+    // words that can be loaded whole; 0 sends every word of an unaligned stream the slow way
+    const uint32_t n_words = (p.codes_aligned & 4) ? (uint32_t)(p.n_bytes >> 2) : 0u;
+    const bool vec = p.sm_aligned && p.out_aligned;  // 16-byte loads and stores allowed
+    int bad = 0;
 
-        int64_t base = 0;
-        int block_cnt = 0, phase = 0;
-        if (MODE != kCount) {
-            base = (int64_t)p.pos[b];
-            const int64_t next = (int64_t)p.pos[b + 1];
-            int64_t c = next - base;
-            if (c < 0 || next > p.n_elements) {
-                bad |= DF11_STATUS_BAD_POSITIONS;
-                c = c < 0 ? 0 : p.n_elements - base;
-                if (c < 0) c = 0;
+    // stream bytes [4i, 4i+4) as a big-endian word, 0 past the end
+    auto word = [&](uint32_t i) -> uint32_t {
+        if (i < n_words) return __byte_perm(__ldg(codes32 + i), 0, 0x0123);
+        uint32_t v = 0;
+        const int64_t off = (int64_t)i * 4;
+        for (int k = 0; k < 4; ++k)
+            if (off + k < p.n_bytes) v |= (uint32_t)__ldg(p.codes + off + k) << (24 - 8 * k);
+        return v;
+    };
+
+    const uint32_t n_chunks = (uint32_t)p.n_chunks;
+    const uint32_t n_elements = (uint32_t)p.n_elements;  // the host side rejects units too close to 2^32
+    const uint32_t warps = gridDim.x * (kFastThreads / 32);
+    for (uint32_t chunk = blockIdx.x * (kFastThreads / 32) + (tid >> 5); chunk < n_chunks; chunk += warps) {
+        const uint32_t group = chunk * 32u + lane;
+        uint32_t first = group * EPT;  // my next output element
+        // seek point: 16 low bits per group, the high part once per 32 groups
+        uint32_t lo = first < n_elements ? (uint32_t)__ldg(p.sync_lo + group) : 0u;
+        const uint32_t hi = __ldg(p.sync_hi + chunk);
+        const uint32_t lo0 = __shfl_sync(0xffffffffu, lo, 0);
+        if (lo < lo0) lo += 65536u;
+        uint32_t wi = (hi << 11) + (lo >> 5);  // stream word and bit inside it where my next code starts
+        uint32_t bit = lo & 31u;
+
+        uint32_t acc = 0, q = 0;  // acc = pos | codes done << 8; q = pending exponents
+#pragma unroll
+        for (int part = 0; part < EPT / 16; ++part, first += 16u) {
+            if (first >= n_elements) break;
+            const bool whole = n_elements - first >= 16u;
+            uint4 m = make_uint4(0, 0, 0, 0);
+            if (whole && vec) m = __ldg(reinterpret_cast<const uint4 *>(p.sm + first));
+
+            // 96-bit window whose position 0 is my next code.  A later part continues where the
+            // previous one stopped: codes it decoded beyond its sixteenth are already in q.
+            uint32_t w0, w1, w2;
+            {
+                const uint32_t at = bit + (acc & 0x7Fu);
+                wi += at >> 5;
+                bit = at & 31u;
+                acc = part ? (acc & ~0xFFu) - (16u << 8) : 0u;
+                const uint32_t a = word(wi), b = word(wi + 1u), c = word(wi + 2u), d = word(wi + 3u);
+                w0 = __funnelshift_l(b, a, bit);
+                w1 = __funnelshift_l(c, b, bit);
+                w2 = __funnelshift_l(d, c, bit);
             }
-            phase = (int)(base & 7);
-            if (c + phase > p.stage_cap) {
-                bad |= DF11_STATUS_TRUNCATED;
-                c = p.stage_cap - phase;
+            uint32_t fa = row_addr;
+            for (;;) {
+                if ((acc & 0xFFFFF040u) == 0u) probe_loop<K>(acc, q, fa, w0, w1, w2, tab.dec_addr);
+                if ((acc & DF11_DEC_ESCAPE) == 0u && (acc & 0x1F00u) >= (16u << 8)) break;  // 16 codes done
+                if (acc & DF11_DEC_ESCAPE) {
+                    // the table could not resolve this code from K bits: full walk for one symbol
+                    acc -= DF11_DEC_ESCAPE;
+                    uint32_t len;
+                    int tbad = 0;
+                    const uint32_t sym = df11_walk_m(tab, p.n_luts, df11_peek(w0, w1, w2, acc), &len, &tbad);
+                    if (tbad) bad |= DF11_STATUS_BAD_TABLE;
+                    const uint32_t sh = (acc >> 5) & 24u;
+                    const uint32_t word_now = q | (sym << sh);
+                    const uint32_t nacc = acc + (len | 256u);
+                    if ((nacc ^ acc) & 0xFC00u) {
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(fa), "r"(word_now) : "memory");
+                        fa += 4u;
+                        q = 0;
+                    } else {
+                        q = word_now;
+                    }
+                    acc = nacc;
+                    if ((acc & 0x1F00u) >= (16u << 8)) break;
+                }
+                if (acc & 64u) {
+                    // position 64..127: slide the window to the code the position has reached
+                    const uint32_t at = bit + (acc & 0x7Fu);
+                    wi += at >> 5;
+                    bit = at & 31u;
+                    const uint32_t a = word(wi), b = word(wi + 1u), c = word(wi + 2u), d = word(wi + 3u);
+                    w0 = __funnelshift_l(b, a, bit);
+                    w1 = __funnelshift_l(c, b, bit);
+                    w2 = __funnelshift_l(d, c, bit);
+                    acc &= ~0xFFu;
+                }
             }
-            block_cnt = (int)c;
+
+            if (whole && vec) {
+                uint32_t e0 = lds32(row_addr), e1 = lds32(row_addr + 4), e2 = lds32(row_addr + 8),
+                         e3 = lds32(row_addr + 12);
+                uint4 r0, r1;
+                df11_merge4(e0, m.x, &r0.x, &r0.y);
+                df11_merge4(e1, m.y, &r0.z, &r0.w);
+                df11_merge4(e2, m.z, &r1.x, &r1.y);
+                df11_merge4(e3, m.w, &r1.z, &r1.w);
+                uint4 *dst = reinterpret_cast<uint4 *>(p.out + first);
+                dst[0] = r0;
+                dst[1] = r1;
+            } else {  // the last, partial piece of the unit, or unaligned tensors
+                for (uint32_t k = 0; k < 16u && first + k < n_elements; ++k)
+                    p.out[first + k] = df11_merge1(lds8(row_addr + k), __ldg(p.sm + first + k));
+            }
         }
+    }
+    if (bad && p.status != nullptr) atomicOr(p.status, bad);
+}
 
-        uint32_t w0 = 0, w1 = 0, w2 = 0, gap = 0;
-        if (live) {
-            load_window(p, t, w0, w1, w2);
-            gap = df11_gap(p.gaps, p.n_gap_bytes, t);
+// ---------------------------------------------------------------------------------------
+// Self-contained decode kernel (behind df11_decode): count pass + scan + decode pass per block.
+//
+// Shared memory (byte offsets from the dynamic shared base):
+//   [0, 8<<K)               decode table
+//   [.., +4<<K)             count table
+//   2 input buffers         each: 4112 stream bytes, then the block's 320 gap bytes
+//   stage                   exponent bytes of the current block
+//   tile                    sign/mantissa bytes of the current block
+//   3 mbarriers, luts, agree, wsum
+// ---------------------------------------------------------------------------------------
+template <int K>
+struct Layout {
+    static constexpr uint32_t dec = 0;
+    static constexpr uint32_t cnt = 8u << K;
+    static constexpr uint32_t in0 = cnt + (4u << K);
+    static constexpr uint32_t stage = in0 + 2u * kInBufBytes;
+};
+
+template <int K>
+__global__ void __launch_bounds__(kThreads, 3) df11_decode_kernel(const Params p)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    using L = Layout<K>;
+    const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t tile_off = L::stage + p.stage_bytes;
+    const uint32_t bars_off = tile_off + p.stage_bytes;
+    uint8_t *luts_s = smem + bars_off + 32;
+    uint8_t *agree = luts_s + p.n_luts * 256;
+    uint32_t *wsum = reinterpret_cast<uint32_t *>(agree + 256);
+
+    SmemPolicy mem;
+    mem.dec_addr = smem_addr + L::dec;
+    mem.cnt_addr = smem_addr + L::cnt;
+    mem.stage_addr = smem_addr + L::stage;
+    mem.luts_addr = smem_addr + bars_off + 32;
+    const uint32_t tile_addr = smem_addr + tile_off;
+    const uint32_t bar_in = smem_addr + bars_off;       // two barriers, 8 bytes apart
+    const uint32_t bar_sm = smem_addr + bars_off + 16;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    int bad = 0;
+
+    // ---- once per CTA --------------------------------------------------------------------
+    if (tid == 0) {
+        mbar_init(bar_in, 1);
+        mbar_init(bar_in + 8, 1);
+        mbar_init(bar_sm, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < p.n_luts * 256; i += kThreads) luts_s[i] = __ldg(p.luts + i);
+    __syncthreads();
+    build_tables_smem(p, luts_s, agree, reinterpret_cast<Df11Entry *>(smem + L::dec),
+                      reinterpret_cast<uint32_t *>(smem + L::cnt), K, tid);
+    __syncthreads();
+
+    // A block's stream bytes come by bulk copy when all 4112 of them exist and are aligned.
+    auto streamed = [&](int64_t b) {
+        return (p.codes_aligned & 1) && (b + 1) * (int64_t)DF11_BLOCK_BYTES + 16 <= p.n_bytes;
+    };
+    // Producer (thread 0): bulk copies of block b's inputs into input buffer `buf`.
+    const bool side_streamed = (p.codes_aligned & 2) != 0;  // gap bytes by bulk copy when aligned
+    auto issue_inputs = [&](int64_t b, uint32_t buf) {
+        const uint32_t dst = smem_addr + L::in0 + buf * kInBufBytes;
+        const uint32_t bar = bar_in + 8 * buf;
+        const bool with_codes = streamed(b);
+        const uint32_t total = (with_codes ? kCodesBufBytes : 0) + (side_streamed ? DF11_GAP_BYTES_PER_BLOCK : 0);
+        if (total == 0) {
+            mbar_arrive(bar);
+            return;
         }
+        mbar_expect_tx(bar, total);
+        if (with_codes) bulk_g2s(dst, p.codes + b * DF11_BLOCK_BYTES, kCodesBufBytes, bar);
+        if (side_streamed)
+            bulk_g2s(dst + kCodesBufBytes, p.gaps + b * DF11_GAP_BYTES_PER_BLOCK, DF11_GAP_BYTES_PER_BLOCK, bar);
+    };
 
-        int o = 0, end = 0;
-        if (MODE == kPrepared) {
-            if (live) {
-                o = (int)p.woff[t];
-                const bool last = tid == DF11_WINDOWS_PER_BLOCK - 1 ||
-                                  (t + 1) * DF11_WINDOW_BYTES >= p.n_bytes;
-                end = last ? block_cnt : (int)p.woff[t + 1];
+    if (tid == 0 && (int64_t)blockIdx.x < p.n_blocks) issue_inputs(blockIdx.x, 0);
+
+    uint32_t it = 0;
+    for (int64_t b = blockIdx.x; b < p.n_blocks; b += gridDim.x, ++it) {
+        const uint32_t cur = it & 1u;
+        const uint32_t in_addr = smem_addr + L::in0 + cur * kInBufBytes;
+
+        // next block's inputs start flowing into the other buffer (all its readers passed
+        // the barrier that ended the previous iteration)
+        if (tid == 0 && b + gridDim.x < p.n_blocks) issue_inputs(b + gridDim.x, cur ^ 1u);
+
+        // after one wait has run out, later ones give up quickly: the launch is lost anyway
+        if (!mbar_wait(bar_in + 8 * cur, (it >> 1) & 1u, (bad & DF11_STATUS_TIMEOUT) ? 8u : kWaitLimit))
+            bad |= DF11_STATUS_TIMEOUT;
+
+        // ---- block bookkeeping (uniform) ---------------------------------------------------
+        const int64_t base = (int64_t)__ldg(p.pos + b);
+        const int64_t next = (int64_t)__ldg(p.pos + b + 1);
+        int64_t c = next - base;
+        if (c < 0 || next > p.n_elements) {
+            bad |= DF11_STATUS_BAD_POSITIONS;
+            c = c < 0 ? 0 : p.n_elements - base;
+            if (c < 0) c = 0;
+        }
+        const uint32_t phase = (uint32_t)(base & 15);
+        if (c + phase > p.stage_bytes - 16) {
+            bad |= DF11_STATUS_TRUNCATED;
+            c = p.stage_bytes - 16 - phase;
+        }
+        const uint32_t block_cnt = (uint32_t)c;
+        const uint32_t last = phase + block_cnt;  // one past the last staging byte in use
+        const int64_t gbase = base - phase;       // multiple of 16
+        const uint8_t *sm_blk = p.sm + gbase;
+
+        // ---- sign/mantissa tile of this block: bulk copy, overlapped with the decode --------
+        // Whole 16-byte pieces that lie inside the tensor come by TMA; a ragged end (only at
+        // the very end of the unit) or an unaligned tensor is fetched with plain loads.
+        uint32_t tma_bytes = 0;
+        if (p.sm_aligned && block_cnt > 0) {  // then base < n_elements, so `avail` is not negative
+            const int64_t avail = (p.n_elements - gbase) & ~(int64_t)15;
+            const uint32_t want = (last + 15u) & ~15u;
+            tma_bytes = (int64_t)want <= avail ? want : (uint32_t)avail;
+        }
+        if (tid == 0) {
+            if (tma_bytes) {
+                mbar_expect_tx(bar_sm, tma_bytes);
+                bulk_g2s(tile_addr, sm_blk, tma_bytes, bar_sm);
+            } else {
+                mbar_arrive(bar_sm);
             }
+        }
+        for (uint32_t i = max(tma_bytes, phase) + tid; i < last; i += kThreads)
+            smem[tile_off + i] = __ldg(sm_blk + i);
+
+        // ---- my window ------------------------------------------------------------------------
+        uint32_t w0 = 0, w1 = 0, w2 = 0;
+        bool live = true;
+        if (streamed(b)) {
+            const uint2 v = lds64(in_addr + 8u * tid);
+            w0 = __byte_perm(v.x, 0, 0x0123);
+            w1 = __byte_perm(v.y, 0, 0x0123);
+            w2 = __byte_perm(lds32(in_addr + 8u * tid + 8u), 0, 0x0123);
         } else {
-            int tbad = 0;
-            const uint32_t cnt =
-                live ? df11_count_window<K>(table, luts_s, p.n_luts, w0, w1, w2, gap, &tbad) : 0u;
-            if (tbad) bad |= DF11_STATUS_BAD_TABLE;
-            // block-wide exclusive scan: shuffles inside a warp, one hop through shared memory
-            uint32_t incl = cnt;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const uint32_t n = __shfl_up_sync(0xffffffffu, incl, d);
-                if (lane >= d) incl += n;
-            }
-            if (lane == 31) wsum[warp] = incl;
-            __syncthreads();
-            uint32_t ws = lane < kWarps ? wsum[lane] : 0u;
-#pragma unroll
-            for (int d = 1; d < kWarps; d <<= 1) {
-                const uint32_t n = __shfl_up_sync(0xffffffffu, ws, d);
-                if (lane >= d) ws += n;
-            }
-            const uint32_t before = __shfl_sync(0xffffffffu, ws, warp > 0 ? warp - 1 : 0);
-            o = (int)((warp > 0 ? before : 0u) + incl - cnt);
-            end = o + (int)cnt;
-            if (MODE == kCount) {
-                if (live) p.woff[t] = (uint16_t)(o > 65535 ? 65535 : o);
-                __syncthreads();  // wsum is reused by the next block
-                continue;
+            const int64_t off = b * DF11_BLOCK_BYTES + (int64_t)tid * DF11_WINDOW_BYTES;
+            live = off < p.n_bytes;
+            if (live) {
+                const uint3 v = load_window_slow(p.codes, p.n_bytes, off);
+                w0 = v.x, w1 = v.y, w2 = v.z;
             }
         }
+
+        uint32_t gap;
+        if (side_streamed) {
+            gap = block_gap([&](uint32_t j) { return lds8(in_addr + kCodesBufBytes + j); }, tid);
+        } else {
+            const uint8_t *g = p.gaps + b * DF11_GAP_BYTES_PER_BLOCK;
+            gap = block_gap([&](uint32_t j) { return (uint32_t)__ldg(g + j); }, tid);
+        }
+        int cbad = 0;
+        const uint32_t cnt = df11_count_window<K>(mem, p.n_luts, w0, w1, w2, live ? gap : 64u, &cbad);
+        if (cbad) bad |= DF11_STATUS_BAD_TABLE;
+        uint32_t o = block_scan(cnt, wsum, lane, warp);
+        uint32_t end = o + cnt;
 
         // clamp to what this block may write, then shift by the block's alignment phase
-        o = o < block_cnt ? o : block_cnt;
-        end = end < block_cnt ? end : block_cnt;
+        o = min(o, block_cnt) + phase;
+        end = min(end, block_cnt) + phase;
         {
             int tbad = 0;
-            df11_decode_window<K>(table, luts_s, p.n_luts, w0, w1, w2, gap, stage, o + phase,
-                                  end + phase, &tbad);
+            df11_decode_window<K>(mem, p.n_luts, w0, w1, w2, gap, o, end, &tbad);
             if (tbad) bad |= DF11_STATUS_BAD_TABLE;
         }
         __syncthreads();
+        if (!mbar_wait(bar_sm, it & 1u, (bad & DF11_STATUS_TIMEOUT) ? 8u : kWaitLimit)) bad |= DF11_STATUS_TIMEOUT;
 
-        // ---- merge with sign/mantissa, eight elements per thread step ------------------
-        const int64_t gbase = base - phase;  // multiple of 8
-        const int n_groups = (phase + block_cnt + 7) >> 3;
-        for (int g = tid; g < n_groups; g += kThreads) {
-            const int64_t G = gbase + 8 * (int64_t)g;
-            const int lo = g == 0 ? phase : 0;
-            const int hi = min(phase + block_cnt - 8 * g, 8);
-            if (lo == 0 && hi == 8 && p.io_aligned) {
-                const uint2 ex = *reinterpret_cast<const uint2 *>(stage + 8 * g);
-                const uint2 m = __ldg(reinterpret_cast<const uint2 *>(p.sm + G));
+        // ---- merge with sign/mantissa ------------------------------------------------------------
+        // Groups of eight elements aligned to eight in the output: group g covers staging and tile
+        // bytes [8g, 8g+8).  Complete groups: two 8-byte shared loads, one 16-byte global store.
+        uint16_t *out_blk = p.out + gbase;
+        if (p.out_aligned) {
+            const uint32_t g_lo = (phase + 7u) >> 3, g_hi = last >> 3;
+            for (uint32_t g = g_lo + tid; g < g_hi; g += kThreads) {
+                const uint2 ex = lds64(mem.stage_addr + 8u * g);
+                const uint2 m = lds64(tile_addr + 8u * g);
                 uint4 r;
-                r.x = df11_merge_pair(__byte_perm(m.x, ex.x, 0x5140));
-                r.y = df11_merge_pair(__byte_perm(m.x, ex.x, 0x7362));
-                r.z = df11_merge_pair(__byte_perm(m.y, ex.y, 0x5140));
-                r.w = df11_merge_pair(__byte_perm(m.y, ex.y, 0x7362));
-                *reinterpret_cast<uint4 *>(p.out + G) = r;
-            } else {
-                for (int k = lo; k < hi; ++k)
-                    p.out[G + k] = merge_one(stage[8 * g + k], __ldg(p.sm + G + k));
+                df11_merge4(ex.x, m.x, &r.x, &r.y);
+                df11_merge4(ex.y, m.y, &r.z, &r.w);
+                reinterpret_cast<uint4 *>(out_blk)[g] = r;
             }
+            // elements of the (at most two) incomplete groups at either end, one per thread
+            if (tid < 16u) {
+                const uint32_t i = tid < 8u ? 8u * (g_lo - 1u) + tid : 8u * g_hi + (tid - 8u);
+                const bool mine = tid < 8u ? ((phase & 7u) != 0u && i >= phase && i < last)
+                                           : (g_hi >= g_lo && i < last);
+                if (mine) out_blk[i] = df11_merge1(lds8(mem.stage_addr + i), lds8(tile_addr + i));
+            }
+        } else {
+            for (uint32_t i = phase + tid; i < last; i += kThreads)
+                out_blk[i] = df11_merge1(lds8(mem.stage_addr + i), lds8(tile_addr + i));
         }
-        __syncthreads();  // staging and wsum are reused by the next block
+        __syncthreads();  // staging, tile, wsum and this input buffer are reused
     }
 
     if (bad && p.status != nullptr) atomicOr(p.status, bad);
@@ -233,7 +695,7 @@ struct DeviceInfo {
 };
 std::mutex g_mutex;
 DeviceInfo g_devices[64];
-bool g_attr_set[64][3] = {};
+bool g_attr_set[64][4] = {};
 
 struct DeviceGuard {
     int prev = -1;
@@ -265,45 +727,58 @@ int device_info(int device, DeviceInfo *out)
     return DF11_OK;
 }
 
-size_t smem_bytes(int n_luts, int stage_bytes)
-{
-    return (sizeof(Df11Entry) << kTableBits) + (size_t)n_luts * 256 + 256 + 32 * 4 + (size_t)stage_bytes;
-}
-
-template <int MODE>
-int launch(Params p, int stage_bytes, int device, cudaStream_t stream)
+template <class Kernel>
+int launch(Kernel kernel, int threads, int slot, size_t smem, int64_t work_items, const Params &p, int device,
+           cudaStream_t stream)
 {
     DeviceInfo info;
     int rc = device_info(device, &info);
     if (rc != DF11_OK) return rc;
     DeviceGuard guard(device);
     if (!guard.ok) return df11_fail(DF11_ERR_CUDA, "cudaSetDevice(%d) failed", device);
-
-    const size_t smem = smem_bytes(p.n_luts, stage_bytes);
     if (smem > (size_t)info.max_smem_optin)
         return df11_fail(DF11_ERR_BADARG, "needs %zu bytes of shared memory, device allows %d", smem,
                          info.max_smem_optin);
-    auto kernel = df11_kernel<kTableBits, MODE>;
     {
         std::lock_guard<std::mutex> lock(g_mutex);
-        if (!g_attr_set[device][MODE]) {
+        if (!g_attr_set[device][slot]) {
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  info.max_smem_optin);
             if (e != cudaSuccess)
                 return df11_fail(DF11_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-            g_attr_set[device][MODE] = true;
+            g_attr_set[device][slot] = true;
         }
     }
     int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
     if (e != cudaSuccess || per_sm < 1)
         return df11_fail(DF11_ERR_CUDA, "occupancy query failed (%s, %d CTAs/SM)", cudaGetErrorString(e), per_sm);
     int64_t grid = (int64_t)info.sm_count * per_sm;
-    if (grid > p.n_blocks) grid = p.n_blocks;
-    kernel<<<(unsigned)grid, kThreads, smem, stream>>>(p);
+    if (grid > work_items) grid = work_items;
+    if (grid < 1) grid = 1;
+    kernel<<<(unsigned)grid, threads, smem, stream>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     return DF11_OK;
+}
+
+size_t small_tables_bytes(int n_luts) { return (size_t)n_luts * 256 + 256 + 32 * 4; }
+
+int launch_decode(const Params &p, int device, cudaStream_t stream)
+{
+    const size_t smem = Layout<kTableBits>::stage + 2 * (size_t)p.stage_bytes + 32 + small_tables_bytes(p.n_luts);
+    return launch(df11_decode_kernel<kTableBits>, kThreads, 0, smem, p.n_blocks, p, device, stream);
+}
+
+// Elements per seek point of the prepared form: 16 unless DF11_EPT=32 is set in the environment
+// (half the auxiliary memory, longer dependent chains per thread).  Read once per process.
+int elements_per_seek_point()
+{
+    static const int ept = [] {
+        const char *e = getenv("DF11_EPT");
+        return (e && atoi(e) == 32) ? 32 : 16;
+    }();
+    return ept;
 }
 
 int check_common(const void *luts, const void *codes, const void *pos, const void *gaps, int32_t n_luts,
@@ -319,13 +794,13 @@ int check_common(const void *luts, const void *codes, const void *pos, const voi
     return DF11_OK;
 }
 
-int stage_bytes_for(int32_t max_block_elems, int *cap)
+// Shared staging: alignment phase (<= 15) + elements of the widest block, rounded up to whole
+// 16-byte pieces, plus the 16 bytes the kernel keeps as a margin.
+int stage_bytes_for(int32_t max_block_elems)
 {
     int64_t m = max_block_elems > 0 ? max_block_elems : DF11_MAX_BLOCK_ELEMS;
     if (m > DF11_MAX_BLOCK_ELEMS) m = DF11_MAX_BLOCK_ELEMS;
-    const int bytes = (int)((m + 7 + 15) / 16 * 16) + 16;  // phase (<= 7) + elements, padded
-    *cap = bytes - 8;
-    return bytes;
+    return (int)((m + 15 + 15) / 16 * 16) + 16;
 }
 
 constexpr int64_t kAuxTableBytes = (int64_t)sizeof(Df11Entry) << kTableBits;
@@ -342,8 +817,31 @@ __global__ void df11_table_kernel(const uint8_t *luts, int n_luts, Df11Entry *ta
         agree[task] = df11_agree_flag(luts_s, u, task - df11_agree_offset(u));
     }
     __syncthreads();
-    for (int v = threadIdx.x; v < (1 << kTableBits); v += blockDim.x)
-        table[v] = df11_build_entry(luts_s, n_luts, agree, (uint32_t)v, kTableBits);
+    for (int v = threadIdx.x; v < (1 << kTableBits); v += blockDim.x) {
+        Df11Entry e;
+        uint32_t c;
+        df11_build_entry(luts_s, n_luts, agree, (uint32_t)v, kTableBits, &e, &c);
+        table[v] = e;
+    }
+}
+
+Params base_params(const void *luts, const void *codes, const void *pos, const void *gaps, int32_t n_luts,
+                   int64_t n_bytes, int64_t n_elements, void *status)
+{
+    Params p = {};
+    p.luts = (const uint8_t *)luts;
+    p.codes = (const uint8_t *)codes;
+    p.pos = (const uint32_t *)pos;
+    p.gaps = (const uint8_t *)gaps;
+    p.status = (int *)status;
+    p.n_bytes = n_bytes;
+    p.n_elements = n_elements;
+    p.n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
+    p.n_luts = n_luts;
+    p.stage_bytes = 16;
+    p.codes_aligned = (((uintptr_t)codes & 15) == 0 ? 1 : 0) | (((uintptr_t)gaps & 15) == 0 ? 2 : 0) |
+                      (((uintptr_t)codes & 3) == 0 ? 4 : 0);
+    return p;
 }
 
 }  // namespace
@@ -357,31 +855,38 @@ extern "C" int df11_decode(const void *luts, const void *codes, const void *sign
     if (rc != DF11_OK) return rc;
     if (n_bytes == 0 || n_elements == 0) return DF11_OK;
     if (!sign_mantissa || !out_bf16) return df11_fail(DF11_ERR_BADARG, "null tensor pointer");
-    Params p = {};
-    p.luts = (const uint8_t *)luts;
-    p.codes = (const uint8_t *)codes;
+    Params p = base_params(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements, status);
     p.sm = (const uint8_t *)sign_mantissa;
-    p.pos = (const uint32_t *)output_positions;
-    p.gaps = (const uint8_t *)gaps;
     p.out = (uint16_t *)out_bf16;
-    p.status = (int *)status;
-    p.n_bytes = n_bytes;
-    p.n_elements = n_elements;
-    p.n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
-    p.n_gap_bytes = p.n_blocks * DF11_GAP_BYTES_PER_BLOCK;
-    p.n_luts = n_luts;
-    const int stage_bytes = stage_bytes_for(max_block_elems, &p.stage_cap);
-    p.codes_aligned = ((uintptr_t)codes & 7) == 0;
-    p.io_aligned = ((uintptr_t)sign_mantissa & 7) == 0 && ((uintptr_t)out_bf16 & 15) == 0;
-    return launch<kTwoPass>(p, stage_bytes, device, (cudaStream_t)stream);
+    p.stage_bytes = stage_bytes_for(max_block_elems);
+    p.sm_aligned = ((uintptr_t)sign_mantissa & 15) == 0;
+    p.out_aligned = ((uintptr_t)out_bf16 & 15) == 0;
+    return launch_decode(p, device, (cudaStream_t)stream);
 }
 
-extern "C" int64_t df11_aux_bytes(int64_t n_bytes)
+namespace {
+// Auxiliary buffer: decode table | seek points, high parts (uint32 per 32 groups, padded to 16
+// bytes) | seek points, low parts (uint16 per group, 32 per chunk).
+constexpr int64_t kMaxPreparedElements = 0xFFFFFFFFll - 32 * 32;  // group arithmetic is 32-bit
+struct AuxLayout {
+    int64_t n_chunks, hi_off, lo_off, total;
+};
+AuxLayout aux_layout(int64_t n_elements, int ept)
 {
-    if (n_bytes < 0) return df11_fail(DF11_ERR_BADARG, "negative size");
-    const int64_t n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
-    // table, then one uint16 per window (+1 so that woff[t + 1] is always readable), padded
-    return kAuxTableBytes + ((n_blocks * DF11_WINDOWS_PER_BLOCK + 1) * 2 + 15) / 16 * 16;
+    AuxLayout a;
+    const int64_t n_groups = (n_elements + ept - 1) / ept;
+    a.n_chunks = (n_groups + 31) / 32;
+    a.hi_off = kAuxTableBytes;
+    a.lo_off = a.hi_off + (a.n_chunks * 4 + 15) / 16 * 16;
+    a.total = a.lo_off + a.n_chunks * 64;
+    return a;
+}
+}  // namespace
+
+extern "C" int64_t df11_aux_bytes(int64_t n_bytes, int64_t n_elements)
+{
+    if (n_bytes < 0 || n_elements < 0) return df11_fail(DF11_ERR_BADARG, "negative size");
+    return aux_layout(n_elements, elements_per_seek_point()).total;
 }
 
 extern "C" int df11_prepare(const void *luts, const void *codes, const void *output_positions,
@@ -391,9 +896,14 @@ extern "C" int df11_prepare(const void *luts, const void *codes, const void *out
     int rc = check_common(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements);
     if (rc != DF11_OK) return rc;
     if (!aux || ((uintptr_t)aux & 15)) return df11_fail(DF11_ERR_BADARG, "aux buffer is null or not 16-byte aligned");
-    if (aux_bytes < df11_aux_bytes(n_bytes))
+    if (n_elements > kMaxPreparedElements)
+        return df11_fail(DF11_ERR_BADARG, "the prepared form handles up to %lld elements per unit; use df11_decode",
+                         (long long)kMaxPreparedElements);
+    const int ept = elements_per_seek_point();
+    const AuxLayout a = aux_layout(n_elements, ept);
+    if (aux_bytes < a.total)
         return df11_fail(DF11_ERR_NOSPACE, "aux buffer holds %lld bytes, %lld needed", (long long)aux_bytes,
-                         (long long)df11_aux_bytes(n_bytes));
+                         (long long)a.total);
     {
         DeviceGuard guard(device);
         if (!guard.ok) return df11_fail(DF11_ERR_CUDA, "cudaSetDevice(%d) failed", device);
@@ -401,23 +911,14 @@ extern "C" int df11_prepare(const void *luts, const void *codes, const void *out
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     }
-    if (n_bytes == 0) return DF11_OK;
-    Params p = {};
-    p.luts = (const uint8_t *)luts;
-    p.codes = (const uint8_t *)codes;
-    p.pos = (const uint32_t *)output_positions;
-    p.gaps = (const uint8_t *)gaps;
-    p.table_g = (const Df11Entry *)aux;  // written by the launch above, same stream
-    p.woff = (uint16_t *)((uint8_t *)aux + kAuxTableBytes);
-    p.status = (int *)status;
-    p.n_bytes = n_bytes;
-    p.n_elements = n_elements;
-    p.n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
-    p.n_gap_bytes = p.n_blocks * DF11_GAP_BYTES_PER_BLOCK;
-    p.n_luts = n_luts;
-    p.stage_cap = 0;
-    p.codes_aligned = ((uintptr_t)codes & 7) == 0;
-    return launch<kCount>(p, 16, device, (cudaStream_t)stream);
+    if (n_bytes == 0 || n_elements == 0) return DF11_OK;
+    Params p = base_params(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements, status);
+    p.sync_hi = (uint32_t *)((uint8_t *)aux + a.hi_off);
+    p.sync_lo = (uint16_t *)((uint8_t *)aux + a.lo_off);
+    p.n_chunks = a.n_chunks;
+    p.ept = ept;
+    const size_t smem = (4u << kTableBits) + small_tables_bytes(n_luts);
+    return launch(df11_sync_kernel<kTableBits>, kThreads, 1, smem, p.n_blocks, p, device, (cudaStream_t)stream);
 }
 
 extern "C" int df11_decode_prepared(const void *luts, const void *codes, const void *sign_mantissa,
@@ -425,28 +926,33 @@ extern "C" int df11_decode_prepared(const void *luts, const void *codes, const v
                                     void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
                                     int32_t max_block_elems, void *status, int32_t device, void *stream)
 {
+    (void)max_block_elems;  // sizes the shared staging of df11_decode only
     int rc = check_common(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements);
     if (rc != DF11_OK) return rc;
     if (n_bytes == 0 || n_elements == 0) return DF11_OK;
     if (!sign_mantissa || !out_bf16 || !aux || ((uintptr_t)aux & 15))
         return df11_fail(DF11_ERR_BADARG, "null tensor pointer or misaligned aux buffer");
-    Params p = {};
-    p.luts = (const uint8_t *)luts;
-    p.codes = (const uint8_t *)codes;
+    if (n_elements > kMaxPreparedElements)
+        return df11_fail(DF11_ERR_BADARG, "the prepared form handles up to %lld elements per unit; use df11_decode",
+                         (long long)kMaxPreparedElements);
+    const int ept = elements_per_seek_point();
+    const AuxLayout a = aux_layout(n_elements, ept);
+    Params p = base_params(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements, status);
     p.sm = (const uint8_t *)sign_mantissa;
-    p.pos = (const uint32_t *)output_positions;
-    p.gaps = (const uint8_t *)gaps;
     p.out = (uint16_t *)out_bf16;
     p.table_g = (const Df11Entry *)aux;
-    p.woff = (uint16_t *)((uint8_t *)aux + kAuxTableBytes);
-    p.status = (int *)status;
-    p.n_bytes = n_bytes;
-    p.n_elements = n_elements;
-    p.n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
-    p.n_gap_bytes = p.n_blocks * DF11_GAP_BYTES_PER_BLOCK;
-    p.n_luts = n_luts;
-    const int stage_bytes = stage_bytes_for(max_block_elems, &p.stage_cap);
-    p.codes_aligned = ((uintptr_t)codes & 7) == 0;
-    p.io_aligned = ((uintptr_t)sign_mantissa & 7) == 0 && ((uintptr_t)out_bf16 & 15) == 0;
-    return launch<kPrepared>(p, stage_bytes, device, (cudaStream_t)stream);
+    p.sync_hi = (uint32_t *)((uint8_t *)aux + a.hi_off);
+    p.sync_lo = (uint16_t *)((uint8_t *)aux + a.lo_off);
+    p.n_chunks = a.n_chunks;
+    p.ept = ept;
+    p.sm_aligned = ((uintptr_t)sign_mantissa & 15) == 0;
+    p.out_aligned = ((uintptr_t)out_bf16 & 15) == 0;
+    // work per CTA pass: one chunk (32 groups) per warp
+    const int64_t cta_items = (a.n_chunks + kFastThreads / 32 - 1) / (kFastThreads / 32);
+    if (ept == 32) {
+        const size_t smem = (8u << kTableBits) + kFastThreads * kRowStride + (size_t)n_luts * 256;
+        return launch(df11_fast_kernel<kTableBits, 32>, kFastThreads, 3, smem, cta_items, p, device, (cudaStream_t)stream);
+    }
+    const size_t smem = (8u << kTableBits) + kFastThreads * kRowStride + (size_t)n_luts * 256;
+    return launch(df11_fast_kernel<kTableBits, 16>, kFastThreads, 2, smem, cta_items, p, device, (cudaStream_t)stream);
 }

@@ -59,8 +59,9 @@ def decode(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_mantissa: to
     return out
 
 
-def aux_bytes(n_bytes: int) -> int:
-    return _lib.check(_lib.lib.df11_aux_bytes(int(n_bytes)))
+def aux_bytes(n_bytes: int, n_elements: int) -> int:
+    """Size in bytes of the auxiliary buffer `prepare` fills for a unit of these sizes."""
+    return _lib.check(_lib.lib.df11_aux_bytes(int(n_bytes), int(n_elements)))
 
 
 def prepare(luts: torch.Tensor, encoded_exponent: torch.Tensor, output_positions: torch.Tensor,
@@ -69,7 +70,7 @@ def prepare(luts: torch.Tensor, encoded_exponent: torch.Tensor, output_positions
     """Fill (allocating if needed) the auxiliary buffer that ``decode_prepared`` reads."""
     device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, output_positions=output_positions,
                            gaps=gaps, aux=aux, status=status)
-    need = aux_bytes(encoded_exponent.numel())
+    need = aux_bytes(encoded_exponent.numel(), n_elements)
     if aux is None:
         aux = torch.empty(need, dtype=torch.uint8, device=device)
     _lib.check(_lib.lib.df11_prepare(

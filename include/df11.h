@@ -40,6 +40,7 @@ extern "C" {
 #define DF11_STATUS_BAD_TABLE 1    /* pointer outside `luts`, or a code length of 0 or > 32 */
 #define DF11_STATUS_BAD_POSITIONS 2 /* output_positions not monotone / beyond n_elements    */
 #define DF11_STATUS_TRUNCATED 4    /* a format block holds more elements than max_block_elems */
+#define DF11_STATUS_TIMEOUT 8      /* a bounded wait for an asynchronous copy ran out        */
 
 /* Library version, major*10000 + minor*100 + patch.  (The reference keeps a format
  * version string, dfloat11.py:44; this number versions the ABI below.) */
@@ -71,9 +72,9 @@ const char *df11_last_error(void);
  *   stream            a cudaStream_t (NULL = the legacy default stream)
  *
  * 64-bit sizes: units above 2^31 elements are fine (the reference's `int`
- * arguments, decode.cu:33, overflow there).  Fast paths need `codes` 8-byte aligned,
- * `sign_mantissa` 8-byte and `out_bf16` 16-byte aligned (any torch allocation is);
- * other alignments work but decode slower.
+ * arguments, decode.cu:33, overflow there).  The fast paths (TMA bulk copies, 16-byte
+ * stores) need `codes`, `gaps`, `sign_mantissa` and `out_bf16` 16-byte aligned (any torch
+ * allocation is); other alignments work but decode slower.
  */
 int df11_decode(const void *luts, const void *codes, const void *sign_mantissa,
                 const void *output_positions, const void *gaps, void *out_bf16,
@@ -84,16 +85,20 @@ int df11_decode(const void *luts, const void *codes, const void *sign_mantissa,
  * Optional two-step form for units that are decoded many times (every forward
  * pass, dfloat11.py:119-151).  df11_prepare() runs once per unit and device: it
  * fills a caller-owned auxiliary device buffer with (a) the multi-symbol decode
- * table derived from `luts` and (b) the output offset of every 8-byte window
- * inside its format block -- the result of the counting pass and block scan that
- * the reference kernel redoes on every launch (decode.cu:104-178).
- * df11_decode_prepared() then decodes in a single pass.  The DF11 tensors on disk
- * are unchanged; the auxiliary buffer is derived data and can be rebuilt at any time.
+ * table derived from `luts` and (b) a seek point -- the stream bit position -- for
+ * every group of 16 consecutive output elements, found by the counting pass and
+ * block scan that the reference kernel redoes on every launch (decode.cu:104-178).
+ * df11_decode_prepared() then lets every thread decode one group straight into its
+ * final place.  The DF11 tensors on disk are unchanged; the auxiliary buffer is
+ * derived data and can be rebuilt at any time.
  *
- * df11_aux_bytes(n_bytes) is the size of that buffer (about n_bytes/4 + 16 KiB).
- * The buffer must be 16-byte aligned.  It has no counterpart in the reference.
+ * df11_aux_bytes(n_bytes, n_elements) is the size of that buffer (about
+ * n_elements/8 + 16 KiB; half of that with DF11_EPT=32 in the environment, which
+ * places a seek point every 32 elements).  The buffer must be 16-byte aligned.
+ * `max_block_elems` is accepted for symmetry with df11_decode and ignored.  This
+ * form has no counterpart in the reference.
  */
-int64_t df11_aux_bytes(int64_t n_bytes);
+int64_t df11_aux_bytes(int64_t n_bytes, int64_t n_elements);
 
 int df11_prepare(const void *luts, const void *codes, const void *output_positions,
                  const void *gaps, void *aux, int64_t aux_bytes, int32_t n_luts,

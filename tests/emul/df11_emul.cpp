@@ -14,16 +14,32 @@
 
 namespace {
 
-uint32_t byte_perm(uint32_t x, uint32_t y, uint32_t sel)
-{
-    const uint64_t both = ((uint64_t)y << 32) | x;
-    uint32_t r = 0;
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t n = (sel >> (4 * i)) & 7u;
-        r |= (uint32_t)((both >> (8 * n)) & 0xFF) << (8 * i);
+// Memory policy of the window routines for plain host arrays.
+struct HostMem {
+    const uint32_t *cnt_t;
+    const Df11Entry *dec_t;
+    const uint8_t *luts;
+    uint8_t *stage;
+    uint32_t cnt(uint32_t i) const { return cnt_t[i]; }
+    Df11Entry dec(uint32_t i) const { return dec_t[i]; }
+    uint32_t lut(uint32_t i) const { return luts[i]; }
+    template <int OFF>
+    void put(uint32_t slot, uint32_t v) const { stage[slot + OFF] = (uint8_t)v; }
+    // seek-point decoder
+    const uint8_t *codes = nullptr;
+    int64_t n_bytes = 0;
+    uint32_t *row = nullptr;
+    uint32_t word(uint32_t i) const
+    {
+        uint32_t v = 0;
+        for (int k = 0; k < 4; ++k) {
+            const int64_t o = (int64_t)i * 4 + k;
+            if (o < n_bytes) v |= (uint32_t)codes[o] << (24 - 8 * k);
+        }
+        return v;
     }
-    return r;
-}
+    void flush(uint32_t k, uint32_t v) const { row[k] = v; }
+};
 
 void load_window(const uint8_t *codes, int64_t n_bytes, int64_t t, uint32_t w[3])
 {
@@ -36,43 +52,102 @@ void load_window(const uint8_t *codes, int64_t n_bytes, int64_t t, uint32_t w[3]
 }
 
 template <int K>
-int run(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, const uint8_t *sm,
-        int64_t n_elements, const uint32_t *pos, const uint8_t *gaps, uint16_t *out, int prepared,
-        int max_block_elems, int *status)
+void build_tables(const uint8_t *luts, int n_luts, std::vector<Df11Entry> &dec, std::vector<uint32_t> &cnt)
 {
-    const int64_t n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
-    const int64_t n_gap_bytes = n_blocks * DF11_GAP_BYTES_PER_BLOCK;
     uint8_t agree[256] = {0};
     for (int u = 1; u <= 8; ++u)
         for (int blk = 0; blk < (256 >> u); ++blk) agree[df11_agree_offset(u) + blk] = df11_agree_flag(luts, u, blk);
-    std::vector<Df11Entry> table(1 << K);
-    for (uint32_t v = 0; v < (1u << K); ++v) table[v] = df11_build_entry(luts, n_luts, agree, v, K);
+    dec.resize(1 << K);
+    cnt.resize(1 << K);
+    for (uint32_t v = 0; v < (1u << K); ++v) df11_build_entry(luts, n_luts, agree, v, K, &dec[v], &cnt[v]);
+}
 
-    int64_t m = max_block_elems > 0 ? max_block_elems : DF11_MAX_BLOCK_ELEMS;
-    const int stage_bytes = (int)((m + 7 + 15) / 16 * 16) + 16;
-    const int stage_cap = stage_bytes - 8;
-    std::vector<uint8_t> stage(stage_bytes);
+// The prepared form: seek points from the marking pass, then one group per "thread".
+template <int K, int EPT>
+int run_seek(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, const uint8_t *sm,
+             int64_t n_elements, const uint32_t *pos, const uint8_t *gaps, uint16_t *out, int *status)
+{
+    const int64_t n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
+    const int64_t n_gap_bytes = n_blocks * DF11_GAP_BYTES_PER_BLOCK;
+    std::vector<Df11Entry> dec;
+    std::vector<uint32_t> cnt;
+    build_tables<K>(luts, n_luts, dec, cnt);
+    HostMem mem{cnt.data(), dec.data(), luts, nullptr};
+    mem.codes = codes;
+    mem.n_bytes = n_bytes;
     int bad = 0;
 
-    std::vector<uint16_t> woff;
-    if (prepared) {  // the counting launch
-        woff.assign(n_blocks * DF11_WINDOWS_PER_BLOCK + 1, 0xFFFF);
-        for (int64_t b = 0; b < n_blocks; ++b) {
-            uint32_t run_sum = 0;
-            for (int tid = 0; tid < DF11_WINDOWS_PER_BLOCK; ++tid) {
-                const int64_t t = b * DF11_WINDOWS_PER_BLOCK + tid;
-                if (t * 8 >= n_bytes) break;
-                uint32_t w[3];
-                load_window(codes, n_bytes, t, w);
-                int tbad = 0;
-                const uint32_t cnt = df11_count_window<K>(table.data(), luts, n_luts, w[0], w[1], w[2],
-                                                          df11_gap(gaps, n_gap_bytes, t), &tbad);
-                if (tbad) bad |= DF11_STATUS_BAD_TABLE;
-                woff[t] = (uint16_t)(run_sum > 65535 ? 65535 : run_sum);
-                run_sum += cnt;
-            }
+    const uint64_t n_groups = ((uint64_t)n_elements + EPT - 1) / EPT;
+    const uint64_t n_chunks = (n_groups + 31) / 32;
+    std::vector<uint16_t> lo(n_chunks * 32, 0xDEAD);
+    std::vector<uint32_t> hi(n_chunks, 0xDEADBEEF);
+    for (int64_t b = 0; b < n_blocks; ++b) {
+        uint64_t index = pos[b];
+        for (int tid = 0; tid < DF11_WINDOWS_PER_BLOCK; ++tid) {
+            const int64_t t = b * DF11_WINDOWS_PER_BLOCK + tid;
+            if (t * 8 >= n_bytes) break;
+            uint32_t w[3];
+            load_window(codes, n_bytes, t, w);
+            const uint32_t gap = df11_gap(gaps, n_gap_bytes, t);
+            int tbad = 0;
+            const uint32_t c = df11_count_window<K>(mem, n_luts, w[0], w[1], w[2], gap, &tbad);
+            df11_mark_window<K>(
+                mem, n_luts, w[0], w[1], w[2], gap, index, EPT,
+                [&](uint64_t group, uint32_t bit_in_window) {
+                    if (group >= n_groups) return;
+                    const uint64_t bit = (uint64_t)t * 64 + bit_in_window;
+                    lo[group] = (uint16_t)bit;
+                    if ((group & 31) == 0) hi[group >> 5] = (uint32_t)(bit >> 16);
+                },
+                &tbad);
+            if (tbad) bad |= DF11_STATUS_BAD_TABLE;
+            index += c;
         }
     }
+    for (uint64_t group = 0; group < n_groups; ++group) {
+        const uint64_t chunk = group >> 5;
+        const uint32_t l = lo[group], l0 = lo[chunk * 32];
+        const uint64_t bitpos = ((uint64_t)hi[chunk] << 16) + l + (l < l0 ? 65536u : 0u);
+        uint32_t row[EPT / 4];
+        for (int k = 0; k < EPT / 4; ++k) row[k] = 0xEEEEEEEEu;
+        mem.row = row;
+        int tbad = 0;
+        df11_decode_group<K, EPT>(mem, n_luts, (uint32_t)(bitpos >> 5), (uint32_t)bitpos & 31u, true, &tbad);
+        if (tbad) bad |= DF11_STATUS_BAD_TABLE;
+        const int64_t first = (int64_t)group * EPT;
+        if (first + EPT <= n_elements) {
+            for (int k = 0; k < EPT / 4; ++k) {
+                uint32_t m4, r[2];
+                memcpy(&m4, sm + first + 4 * k, 4);
+                df11_merge4(row[k], m4, &r[0], &r[1]);
+                memcpy(out + first + 4 * k, r, 8);
+            }
+        } else {
+            const uint8_t *bytes = reinterpret_cast<const uint8_t *>(row);
+            for (int k = 0; k < EPT && first + k < n_elements; ++k) out[first + k] = df11_merge1(bytes[k], sm[first + k]);
+        }
+    }
+    if (status) *status = bad;
+    return 0;
+}
+
+template <int K>
+int run(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, const uint8_t *sm,
+        int64_t n_elements, const uint32_t *pos, const uint8_t *gaps, uint16_t *out, int max_block_elems,
+        int *status)
+{
+    const int64_t n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
+    const int64_t n_gap_bytes = n_blocks * DF11_GAP_BYTES_PER_BLOCK;
+    std::vector<Df11Entry> dec;
+    std::vector<uint32_t> cnt;
+    build_tables<K>(luts, n_luts, dec, cnt);
+
+    int64_t m = max_block_elems > 0 ? max_block_elems : DF11_MAX_BLOCK_ELEMS;
+    if (m > DF11_MAX_BLOCK_ELEMS) m = DF11_MAX_BLOCK_ELEMS;
+    const int stage_bytes = (int)((m + 15 + 15) / 16 * 16) + 16;
+    std::vector<uint8_t> stage(stage_bytes);
+    HostMem mem{cnt.data(), dec.data(), luts, stage.data()};
+    int bad = 0;
 
     for (int64_t b = 0; b < n_blocks; ++b) {
         int64_t base = pos[b];
@@ -83,12 +158,12 @@ int run(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, 
             c = c < 0 ? 0 : n_elements - base;
             if (c < 0) c = 0;
         }
-        const int phase = (int)(base & 7);
-        if (c + phase > stage_cap) {
+        const uint32_t phase = (uint32_t)(base & 15);
+        if (c + phase > stage_bytes - 16) {
             bad |= DF11_STATUS_TRUNCATED;
-            c = stage_cap - phase;
+            c = stage_bytes - 16 - phase;
         }
-        const int block_cnt = (int)c;
+        const uint32_t block_cnt = (uint32_t)c;
         memset(stage.data(), 0xEE, stage.size());  // poison: stale bytes must never reach the output
 
         uint32_t run_sum = 0;
@@ -97,47 +172,36 @@ int run(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, 
             if (t * 8 >= n_bytes) break;
             uint32_t w[3];
             load_window(codes, n_bytes, t, w);
-            const uint32_t gap = df11_gap(gaps, n_gap_bytes, t);
-            int o, end, tbad = 0;
-            if (prepared) {
-                o = woff[t];
-                const bool last = tid == DF11_WINDOWS_PER_BLOCK - 1 || (t + 1) * 8 >= n_bytes;
-                end = last ? block_cnt : (int)woff[t + 1];
-            } else {
-                const uint32_t cnt = df11_count_window<K>(table.data(), luts, n_luts, w[0], w[1], w[2], gap, &tbad);
-                o = (int)run_sum;
-                end = o + (int)cnt;
-                run_sum += cnt;
-            }
-            o = o < block_cnt ? o : block_cnt;
-            end = end < block_cnt ? end : block_cnt;
-            df11_decode_window<K>(table.data(), luts, n_luts, w[0], w[1], w[2], gap, stage.data(), o + phase,
-                                  end + phase, &tbad);
+            uint32_t gap, o, end;
+            int tbad = 0;
+            gap = df11_gap(gaps, n_gap_bytes, t);
+            const uint32_t n = df11_count_window<K>(mem, n_luts, w[0], w[1], w[2], gap, &tbad);
+            o = run_sum;
+            end = o + n;
+            run_sum += n;
+            o = (o < block_cnt ? o : block_cnt) + phase;
+            end = (end < block_cnt ? end : block_cnt) + phase;
+            df11_decode_window<K>(mem, n_luts, w[0], w[1], w[2], gap, o, end, &tbad);
             if (tbad) bad |= DF11_STATUS_BAD_TABLE;
         }
 
         const int64_t gbase = base - phase;
-        const int n_groups = (phase + block_cnt + 7) >> 3;
-        for (int g = 0; g < n_groups; ++g) {
-            const int64_t G = gbase + 8 * (int64_t)g;
-            const int lo = g == 0 ? phase : 0;
-            int hi = phase + block_cnt - 8 * g;
-            if (hi > 8) hi = 8;
-            if (lo == 0 && hi == 8) {
-                uint32_t ex[2], mm[2], r[4];
-                memcpy(ex, stage.data() + 8 * g, 8);
-                memcpy(mm, sm + G, 8);
-                r[0] = df11_merge_pair(byte_perm(mm[0], ex[0], 0x5140));
-                r[1] = df11_merge_pair(byte_perm(mm[0], ex[0], 0x7362));
-                r[2] = df11_merge_pair(byte_perm(mm[1], ex[1], 0x5140));
-                r[3] = df11_merge_pair(byte_perm(mm[1], ex[1], 0x7362));
-                memcpy(out + G, r, 16);
-            } else {
-                for (int k = lo; k < hi; ++k) {
-                    const uint32_t e = stage[8 * g + k], mv = sm[G + k];
-                    out[G + k] = (uint16_t)(((mv & 0x80u) << 8) | (e << 7) | (mv & 0x7Fu));
-                }
-            }
+        const uint8_t *sm_blk = sm + gbase;
+        uint16_t *out_blk = out + gbase;
+        const uint32_t last = phase + block_cnt;
+        const uint32_t g_lo = (phase + 7u) >> 3, g_hi = last >> 3;
+        for (uint32_t g = g_lo; g < g_hi; ++g) {
+            uint32_t ex[2], mm[2], r[4];
+            memcpy(ex, stage.data() + 8 * g, 8);
+            memcpy(mm, sm_blk + 8 * g, 8);
+            df11_merge4(ex[0], mm[0], &r[0], &r[1]);
+            df11_merge4(ex[1], mm[1], &r[2], &r[3]);
+            memcpy(out_blk + 8 * g, r, 16);
+        }
+        for (uint32_t tid = 0; tid < 16; ++tid) {
+            const uint32_t i = tid < 8u ? 8u * (g_lo - 1u) + tid : 8u * g_hi + (tid - 8u);
+            const bool mine = tid < 8u ? ((phase & 7u) != 0u && i >= phase && i < last) : (g_hi >= g_lo && i < last);
+            if (mine) out_blk[i] = df11_merge1(stage[i], sm_blk[i]);
         }
     }
     if (status) *status = bad;
@@ -146,32 +210,48 @@ int run(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, 
 
 }  // namespace
 
+// prepared: 0 = the self-contained two-pass flow, 16 / 32 = seek points every 16 / 32 elements
 extern "C" int df11_emul_decode(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes,
                                 const uint8_t *sm, int64_t n_elements, const uint32_t *pos,
                                 const uint8_t *gaps, uint16_t *out, int K, int prepared, int max_block_elems,
                                 int *status)
 {
+#define DF11_EMUL_CASE(KK)                                                                                          \
+    case KK:                                                                                                        \
+        if (prepared == 16) return run_seek<KK, 16>(luts, n_luts, codes, n_bytes, sm, n_elements, pos, gaps, out, status); \
+        if (prepared == 32) return run_seek<KK, 32>(luts, n_luts, codes, n_bytes, sm, n_elements, pos, gaps, out, status); \
+        return run<KK>(luts, n_luts, codes, n_bytes, sm, n_elements, pos, gaps, out, max_block_elems, status);
     switch (K) {
-    case 9: return run<9>(luts, n_luts, codes, n_bytes, sm, n_elements, pos, gaps, out, prepared, max_block_elems, status);
-    case 10: return run<10>(luts, n_luts, codes, n_bytes, sm, n_elements, pos, gaps, out, prepared, max_block_elems, status);
-    case 11: return run<11>(luts, n_luts, codes, n_bytes, sm, n_elements, pos, gaps, out, prepared, max_block_elems, status);
-    case 12: return run<12>(luts, n_luts, codes, n_bytes, sm, n_elements, pos, gaps, out, prepared, max_block_elems, status);
-    case 13: return run<13>(luts, n_luts, codes, n_bytes, sm, n_elements, pos, gaps, out, prepared, max_block_elems, status);
-    case 14: return run<14>(luts, n_luts, codes, n_bytes, sm, n_elements, pos, gaps, out, prepared, max_block_elems, status);
+        DF11_EMUL_CASE(9)
+        DF11_EMUL_CASE(10)
+        DF11_EMUL_CASE(11)
+        DF11_EMUL_CASE(12)
+        DF11_EMUL_CASE(13)
+        DF11_EMUL_CASE(14)
     }
+#undef DF11_EMUL_CASE
     return -1;
 }
 
-// Table statistics for a given K: fraction of escape entries and mean symbols per entry.
-extern "C" int df11_emul_table(const uint8_t *luts, int n_luts, int K, uint32_t *meta_out, uint32_t *syms_out)
+// The two tables for a given K (for statistics and direct inspection in tests).
+extern "C" int df11_emul_table(const uint8_t *luts, int n_luts, int K, uint32_t *meta_out, uint32_t *syms_out,
+                               uint32_t *cnt_out)
 {
-    uint8_t agree[256] = {0};
-    for (int u = 1; u <= 8; ++u)
-        for (int blk = 0; blk < (256 >> u); ++blk) agree[df11_agree_offset(u) + blk] = df11_agree_flag(luts, u, blk);
-    for (uint32_t v = 0; v < (1u << K); ++v) {
-        const Df11Entry e = df11_build_entry(luts, n_luts, agree, v, K);
-        meta_out[v] = e.meta;
-        syms_out[v] = e.syms;
+    std::vector<Df11Entry> dec;
+    std::vector<uint32_t> cnt;
+    switch (K) {
+    case 9: build_tables<9>(luts, n_luts, dec, cnt); break;
+    case 10: build_tables<10>(luts, n_luts, dec, cnt); break;
+    case 11: build_tables<11>(luts, n_luts, dec, cnt); break;
+    case 12: build_tables<12>(luts, n_luts, dec, cnt); break;
+    case 13: build_tables<13>(luts, n_luts, dec, cnt); break;
+    case 14: build_tables<14>(luts, n_luts, dec, cnt); break;
+    default: return -1;
+    }
+    for (size_t v = 0; v < dec.size(); ++v) {
+        meta_out[v] = dec[v].meta;
+        syms_out[v] = dec[v].syms;
+        cnt_out[v] = cnt[v];
     }
     return 0;
 }

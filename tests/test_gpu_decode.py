@@ -66,7 +66,7 @@ def test_golden_prepared(golden):
     d = _to_dev(golden)
     st = _status()
     aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], golden["w"].size, status=st)
-    assert aux.numel() == ops.aux_bytes(d["enc"].numel())
+    assert aux.numel() == ops.aux_bytes(d["enc"].numel(), golden["w"].size)
     for _ in range(2):   # the auxiliary buffer is reusable
         out = torch.full((golden["w"].size,), -1.0, dtype=torch.bfloat16, device=DEV)
         ops.decode_prepared(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], aux, out=out,
@@ -162,6 +162,14 @@ def test_misaligned_pointers_take_the_slow_paths(golden):
     out = out_buf[1:1 + golden["w"].size]          # 2-byte aligned only
     st = _status()
     ops.decode(d["luts"], enc, sm, d["pos"], d["gaps"], out=out, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert np.array_equal(_bits(out.contiguous()), golden["w"])
+    assert out_buf[0].item() == 0 and out_buf[1 + golden["w"].size].item() == 0
+    # the prepared form on the same misaligned tensors
+    out_buf.zero_()
+    aux = ops.prepare(d["luts"], enc, d["pos"], d["gaps"], golden["w"].size, status=st)
+    ops.decode_prepared(d["luts"], enc, sm, d["pos"], d["gaps"], aux, out=out, status=st)
     torch.cuda.synchronize()
     assert st.item() == 0
     assert np.array_equal(_bits(out.contiguous()), golden["w"])
