@@ -42,7 +42,17 @@ namespace {
 
 constexpr int kThreads = 512;  // one window per thread, one format block per CTA pass
 constexpr int kWarps = kThreads / 32;
-constexpr int kTableBits = 11;  // K: index width of the multi-symbol tables
+#ifndef DF11_TABLE_BITS
+#define DF11_TABLE_BITS 11
+#endif
+#ifndef DF11_FAST_TABLE_BITS
+#define DF11_FAST_TABLE_BITS 12
+#endif
+#ifndef DF11_FAST_MIN_CTAS
+#define DF11_FAST_MIN_CTAS 4
+#endif
+constexpr int kTableBits = DF11_TABLE_BITS;           // K of the self-contained decoder and the seek-point pass
+constexpr int kFastTableBits = DF11_FAST_TABLE_BITS;  // K of the fast decoder (its table is larger, its CTAs smaller)
 
 constexpr int kCodesBufBytes = DF11_BLOCK_BYTES + 16;      // block + look-ahead, multiple of 16
 constexpr int kInBufBytes = kCodesBufBytes + DF11_GAP_BYTES_PER_BLOCK;  // stream bytes, then gap bytes
@@ -285,80 +295,93 @@ __global__ void __launch_bounds__(kThreads, 3) df11_sync_kernel(const Params p)
     if (bad && p.status != nullptr) atomicOr(p.status, bad);
 }
 
-// ---------------------------------------------------------------------------------------
-// Fast decoder (behind df11_decode_prepared).  One group of EPT output elements per thread
-// and step; a warp handles 32 consecutive groups, i.e. one contiguous run of 32*EPT outputs.
-// Shared memory: the decode table, `luts` (for the rare full walk) and one private row per
-// thread through which the decoded exponents pass from the decode loop to the merge.
-// ---------------------------------------------------------------------------------------
-// Row of shared memory through which a thread's 16 decoded exponents pass from the probe
-// loop to the merge: four words in a 20-byte row, so that equal word slots of the 32 lanes
-// of a warp fall on 32 different banks.
-constexpr uint32_t kRowStride = 20;
-
 struct FastTables {
     uint32_t dec_addr, luts_addr;
     __device__ __forceinline__ uint32_t lut(uint32_t i) const { return lds8(luts_addr + i); }
 };
 
+// Sixteen exponents of a group, four per word, lowest byte first.  A completed word enters
+// at e3 and pushes the others down, so after four completions e0..e3 are in order.
+struct Exp16 {
+    uint32_t e0, e1, e2, e3;
+    __device__ __forceinline__ void push(uint32_t w)
+    {
+        e0 = e1, e1 = e2, e2 = e3, e3 = w;
+    }
+};
+
+// Fast-decoder form of a decode-table entry's first word: bits consumed in bits 0..7 (at most
+// 31), eight times the number of symbols in bits 16..23; an entry that needs the full walk is
+// kFastEscape alone.  The running state `acc` of a thread is the sum of the entries it used:
+//   bits 0..7   position in the window (64 and more: window used up)
+//   bits 16..23 8 * codes done (128: the sixteen codes of this pass are done)
+//   bit 28      an escape entry was met
+constexpr uint32_t kFastEscape = 1u << 28;
+constexpr uint32_t kFastDone = 128u << 16;
+constexpr uint32_t kFastLeave = kFastEscape | kFastDone | 64u;
+
+__host__ __device__ constexpr uint32_t fast_meta(uint32_t meta)
+{
+    return (meta == DF11_DEC_ESCAPE || (meta & 0xFFu) > 31u) ? kFastEscape
+                                                             : (meta & 0xFFu) | (((meta >> 8) & 7u) << 19);
+}
+
 // The probe loop of the fast decoder (the device form of df11_decode_group's inner loop,
-// df11_common.h, for 16 codes).  State: acc = pos | codes done << 8, q = pending exponents,
-// fa = address of the next row word.  One pass: take the 32 stream bits at `pos`, probe the
-// table, append up to four exponents to q, store q when a fourth exponent completes a word.
-// Leaves when 16 codes are done, when the position passes 63 (window exhausted) or when an
-// escape entry was met (its value sets bit 24); the caller looks at acc to tell which.
+// df11_common.h, for 16 codes).  The 96-bit window w0:w1:w2 is kept shifted so that the next
+// code starts at its top bit.  One pass: index the table with the top K bits, append up to
+// four exponents to the pending word q, push q into E when a fourth exponent completes a
+// word, shift the window by the bits consumed.  Shift amounts are taken modulo 32 by the
+// funnel shifter, so `acc >> 16` (8 * codes done) and the entry word itself serve as such.
+// Table index and address are formed with multiply-add instructions to keep them off the
+// integer ALU pipe, which is the busiest unit of this kernel.
 template <int K>
-__device__ __forceinline__ void probe_loop(uint32_t &acc, uint32_t &q, uint32_t &fa, uint32_t w0, uint32_t w1,
-                                           uint32_t w2, uint32_t dec_addr)
+__device__ __forceinline__ void probe_loop(uint32_t &acc, uint32_t &q, Exp16 &E, uint32_t &w0, uint32_t &w1,
+                                           uint32_t &w2, uint32_t dec_addr)
 {
     asm volatile(
         "{\n\t"
-        ".reg .pred p, pc, pl;\n\t"
-        ".reg .b32 t, a, b, x, i, m, s, sh, t2, lo, hi, nacc, c;\n\t"
+        ".reg .pred pc, pl;\n\t"
+        ".reg .b32 t, i, m, s, sh, t2, lo, hi, nacc, c;\n\t"
         "DF11_PROBE:\n\t"
-        "and.b32 t, %0, 32;\n\t"
-        "setp.ne.u32 p, t, 0;\n\t"
-        "selp.b32 a, %4, %3, p;\n\t"
-        "selp.b32 b, %5, %4, p;\n\t"
-        "shf.l.wrap.b32 x, b, a, %0;\n\t"
-        "shr.u32 i, x, %7;\n\t"
-        "mad.lo.u32 i, i, 8, %6;\n\t"
+        "mul.hi.u32 i, %6, %10;\n\t"             // top K bits of the window
+        "mad.lo.u32 i, i, 8, %9;\n\t"
         "ld.shared.v2.u32 {m, s}, [i];\n\t"
-        "shr.u32 sh, %0, 5;\n\t"
-        "and.b32 sh, sh, 24;\n\t"
-        "shl.b32 t2, s, sh;\n\t"
+        "shr.u32 sh, %0, 16;\n\t"
+        "shf.l.wrap.b32 t2, 0, s, sh;\n\t"       // s << (8 * codes done mod 32)
+        "shf.l.wrap.b32 hi, s, 0, sh;\n\t"       // the exponents that do not fit the word
         "or.b32 lo, %1, t2;\n\t"
-        "shf.l.wrap.b32 hi, s, 0, sh;\n\t"
+        "shf.l.wrap.b32 %6, %7, %6, m;\n\t"      // window <<= bits consumed
+        "shf.l.wrap.b32 %7, %8, %7, m;\n\t"
+        "shf.l.wrap.b32 %8, 0, %8, m;\n\t"
         "add.u32 nacc, %0, m;\n\t"
         "xor.b32 c, nacc, %0;\n\t"
-        "and.b32 c, c, 0xFC00;\n\t"
-        "setp.ne.u32 pc, c, 0;\n\t"
-        "@pc st.shared.u32 [%2], lo;\n\t"
-        "@pc add.u32 %2, %2, 4;\n\t"
+        "and.b32 c, c, 0x00E00000;\n\t"
+        "setp.ne.u32 pc, c, 0;\n\t"              // the count crossed a multiple of four
+        "@pc mov.b32 %2, %3;\n\t"
+        "@pc mov.b32 %3, %4;\n\t"
+        "@pc mov.b32 %4, %5;\n\t"
+        "@pc mov.b32 %5, lo;\n\t"
         "selp.b32 %1, hi, lo, pc;\n\t"
         "mov.u32 %0, nacc;\n\t"
-        "and.b32 t, nacc, 0xFFFFF040;\n\t"
+        "and.b32 t, nacc, %11;\n\t"
         "setp.eq.u32 pl, t, 0;\n\t"
         "@pl bra DF11_PROBE;\n\t"
         "}"
-        : "+r"(acc), "+r"(q), "+r"(fa)
-        : "r"(w0), "r"(w1), "r"(w2), "r"(dec_addr), "n"(32 - K)
-        : "memory");
+        : "+r"(acc), "+r"(q), "+r"(E.e0), "+r"(E.e1), "+r"(E.e2), "+r"(E.e3), "+r"(w0), "+r"(w1), "+r"(w2)
+        : "r"(dec_addr), "n"(1 << K), "n"(kFastLeave));
 }
 
 // ---------------------------------------------------------------------------------------
 // Fast decoder (behind df11_decode_prepared).  A warp handles 32 consecutive groups, i.e. one
 // contiguous run of 32*EPT outputs; a thread decodes its group 16 codes at a time.
-// Shared memory: the decode table, `luts` (for the rare full walk) and one private row per
-// thread.
+// Shared memory: the decode table and `luts` (for the rare full walk).
 // ---------------------------------------------------------------------------------------
 template <int K, int EPT>
-__global__ void __launch_bounds__(kFastThreads) df11_fast_kernel(const Params p)
+__global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_kernel(const Params p)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
-    constexpr uint32_t rows_off = 8u << K;
-    constexpr uint32_t luts_off = rows_off + kFastThreads * kRowStride;
+    constexpr uint32_t luts_off = 8u << K;
     const uint32_t tid = threadIdx.x, lane = tid & 31u;
 
     {   // once per CTA: decode table (built by df11_prepare) and luts into shared memory
@@ -372,111 +395,162 @@ __global__ void __launch_bounds__(kFastThreads) df11_fast_kernel(const Params p)
     FastTables tab;
     tab.dec_addr = smem_addr;
     tab.luts_addr = smem_addr + luts_off;
-    const uint32_t row_addr = smem_addr + rows_off + tid * kRowStride;
     const uint32_t *codes32 = reinterpret_cast<const uint32_t *>(p.codes);
     // words that can be loaded whole; 0 sends every word of an unaligned stream the slow way
     const uint32_t n_words = (p.codes_aligned & 4) ? (uint32_t)(p.n_bytes >> 2) : 0u;
     const bool vec = p.sm_aligned && p.out_aligned;  // 16-byte loads and stores allowed
     int bad = 0;
 
-    // stream bytes [4i, 4i+4) as a big-endian word, 0 past the end
-    auto word = [&](uint32_t i) -> uint32_t {
-        if (i < n_words) return __byte_perm(__ldg(codes32 + i), 0, 0x0123);
-        uint32_t v = 0;
-        const int64_t off = (int64_t)i * 4;
-        for (int k = 0; k < 4; ++k)
-            if (off + k < p.n_bytes) v |= (uint32_t)__ldg(p.codes + off + k) << (24 - 8 * k);
-        return v;
+    // Four raw stream words starting at word `wi` (bytes past the end read as 0), and the 96-bit
+    // window they give once byte-swapped and shifted left by `bit`.
+    auto load_words_slow = [&](uint32_t wi, uint4 &r) {  // end of the stream, or an unaligned stream
+        uint32_t v[4] = {0, 0, 0, 0};
+        const int64_t off = (int64_t)wi * 4;
+        for (int k = 0; k < 16; ++k)
+            if (off + k < p.n_bytes) v[k >> 2] |= (uint32_t)__ldg(p.codes + off + k) << (8 * (k & 3));
+        r = make_uint4(v[0], v[1], v[2], v[3]);
+    };
+    auto load_words = [&](uint32_t wi, uint4 &r) {
+        if (wi + 3u < n_words) {  // the common case: four whole words, one bounds check
+            const uint32_t *src = codes32 + wi;
+            r = make_uint4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3));
+        } else {
+            load_words_slow(wi, r);
+        }
+    };
+    auto make_window = [&](const uint4 &r, uint32_t bit, uint32_t &w0, uint32_t &w1, uint32_t &w2) {
+        const uint32_t a = __byte_perm(r.x, 0, 0x0123), b = __byte_perm(r.y, 0, 0x0123);
+        const uint32_t c = __byte_perm(r.z, 0, 0x0123), d = __byte_perm(r.w, 0, 0x0123);
+        w0 = __funnelshift_l(b, a, bit);
+        w1 = __funnelshift_l(c, b, bit);
+        w2 = __funnelshift_l(d, c, bit);
     };
 
     const uint32_t n_chunks = (uint32_t)p.n_chunks;
     const uint32_t n_elements = (uint32_t)p.n_elements;  // the host side rejects units too close to 2^32
     const uint32_t warps = gridDim.x * (kFastThreads / 32);
-    for (uint32_t chunk = blockIdx.x * (kFastThreads / 32) + (tid >> 5); chunk < n_chunks; chunk += warps) {
-        const uint32_t group = chunk * 32u + lane;
-        uint32_t first = group * EPT;  // my next output element
-        // seek point: 16 low bits per group, the high part once per 32 groups
-        uint32_t lo = first < n_elements ? (uint32_t)__ldg(p.sync_lo + group) : 0u;
-        const uint32_t hi = __ldg(p.sync_hi + chunk);
+
+    // What a task needs before it can run: where its first code starts, the stream words
+    // there and its first sixteen sign/mantissa bytes.  Loaded one task ahead.
+    struct Inputs {
+        uint32_t wi, bit;
+        uint4 words, sm;
+    };
+    // Stage 1 of the pipeline: the raw seek point of a chunk (16 low bits per group, the high
+    // part once per 32 groups).  Stage 2: stream word / bit of every lane, then the loads.
+    auto load_seek = [&](uint32_t chunk, uint32_t &lo, uint32_t &hi) {
+        lo = (uint32_t)__ldg(p.sync_lo + chunk * 32u + lane);  // padded to 32 per chunk: always readable
+        hi = __ldg(p.sync_hi + chunk);
+    };
+    auto issue_inputs = [&](uint32_t chunk, uint32_t lo, uint32_t hi, Inputs &in) {
         const uint32_t lo0 = __shfl_sync(0xffffffffu, lo, 0);
         if (lo < lo0) lo += 65536u;
-        uint32_t wi = (hi << 11) + (lo >> 5);  // stream word and bit inside it where my next code starts
-        uint32_t bit = lo & 31u;
+        in.wi = (hi << 11) + (lo >> 5);  // (hi << 16 | lo) >> 5
+        in.bit = lo & 31u;
+        const uint32_t first = (chunk * 32u + lane) * EPT;
+        if (first < n_elements) {
+            load_words(in.wi, in.words);
+            if (vec && n_elements - first >= 16u) in.sm = __ldg(reinterpret_cast<const uint4 *>(p.sm + first));
+        }
+    };
 
-        uint32_t acc = 0, q = 0;  // acc = pos | codes done << 8; q = pending exponents
+    uint32_t chunk = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
+    Inputs cur = {0, 0, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    uint32_t lo_next = 0, hi_next = 0;
+    if (chunk < n_chunks) {
+        uint32_t lo, hi;
+        load_seek(chunk, lo, hi);
+        issue_inputs(chunk, lo, hi, cur);
+        if (chunk + warps < n_chunks) load_seek(chunk + warps, lo_next, hi_next);
+    }
+    for (; chunk < n_chunks; chunk += warps) {
+        // keep the pipeline full: inputs of the next task, seek point of the one after it
+        Inputs nxt = {0, 0, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        if (chunk + warps < n_chunks) {
+            issue_inputs(chunk + warps, lo_next, hi_next, nxt);
+            if (chunk + 2u * warps < n_chunks) load_seek(chunk + 2u * warps, lo_next, hi_next);
+        }
+
+        uint32_t first = (chunk * 32u + lane) * EPT;  // my next output element
+        uint32_t wi = cur.wi, bit = cur.bit;
+        uint32_t acc = 0, q = 0;  // acc: see kFastEscape; q = pending exponents
 #pragma unroll
         for (int part = 0; part < EPT / 16; ++part, first += 16u) {
             if (first >= n_elements) break;
             const bool whole = n_elements - first >= 16u;
-            uint4 m = make_uint4(0, 0, 0, 0);
-            if (whole && vec) m = __ldg(reinterpret_cast<const uint4 *>(p.sm + first));
-
-            // 96-bit window whose position 0 is my next code.  A later part continues where the
+            uint4 m = cur.sm;
+            // 96-bit window whose top bit is my next code.  A later part continues where the
             // previous one stopped: codes it decoded beyond its sixteenth are already in q.
             uint32_t w0, w1, w2;
-            {
+            if (part == 0) {
+                make_window(cur.words, bit, w0, w1, w2);
+            } else {
+                if (whole && vec) m = __ldg(reinterpret_cast<const uint4 *>(p.sm + first));
                 const uint32_t at = bit + (acc & 0x7Fu);
                 wi += at >> 5;
                 bit = at & 31u;
-                acc = part ? (acc & ~0xFFu) - (16u << 8) : 0u;
-                const uint32_t a = word(wi), b = word(wi + 1u), c = word(wi + 2u), d = word(wi + 3u);
-                w0 = __funnelshift_l(b, a, bit);
-                w1 = __funnelshift_l(c, b, bit);
-                w2 = __funnelshift_l(d, c, bit);
+                acc = (acc & ~0xFFu) - kFastDone;
+                uint4 r;
+                load_words(wi, r);
+                make_window(r, bit, w0, w1, w2);
             }
-            uint32_t fa = row_addr;
+            Exp16 E = {0, 0, 0, 0};
             for (;;) {
-                if ((acc & 0xFFFFF040u) == 0u) probe_loop<K>(acc, q, fa, w0, w1, w2, tab.dec_addr);
-                if ((acc & DF11_DEC_ESCAPE) == 0u && (acc & 0x1F00u) >= (16u << 8)) break;  // 16 codes done
-                if (acc & DF11_DEC_ESCAPE) {
+                if ((acc & kFastLeave) == 0u) probe_loop<K>(acc, q, E, w0, w1, w2, tab.dec_addr);
+                if ((acc & (kFastEscape | 64u)) == 0u) break;  // 16 codes done, nothing special
+                if (acc & kFastEscape) {
                     // the table could not resolve this code from K bits: full walk for one symbol
-                    acc -= DF11_DEC_ESCAPE;
+                    acc -= kFastEscape;
                     uint32_t len;
                     int tbad = 0;
-                    const uint32_t sym = df11_walk_m(tab, p.n_luts, df11_peek(w0, w1, w2, acc), &len, &tbad);
+                    const uint32_t sym = df11_walk_m(tab, p.n_luts, w0, &len, &tbad);
                     if (tbad) bad |= DF11_STATUS_BAD_TABLE;
-                    const uint32_t sh = (acc >> 5) & 24u;
-                    const uint32_t word_now = q | (sym << sh);
-                    const uint32_t nacc = acc + (len | 256u);
-                    if ((nacc ^ acc) & 0xFC00u) {
-                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(fa), "r"(word_now) : "memory");
-                        fa += 4u;
+                    const uint32_t word_now = q | (sym << ((acc >> 16) & 24u));
+                    const uint32_t nacc = acc + (len | (8u << 16));
+                    if ((nacc ^ acc) & 0x00E00000u) {
+                        E.push(word_now);
                         q = 0;
                     } else {
                         q = word_now;
                     }
                     acc = nacc;
-                    if ((acc & 0x1F00u) >= (16u << 8)) break;
+                    if (len < 32u) {  // window <<= len
+                        w0 = __funnelshift_l(w1, w0, len);
+                        w1 = __funnelshift_l(w2, w1, len);
+                        w2 <<= len;
+                    } else {          // a 32-bit code, or an unusable table (len 64): the reload below follows
+                        w0 = w1, w1 = w2, w2 = 0;
+                    }
                 }
+                if (acc & kFastDone) break;  // 16 codes done (the position may be past 63)
                 if (acc & 64u) {
-                    // position 64..127: slide the window to the code the position has reached
+                    // position 64..127: reload the window at the code the position has reached
                     const uint32_t at = bit + (acc & 0x7Fu);
                     wi += at >> 5;
                     bit = at & 31u;
-                    const uint32_t a = word(wi), b = word(wi + 1u), c = word(wi + 2u), d = word(wi + 3u);
-                    w0 = __funnelshift_l(b, a, bit);
-                    w1 = __funnelshift_l(c, b, bit);
-                    w2 = __funnelshift_l(d, c, bit);
+                    uint4 r;
+                    load_words(wi, r);
+                    make_window(r, bit, w0, w1, w2);
                     acc &= ~0xFFu;
                 }
             }
 
             if (whole && vec) {
-                uint32_t e0 = lds32(row_addr), e1 = lds32(row_addr + 4), e2 = lds32(row_addr + 8),
-                         e3 = lds32(row_addr + 12);
                 uint4 r0, r1;
-                df11_merge4(e0, m.x, &r0.x, &r0.y);
-                df11_merge4(e1, m.y, &r0.z, &r0.w);
-                df11_merge4(e2, m.z, &r1.x, &r1.y);
-                df11_merge4(e3, m.w, &r1.z, &r1.w);
+                df11_merge4(E.e0, m.x, &r0.x, &r0.y);
+                df11_merge4(E.e1, m.y, &r0.z, &r0.w);
+                df11_merge4(E.e2, m.z, &r1.x, &r1.y);
+                df11_merge4(E.e3, m.w, &r1.z, &r1.w);
                 uint4 *dst = reinterpret_cast<uint4 *>(p.out + first);
                 dst[0] = r0;
                 dst[1] = r1;
             } else {  // the last, partial piece of the unit, or unaligned tensors
+                const uint32_t e[4] = {E.e0, E.e1, E.e2, E.e3};
                 for (uint32_t k = 0; k < 16u && first + k < n_elements; ++k)
-                    p.out[first + k] = df11_merge1(lds8(row_addr + k), __ldg(p.sm + first + k));
+                    p.out[first + k] = df11_merge1((e[k >> 2] >> (8u * (k & 3u))) & 255u, __ldg(p.sm + first + k));
             }
         }
+        cur = nxt;
     }
     if (bad && p.status != nullptr) atomicOr(p.status, bad);
 }
@@ -803,7 +877,7 @@ int stage_bytes_for(int32_t max_block_elems)
     return (int)((m + 15 + 15) / 16 * 16) + 16;
 }
 
-constexpr int64_t kAuxTableBytes = (int64_t)sizeof(Df11Entry) << kTableBits;
+constexpr int64_t kAuxTableBytes = (int64_t)sizeof(Df11Entry) << kFastTableBits;
 
 __global__ void df11_table_kernel(const uint8_t *luts, int n_luts, Df11Entry *table)
 {
@@ -817,10 +891,11 @@ __global__ void df11_table_kernel(const uint8_t *luts, int n_luts, Df11Entry *ta
         agree[task] = df11_agree_flag(luts_s, u, task - df11_agree_offset(u));
     }
     __syncthreads();
-    for (int v = threadIdx.x; v < (1 << kTableBits); v += blockDim.x) {
+    for (int v = threadIdx.x; v < (1 << kFastTableBits); v += blockDim.x) {
         Df11Entry e;
         uint32_t c;
-        df11_build_entry(luts_s, n_luts, agree, (uint32_t)v, kTableBits, &e, &c);
+        df11_build_entry(luts_s, n_luts, agree, (uint32_t)v, kFastTableBits, &e, &c);
+        e.meta = fast_meta(e.meta);  // the prepared form's table is read by df11_fast_kernel only
         table[v] = e;
     }
 }
@@ -950,9 +1025,9 @@ extern "C" int df11_decode_prepared(const void *luts, const void *codes, const v
     // work per CTA pass: one chunk (32 groups) per warp
     const int64_t cta_items = (a.n_chunks + kFastThreads / 32 - 1) / (kFastThreads / 32);
     if (ept == 32) {
-        const size_t smem = (8u << kTableBits) + kFastThreads * kRowStride + (size_t)n_luts * 256;
-        return launch(df11_fast_kernel<kTableBits, 32>, kFastThreads, 3, smem, cta_items, p, device, (cudaStream_t)stream);
+        const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
+        return launch(df11_fast_kernel<kFastTableBits, 32>, kFastThreads, 3, smem, cta_items, p, device, (cudaStream_t)stream);
     }
-    const size_t smem = (8u << kTableBits) + kFastThreads * kRowStride + (size_t)n_luts * 256;
-    return launch(df11_fast_kernel<kTableBits, 16>, kFastThreads, 2, smem, cta_items, p, device, (cudaStream_t)stream);
+    const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
+    return launch(df11_fast_kernel<kFastTableBits, 16>, kFastThreads, 2, smem, cta_items, p, device, (cudaStream_t)stream);
 }
