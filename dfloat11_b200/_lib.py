@@ -9,7 +9,7 @@ import ctypes
 import os
 from ctypes import c_char_p, c_int32, c_int64, c_uint32, c_void_p
 
-from .build import LIB_PATH
+from .build import LIB_PATH, _stale, build_lib
 
 DF11_OK = 0
 DF11_ERR_BADARG = -1
@@ -43,13 +43,23 @@ class DF11Error(RuntimeError):
 
 
 def _load() -> ctypes.CDLL:
-    if not os.path.exists(LIB_PATH):
-        raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m dfloat11_b200.build` "
-            "(needs nvcc; there is no non-CUDA fallback)")
+    # A library older than its sources is rebuilt first (needs nvcc); a missing one that
+    # cannot be built, or one that lacks a declared symbol, is an ImportError.
+    if _stale():
+        try:
+            build_lib(force=True)
+        except Exception as exc:  # noqa: BLE001
+            if not os.path.exists(LIB_PATH):
+                raise ImportError(
+                    f"{LIB_PATH} is missing and could not be built ({exc}); build it with "
+                    "`python dfloat11_b200/build.py` (needs nvcc; there is no non-CUDA fallback)") from exc
     lib = ctypes.CDLL(LIB_PATH)
     for name, (restype, argtypes) in SIGNATURES.items():
-        fn = getattr(lib, name)          # AttributeError if the library is stale
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise ImportError(f"{LIB_PATH} does not export {name}; rebuild it with "
+                              "`python dfloat11_b200/build.py --force`") from exc
         fn.restype = restype
         fn.argtypes = argtypes
     return lib

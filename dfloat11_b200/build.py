@@ -1,6 +1,6 @@
 """Builds ``libdf11.so`` (CUDA kernels + C ABI) in-tree with nvcc for sm_100a.
 
-    python -m dfloat11_b200.build [--force] [--verbose]
+    python dfloat11_b200/build.py [--force] [--verbose]
 
 nvcc cross-compiles without a GPU.  The library is written next to this file so
 that it travels with the source tree; nothing is installed into site-packages.
