@@ -1031,3 +1031,63 @@ extern "C" int df11_decode_prepared(const void *luts, const void *codes, const v
     const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
     return launch(df11_fast_kernel<kFastTableBits, 16>, kFastThreads, 2, smem, cta_items, p, device, (cudaStream_t)stream);
 }
+
+// ---------------------------------------------------------------------------------------
+// Decode without any allocation by anybody: the auxiliary buffer of the prepared form lives
+// in a fixed array inside the library image.
+// ---------------------------------------------------------------------------------------
+namespace {
+// Decode table, then the seek points of a unit of at most DF11_STATIC_MAX_ELEMENTS elements
+// (68 bytes per 512 elements).  About 4.3 MiB, held by every GPU that loads the library
+// until the process exits.
+constexpr int64_t kStaticAuxBytes =
+    kAuxTableBytes + 68 * ((int64_t)DF11_STATIC_MAX_ELEMENTS / 512 + 1) + 64;
+static __device__ __align__(256) uint8_t g_static_aux[kStaticAuxBytes];
+
+// Device address of g_static_aux on each device.  In host code the array's name is only a
+// handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress,
+// asked once per device with that device current.
+void *g_static_ptr[64] = {};
+
+int static_aux_address(int device, void **out)
+{
+    if (device < 0 || device >= 64) return df11_fail(DF11_ERR_BADARG, "device index %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_static_ptr[device] == nullptr) {
+        DeviceGuard guard(device);
+        if (!guard.ok) return df11_fail(DF11_ERR_CUDA, "cudaSetDevice(%d) failed", device);
+        void *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_aux);
+        if (e != cudaSuccess || ptr == nullptr)
+            return df11_fail(DF11_ERR_CUDA, "cudaGetSymbolAddress failed on device %d: %s", device,
+                             cudaGetErrorString(e));
+        g_static_ptr[device] = ptr;
+    }
+    *out = g_static_ptr[device];
+    return DF11_OK;
+}
+}  // namespace
+
+extern "C" int df11_decode_static(const void *luts, const void *codes, const void *sign_mantissa,
+                                  const void *output_positions, const void *gaps, void *out_bf16, int32_t n_luts,
+                                  int64_t n_bytes, int64_t n_elements, void *status, int32_t device, void *stream)
+{
+    if (n_elements > (int64_t)DF11_STATIC_MAX_ELEMENTS)
+        return df11_fail(DF11_ERR_NOSPACE,
+                         "df11_decode_static handles units of up to %lld elements, this one has %lld; "
+                         "use df11_prepare + df11_decode_prepared with a buffer of your own, or df11_decode",
+                         (long long)DF11_STATIC_MAX_ELEMENTS, (long long)n_elements);
+    if (n_elements >= 0 && n_bytes >= 0 && df11_aux_bytes(n_bytes, n_elements) > kStaticAuxBytes)
+        return df11_fail(DF11_ERR_NOSPACE, "the built-in buffer (%lld bytes) is too small for this unit",
+                         (long long)kStaticAuxBytes);
+    void *aux = nullptr;
+    int rc = static_aux_address(device, &aux);
+    if (rc != DF11_OK) return rc;
+    // Both steps go to the caller's stream, so the decode sees the seek points of THIS unit;
+    // every entry it reads is written by the step before it, nothing needs to start at zero.
+    rc = df11_prepare(luts, codes, output_positions, gaps, aux, kStaticAuxBytes, n_luts, n_bytes, n_elements, status,
+                      device, stream);
+    if (rc != DF11_OK) return rc;
+    return df11_decode_prepared(luts, codes, sign_mantissa, output_positions, gaps, aux, out_bf16, n_luts, n_bytes,
+                                n_elements, 0, status, device, stream);
+}

@@ -111,6 +111,31 @@ int df11_decode_prepared(const void *luts, const void *codes, const void *sign_m
                          int32_t max_block_elems, void *status, int32_t device, void *stream);
 
 /*
+ * Decode for callers that cannot allocate device memory at all and have nobody to do it
+ * for them: code running inside a CUDA-graph capture or a stream callback, a plug-in
+ * called from a serving loop whose memory pool is already carved up, a host runtime
+ * that forbids cudaMalloc after start-up.  df11_decode needs no extra memory but is the
+ * slower kernel; the fast kernel behind df11_decode_prepared needs an auxiliary buffer.
+ * Here that buffer is a fixed array inside the library (about 4.3 MiB of every GPU that
+ * loads libdf11, held until the process exits), so the call allocates nothing, and
+ * neither does anything it calls.  Same tensors and meaning as df11_decode; the
+ * auxiliary data is rebuilt on every call (two extra short launches on `stream`).
+ *
+ *   - Units of more than DF11_STATIC_MAX_ELEMENTS elements are refused with
+ *     DF11_ERR_NOSPACE (the message says what to use instead).
+ *   - The first call on each device looks up the array's device address; make that
+ *     call outside any stream capture.
+ *   - All calls on one device share the array: two calls whose kernels may overlap on
+ *     the GPU (different streams) corrupt each other.  Calls ordered on one stream are fine.
+ * This entry point has no counterpart in the reference.
+ */
+#define DF11_STATIC_MAX_ELEMENTS (1 << 25)
+int df11_decode_static(const void *luts, const void *codes, const void *sign_mantissa,
+                       const void *output_positions, const void *gaps, void *out_bf16,
+                       int32_t n_luts, int64_t n_bytes, int64_t n_elements, void *status,
+                       int32_t device, void *stream);
+
+/*
  * Host-side check of one unit before its first launch (all pointers HOST memory).
  * The reference performs no validation: a zero entry in the length row makes its
  * kernel spin forever (decode.cu:116-118).  Checks: table count, pointers stay
