@@ -1,0 +1,608 @@
+"""Host side of the decompression path: scratch buffers, the forward pre-hook, the loader,
+device placement and the public model API.
+
+This module mirrors the reference's ``dfloat11/dfloat11.py`` name for name -- ``TensorManager``
+(:52-100), ``get_hook`` / ``decode_hook`` (:103-176), ``load_and_replace_tensors`` (:179-308),
+``get_no_split_classes`` (:311-333), ``DFloat11Model.from_pretrained`` / ``from_single_file``
+(:336-493) and ``compress_model`` (:496-636) -- with the same arguments, module attributes and
+on-disk layout, so that code written against the reference keeps working.  What differs:
+
+* the kernel is launched through the C ABI of libdf11 on torch's current stream (the
+  reference goes through cupy's stream, dfloat11.py:142-151);
+* every unit gets, on first use on a device, the auxiliary buffer of the fast decoder
+  (``module.df11_aux``; set ``DF11_PREPARED=0`` to decode with no extra memory instead);
+* ``cpu_offload`` copies the next unit's compressed tensors host->device on a side stream,
+  into one of two reusable staging slots, while the current unit is being decoded and used
+  (the reference issues the copy on the compute stream inside the hook, dfloat11.py:123-128);
+* the loader resolves tensor names through dictionaries built once (the reference rebuilds
+  ``state_dict()`` per tensor, dfloat11.py:224-228) and validates every unit before it can
+  be launched;
+* device placement is done here (accelerate is not a dependency).
+"""
+from __future__ import annotations
+
+import json
+import logging
+import math
+import os
+import re
+from sys import stderr
+from typing import Dict, List, Optional, Union
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import codec, ops
+
+log = logging.getLogger("dfloat11")
+
+# Format constants (dfloat11.py:44-49); baked into every DF11 file's gaps / output_positions.
+version = "0.5.0"
+bytes_per_thread = 8
+threads_per_block = (512,)
+offloaded_tensor_names = ("encoded_exponent", "sign_mantissa")
+
+
+def _use_prepared() -> bool:
+    return os.environ.get("DF11_PREPARED", "1") != "0"
+
+
+class TensorManager:
+    """One BF16 scratch tensor per device, shared by every compressed unit (dfloat11.py:52-100).
+
+    A unit's decode overwrites what the previous unit left there; correctness rests on stream
+    order alone, as in the reference.
+    """
+
+    _tensors: Dict[torch.device, torch.Tensor] = {}
+
+    @staticmethod
+    def allocate_bfloat16(device, n_elements: int) -> torch.Tensor:
+        """A BF16 tensor of exactly ``n_elements`` on ``device``: a slice of the device's scratch,
+        which is replaced by a larger one when it is too small."""
+        device = torch.device(device)
+        if device.type == "cuda" and device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        existing = TensorManager._tensors.get(device)
+        if existing is not None:
+            if existing.numel() >= n_elements:
+                return existing[:n_elements]
+            del TensorManager._tensors[device]
+            del existing
+            if device.type == "cuda":
+                torch.cuda.empty_cache()
+        new_tensor = torch.empty(n_elements, dtype=torch.bfloat16, device=device)
+        log.info("Allocated %d bf16 on device %s", n_elements, device)
+        TensorManager._tensors[device] = new_tensor
+        return new_tensor
+
+    @staticmethod
+    def release(device=None) -> None:
+        """Drop the scratch of one device (or of all)."""
+        if device is None:
+            TensorManager._tensors.clear()
+        else:
+            TensorManager._tensors.pop(torch.device(device), None)
+
+
+class _OffloadStager:
+    """Per-device machinery of ``cpu_offload``: a copy stream and two staging slots.
+
+    Units are visited in a fixed cyclic order (``module.df11_next_offloaded``).  While unit i is
+    decoded, the pinned host tensors of unit i+1 are already on their way into the other slot
+    (``cudaMemcpyAsync`` on the copy stream).  A slot is handed back to the copy stream by an
+    event recorded on the compute stream after the decode that read it.
+    """
+
+    _by_device: Dict[torch.device, "_OffloadStager"] = {}
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.stream = torch.cuda.Stream(device=device)
+        self.slots = [dict(buf={}, ready=None, free=None, owner=None) for _ in range(2)]
+        self.stats = dict(h2d_bytes=0, copies=0, prefetch_hits=0)
+
+    @classmethod
+    def get(cls, device: torch.device) -> "_OffloadStager":
+        if device not in cls._by_device:
+            cls._by_device[device] = cls(device)
+        return cls._by_device[device]
+
+    def _issue(self, module: nn.Module, keep: Optional[nn.Module] = None) -> dict:
+        # a free slot if there is one, otherwise the one that does not hold `keep`
+        slot = next((s for s in self.slots if s["owner"] is None), None)
+        if slot is None:
+            slot = next(s for s in self.slots if s["owner"] is not keep)
+        compute = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self.stream):
+            if slot["free"] is not None:
+                self.stream.wait_event(slot["free"])
+            for name, host in module.offloaded_tensors.items():
+                buf = slot["buf"].get(name)
+                if buf is None or buf.numel() < host.numel():
+                    # grown on the compute stream's allocator view; sized once per run in practice
+                    buf = torch.empty(host.numel(), dtype=torch.uint8, device=self.device)
+                    buf.record_stream(compute)
+                    slot["buf"][name] = buf
+                buf[:host.numel()].copy_(host, non_blocking=True)
+                self.stats["h2d_bytes"] += host.numel()
+                self.stats["copies"] += 1
+            slot["ready"] = torch.cuda.Event()
+            slot["ready"].record(self.stream)
+        slot["owner"] = module
+        return slot
+
+    def fetch(self, module: nn.Module) -> Dict[str, torch.Tensor]:
+        """Device views of the unit's offloaded tensors, valid for work queued on the current
+        stream after this call; also starts the copy of the unit that follows."""
+        slot = next((s for s in self.slots if s["owner"] is module and s["ready"] is not None), None)
+        if slot is None:
+            slot = self._issue(module)
+        else:
+            self.stats["prefetch_hits"] += 1
+        torch.cuda.current_stream(self.device).wait_event(slot["ready"])
+        views = {name: slot["buf"][name][:host.numel()] for name, host in module.offloaded_tensors.items()}
+        # prefetch the unit that runs next (the loader links the offloaded units in forward order)
+        nxt = getattr(module, "df11_next_offloaded", None)
+        if nxt is not None and nxt is not module and nxt.luts.device == self.device and not any(s["owner"] is nxt and s["ready"] is not None for s in self.slots):
+            self._issue(nxt, keep=module)
+        return views
+
+    def done(self, module: nn.Module) -> None:
+        """Call after the decode of ``module`` has been queued: its slot may be overwritten
+        once that decode has run."""
+        for s in self.slots:
+            if s["owner"] is module:
+                s["free"] = torch.cuda.Event()
+                s["free"].record(torch.cuda.current_stream(self.device))
+                s["ready"] = None
+                s["owner"] = None
+
+
+def _inject_weights(module: nn.Module, reconstructed: torch.Tensor) -> None:
+    """Hand the decoded BF16 buffer to the layers as views (dfloat11.py:154-166)."""
+    if isinstance(module, nn.Linear):
+        module.weight = reconstructed.view(module.out_features, module.in_features)
+    elif isinstance(module, nn.Embedding):
+        module.weight = reconstructed.view(module.num_embeddings, module.embedding_dim)
+    else:
+        weights = torch.tensor_split(reconstructed, module.split_positions)
+        for sub_module, weight in zip(module.weight_injection_modules, weights):
+            sub_module.weight = weight.view(sub_module.out_features, sub_module.in_features)
+
+
+def get_hook(threads_per_block, bytes_per_thread):
+    """Forward pre-hook that decompresses a unit's weights right before its forward
+    (dfloat11.py:103-176).  The two arguments are the format constants; only 512 / 8 exist."""
+    threads_per_block = tuple(threads_per_block)
+    if threads_per_block[0] != 512 or bytes_per_thread != 8:
+        raise ValueError("DF11 files are laid out for 512 threads per block and 8 bytes per thread "
+                         f"(got {threads_per_block[0]} / {bytes_per_thread})")
+
+    def decode_hook(module, _):
+        device = module.luts.device
+        if device.type != "cuda":
+            raise RuntimeError("DF11 weights can only be decompressed on a CUDA device; move the model to "
+                               f"one (this unit's tables are on {device})")
+
+        # compressed tensors: resident buffers, or the staging slot of the offload pipeline
+        stager = None
+        if hasattr(module, "offloaded_tensors"):
+            stager = _OffloadStager.get(device)
+            staged = stager.fetch(module)
+            encoded_exponent, sign_mantissa = staged["encoded_exponent"], staged["sign_mantissa"]
+        else:
+            encoded_exponent, sign_mantissa = module.encoded_exponent, module.sign_mantissa
+
+        n_elements = sign_mantissa.numel()
+        reconstructed = TensorManager.allocate_bfloat16(device, n_elements)
+        widest = getattr(module, "max_block_elems", 0)
+
+        if _use_prepared():
+            aux = getattr(module, "df11_aux", None)
+            if aux is None or aux.device != device:
+                # once per unit and device: decode table + seek points (derived data, never saved)
+                aux = ops.prepare(module.luts, encoded_exponent, module.output_positions, module.gaps, n_elements)
+                module.df11_aux = aux
+            ops.decode_prepared(module.luts, encoded_exponent, sign_mantissa, module.output_positions,
+                                module.gaps, aux, out=reconstructed, max_block_elems=widest)
+        else:
+            ops.decode(module.luts, encoded_exponent, sign_mantissa, module.output_positions, module.gaps,
+                       out=reconstructed, max_block_elems=widest)
+
+        _inject_weights(module, reconstructed)
+        if stager is not None:
+            stager.done(module)
+
+    return decode_hook
+
+
+def _positions_u32(tensor: torch.Tensor) -> np.ndarray:
+    """``output_positions`` is stored as a byte view of uint32 values (dfloat11.py:596)."""
+    arr = tensor.cpu().numpy()
+    return arr.view(np.uint32) if arr.dtype == np.uint8 else arr.astype(np.uint32)
+
+
+def _finish_unit(module: nn.Module, full_name: str) -> None:
+    """Checks a freshly loaded unit and derives what the launches need from it."""
+    have = {n: getattr(module, n, None) for n in ("luts", "output_positions", "gaps")}
+    enc = getattr(module, "encoded_exponent", None)
+    sm = getattr(module, "sign_mantissa", None)
+    if hasattr(module, "offloaded_tensors"):
+        enc = module.offloaded_tensors.get("encoded_exponent", enc)
+        sm = module.offloaded_tensors.get("sign_mantissa", sm)
+    missing = [n for n, t in dict(have, encoded_exponent=enc, sign_mantissa=sm).items() if t is None]
+    if missing:
+        raise ValueError(f"DF11 unit '{full_name}' is incomplete: missing {', '.join(missing)}")
+    widest = codec.validate_unit(have["luts"], enc, sm, have["output_positions"], have["gaps"])
+    module.max_block_elems = widest
+    # kept for code that reads the reference's attribute (dfloat11.py:299-306)
+    module.shared_mem_size = threads_per_block[0] * 4 + 4 + widest * 2
+    if not hasattr(module, "split_positions"):
+        module.split_positions = []
+
+
+def load_and_replace_tensors(
+    model,
+    directory_path,
+    dfloat11_config,
+    cpu_offload=False,
+    cpu_offload_blocks=None,
+    pin_memory=True,
+    from_single_file=False,
+):
+    """Loads DF11 safetensors into ``model`` and arms on-the-fly decompression (dfloat11.py:179-308).
+
+    Ordinary tensors are copied into the matching parameters / buffers.  The six tensors of a
+    compressed unit become buffers of the module named by their prefix (``split_positions``
+    a Python list); with ``cpu_offload`` the two large ones stay in (pinned) host memory in
+    ``module.offloaded_tensors``.  The module gets the decode hook and loses the ``weight``
+    attributes the hook will supply.
+    """
+    from safetensors.torch import load_file
+
+    tpb = dfloat11_config["threads_per_block"]
+    bpt = dfloat11_config["bytes_per_thread"]
+    pattern_dict = dfloat11_config["pattern_dict"] or {}
+    hook = get_hook(tpb, bpt)
+
+    if from_single_file:
+        files = [directory_path]
+    else:
+        files = sorted(os.path.join(directory_path, f) for f in os.listdir(directory_path)
+                       if f.endswith(".safetensors"))
+    params = dict(model.named_parameters())
+    buffers = dict(model.named_buffers())
+    modules = dict(model.named_modules())
+    units: Dict[str, nn.Module] = {}
+
+    for file_path in files:
+        loaded = load_file(file_path)
+        for tensor_name, value in loaded.items():
+            target = params.get(tensor_name)
+            if target is None:
+                target = buffers.get(tensor_name)
+            if target is not None:
+                if target.shape == value.shape:
+                    with torch.no_grad():
+                        target.copy_(value)
+                else:
+                    print(f"Shape mismatch for {tensor_name}: model {tuple(target.shape)} vs loaded "
+                          f"{tuple(value.shape)}", file=stderr)
+                continue
+
+            module_path, _, leaf = tensor_name.rpartition(".")
+            module = modules.get(module_path)
+            if module is None:
+                print(f"Cannot find module path for {tensor_name}", file=stderr)
+                continue
+            units[module_path] = module
+
+            if leaf == "split_positions":
+                module.split_positions = value.tolist()
+            elif (cpu_offload and (cpu_offload_blocks is None or cpu_offload_blocks > 0)
+                  and leaf in offloaded_tensor_names):
+                if not hasattr(module, "offloaded_tensors"):
+                    module.offloaded_tensors = {}
+                module.offloaded_tensors[leaf] = value.pin_memory() if pin_memory else value
+                if (cpu_offload_blocks is not None and cpu_offload_blocks > 0
+                        and len(module.offloaded_tensors) == len(offloaded_tensor_names)):
+                    cpu_offload_blocks -= 1
+            else:
+                module.register_buffer(leaf, value)
+
+            if leaf == "encoded_exponent":
+                module.register_forward_pre_hook(hook)
+                _remove_weights(module, module_path, pattern_dict)
+
+    for name, module in units.items():
+        _finish_unit(module, name)
+
+    # offloaded units, linked in forward (definition) order for the prefetcher
+    offloaded = [m for m in modules.values() if hasattr(m, "offloaded_tensors")]
+    for a, b in zip(offloaded, offloaded[1:] + offloaded[:1]):
+        a.__dict__["df11_next_offloaded"] = b          # a plain reference, not a registered submodule
+    return model
+
+
+def _remove_weights(module: nn.Module, module_path: str, pattern_dict) -> None:
+    """Deletes the ``weight`` attributes that the hook supplies (dfloat11.py:273-298)."""
+    def drop(target):
+        if "weight" in target._parameters:
+            del target._parameters["weight"]
+        elif hasattr(target, "weight"):
+            delattr(target, "weight")
+
+    if isinstance(module, (nn.Linear, nn.Embedding)):
+        drop(module)
+        return
+    for pattern, attr_names in pattern_dict.items():
+        if re.fullmatch(pattern, module_path):
+            module.weight_injection_modules = []
+            for attr_path in attr_names:
+                target = module
+                for part in attr_path.split("."):
+                    target = getattr(target, part)
+                drop(target)
+                module.weight_injection_modules.append(target)
+            return
+    raise ValueError(f"compressed unit '{module_path}' is neither a Linear / Embedding nor matched by "
+                     "`pattern_dict`, so its weights cannot be injected")
+
+
+def get_no_split_classes(model, pattern_dict):
+    """Class names of the modules matched by ``pattern_dict``: a compressed unit must stay on one
+    device together with its decompression buffer (dfloat11.py:311-333)."""
+    no_split_classes = []
+    for pattern in pattern_dict or {}:
+        for full_name, sub_module in model.named_modules():
+            if re.fullmatch(pattern, full_name):
+                class_name = sub_module.__class__.__name__
+                if class_name not in no_split_classes:
+                    no_split_classes.append(class_name)
+    return no_split_classes
+
+
+class DFloat11Model:
+    """Loads models whose weights are stored in the DF11 format (dfloat11.py:336-493)."""
+
+    @classmethod
+    def from_pretrained(
+        cls,
+        dfloat11_model_name_or_path: str,
+        device: Optional[str] = None,
+        device_map: str = "auto",
+        max_memory: Optional[Dict[Union[int, str], Union[int, str]]] = None,
+        bfloat16_model=None,
+        cpu_offload: bool = False,
+        cpu_offload_blocks: Optional[int] = None,
+        pin_memory: bool = True,
+        from_single_file: bool = False,
+        pattern_dict: Optional[Dict[str, List[str]]] = None,
+        **kwargs,
+    ):
+        """Same arguments and behaviour as the reference's ``from_pretrained`` (dfloat11.py:343-464):
+        resolve the path, build the model skeleton (or take ``bfloat16_model``), read
+        ``dfloat11_config``, load and arm the compressed units, place the model on ``device``
+        or spread whole units over the visible GPUs."""
+        path = _resolve_path(dfloat11_model_name_or_path, from_single_file)
+
+        if bfloat16_model is not None:
+            if from_single_file:
+                config = {"dfloat11_config": {"version": version, "threads_per_block": threads_per_block,
+                                              "bytes_per_thread": bytes_per_thread, "pattern_dict": pattern_dict}}
+            else:
+                with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as f:
+                    config = json.load(f)
+            model = bfloat16_model
+        else:
+            from transformers import AutoConfig, AutoModelForCausalLM, GenerationConfig
+            try:
+                from transformers.initialization import no_init_weights
+            except ImportError:  # older transformers
+                from transformers.modeling_utils import no_init_weights
+            config = AutoConfig.from_pretrained(path)
+            with no_init_weights():
+                model = AutoModelForCausalLM.from_config(config, dtype=torch.bfloat16, **kwargs)
+                model.tie_weights()
+                model.eval()
+            try:
+                model.generation_config = GenerationConfig.from_pretrained(path)
+            except Exception:  # noqa: BLE001 - optional file
+                pass
+
+        if isinstance(config, dict) and "dfloat11_config" in config:
+            dfloat11_config = config["dfloat11_config"]
+        elif hasattr(config, "dfloat11_config"):
+            dfloat11_config = config.dfloat11_config
+        else:
+            raise AttributeError('"dfloat11_config" not found: it is expected to be found in the config file or '
+                                 "passed as an argument.")
+
+        load_and_replace_tensors(model, path, dfloat11_config, cpu_offload=cpu_offload,
+                                 cpu_offload_blocks=cpu_offload_blocks, pin_memory=pin_memory,
+                                 from_single_file=from_single_file)
+
+        if not cpu_offload:
+            model_bytes = sum(t.numel() * t.element_size() for t in model.state_dict().values())
+            print(f"Total model size: {model_bytes / 1e9:0.4f} GB", file=stderr)
+
+        if device:
+            model = model.to(device)
+        else:
+            assert device_map == "auto", "device_map should be 'auto' if no specific device is provided."
+            from .placement import dispatch_model, infer_device_map
+            no_split = get_no_split_classes(model, dfloat11_config["pattern_dict"])
+            mapping = infer_device_map(model, no_split_module_classes=no_split, max_memory=max_memory)
+            model = dispatch_model(model, mapping)
+            if any(p.device.type == "cpu" for p in model.parameters()):
+                print("Warning: Some model layers are on CPU. For inference, ensure the model is fully loaded "
+                      "onto CUDA-compatible GPUs.", file=stderr)
+        return model
+
+    @classmethod
+    def from_single_file(
+        cls,
+        dfloat11_model_path: str,
+        pattern_dict: Dict[str, List[str]],
+        bfloat16_model,
+        device: Optional[str] = None,
+        device_map: str = "auto",
+        max_memory: Optional[Dict[Union[int, str], Union[int, str]]] = None,
+        cpu_offload: bool = False,
+        cpu_offload_blocks: Optional[int] = None,
+        pin_memory: bool = True,
+    ):
+        return cls.from_pretrained(
+            dfloat11_model_name_or_path=dfloat11_model_path, device=device, device_map=device_map,
+            max_memory=max_memory, bfloat16_model=bfloat16_model, cpu_offload=cpu_offload,
+            cpu_offload_blocks=cpu_offload_blocks, pin_memory=pin_memory, from_single_file=True,
+            pattern_dict=pattern_dict)
+
+
+def _resolve_path(name_or_path: str, from_single_file: bool) -> str:
+    """dfloat11.py:377-390, with the hub download optional (it needs a network)."""
+    if from_single_file:
+        if os.path.isfile(name_or_path):
+            return name_or_path
+        if os.path.isdir(name_or_path):
+            raise IsADirectoryError("Expected `dfloat11_model_name_or_path` to be the path to a safetensors file, "
+                                    f'but found a directory: "{name_or_path}".')
+        raise FileNotFoundError(f'The file "{name_or_path}" does not exist.')
+    if os.path.exists(name_or_path):
+        return name_or_path
+    local = name_or_path.replace("/", "__")
+    if not os.path.exists(local):
+        try:
+            from huggingface_hub import snapshot_download
+        except ImportError as exc:
+            raise FileNotFoundError(f'"{name_or_path}" is not a local path and huggingface_hub is not '
+                                    "installed to download it") from exc
+        snapshot_download(name_or_path, local_dir=local)
+    return local
+
+
+def _unit_weights(full_name: str, sub_module: nn.Module, attr_names) -> List[torch.Tensor]:
+    """Flattened BF16 weights of one unit, in the order they are concatenated, removed from
+    their modules (dfloat11.py:528-550)."""
+    if isinstance(sub_module, (nn.Embedding, nn.Linear)):
+        targets = [("", sub_module)]
+    else:
+        targets = []
+        for attr_path in attr_names:
+            target = sub_module
+            for part in attr_path.split("."):
+                target = getattr(target, part)
+            targets.append((attr_path, target))
+    weights = []
+    for attr_path, target in targets:
+        where = f"{full_name}.{attr_path}" if attr_path else full_name
+        assert target.weight.data.dtype == torch.bfloat16, \
+            f"Expected weights to be in bfloat16 format for compression, but '{where}' has dtype " \
+            f"{target.weight.data.dtype}"
+        weights.append(target.weight.data.detach().cpu().flatten())
+        delattr(target, "weight")
+    return weights
+
+
+def check_unit(tensors: Dict[str, torch.Tensor], weights: List[torch.Tensor], device="cuda:0") -> bool:
+    """Decompresses freshly made DF11 tensors on the GPU and compares them with the original
+    weights, bit for bit -- the reference's self-check (dfloat11.py:560-591)."""
+    dev = torch.device(device)
+    d = {k: tensors[k].to(dev) for k in ("luts", "encoded_exponent", "sign_mantissa", "output_positions", "gaps")}
+    widest = codec.validate_unit(tensors["luts"], tensors["encoded_exponent"], tensors["sign_mantissa"],
+                                 tensors["output_positions"], tensors["gaps"])
+    out = ops.decode(d["luts"], d["encoded_exponent"], d["sign_mantissa"], d["output_positions"], d["gaps"],
+                     max_block_elems=widest)
+    want = torch.cat([w.reshape(-1) for w in weights]).view(torch.int16)
+    return bool(torch.equal(out.cpu().view(torch.int16), want))
+
+
+def compress_model(
+    model,
+    pattern_dict: Dict[str, List[str]],
+    save_path: str,
+    block_range: List[int] = [0, 10000],
+    save_single_file: bool = True,
+    check_correctness: bool = True,
+):
+    """Compresses the matched modules of a BF16 model into DF11 and saves it (dfloat11.py:496-636).
+
+    Same arguments, same files: ``model.safetensors`` (or one file per unit plus the model's own
+    ``save_pretrained``) and a ``config.json`` carrying ``dfloat11_config``.  ``check_correctness``
+    decompresses every unit on ``cuda:0`` and compares it with the original weights.
+    """
+    from safetensors.torch import save_file
+
+    os.makedirs(save_path, exist_ok=True)
+    if check_correctness and not torch.cuda.is_available():
+        raise RuntimeError("check_correctness decompresses on cuda:0; no CUDA device is available")
+
+    block_index = 0
+    save_model = True
+    for pattern, attr_names in pattern_dict.items():
+        for full_name, sub_module in list(model.named_modules()):
+            if not re.fullmatch(pattern, full_name):
+                continue
+            if not save_single_file:
+                if "." in full_name:
+                    parent_name, child_name = full_name.rsplit(".", 1)
+                    setattr(model.get_submodule(parent_name), child_name, None)
+                else:
+                    setattr(model, full_name, None)
+
+            block_index += 1
+            if block_index <= block_range[0]:
+                continue
+            elif block_index > block_range[1]:
+                save_model = False
+                break
+
+            weights = _unit_weights(full_name, sub_module, attr_names)
+            tensors = codec.encode_weights(weights)
+            n = tensors["sign_mantissa"].numel()
+            stored = sum(tensors[k].numel() for k in ("encoded_exponent", "sign_mantissa", "output_positions", "gaps"))
+            log.info("%s: %d elements, %.2f%% of BF16", full_name, n, stored * 100 / (2 * n))
+
+            if check_correctness and not check_unit(tensors, weights):
+                raise RuntimeError("Correctness check failed: the decompressed weights do not match the original "
+                                   f'weights for module "{full_name}".')
+
+            for key in ("luts", "encoded_exponent", "sign_mantissa", "output_positions", "gaps", "split_positions"):
+                sub_module.register_buffer(key, tensors[key])
+
+            if not save_single_file:
+                state_dict = {f"{full_name}.{key}": value for key, value in sub_module.state_dict().items()}
+                save_file(state_dict, os.path.join(save_path, full_name.replace(".", "_") + ".safetensors"))
+
+    if save_model:
+        dfloat11_config = {"version": version, "threads_per_block": threads_per_block,
+                           "bytes_per_thread": bytes_per_thread, "pattern_dict": pattern_dict}
+        if hasattr(model, "config"):
+            try:
+                model.config.dfloat11_config = dfloat11_config
+            except Exception:  # noqa: BLE001
+                pass
+
+        if hasattr(model, "save_pretrained") and not save_single_file:
+            model.save_pretrained(save_path)
+        else:
+            save_file({k: v.contiguous() for k, v in model.state_dict().items()},
+                      os.path.join(save_path, "model.safetensors"))
+
+        save_config = True
+        config_path = os.path.join(save_path, "config.json")
+        if os.path.exists(config_path):
+            with open(config_path, "r", encoding="utf-8") as f:
+                existing = json.load(f)
+            if isinstance(existing.get("dfloat11_config"), dict):
+                save_config = False
+        if save_config:
+            existing = {}
+            if os.path.exists(config_path):
+                with open(config_path, "r", encoding="utf-8") as f:
+                    existing = json.load(f)
+            existing["dfloat11_config"] = dfloat11_config
+            with open(config_path, "w", encoding="utf-8") as f:
+                json.dump(existing, f, indent=2)

@@ -1,0 +1,223 @@
+"""Loader, hook, buffer manager, offload and model API (mirrors of dfloat11/dfloat11.py).
+
+CPU tests cover the file format round trip (``compress_model`` -> safetensors + config ->
+``load_and_replace_tensors``) with every unit decoded by the CPU oracle; GPU tests check that a
+DF11 model produces logits bit-identical to the uncompressed BF16 model, with and without
+``cpu_offload``, through ``DFloat11Model.from_pretrained``.
+"""
+import copy
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+import dfloat11_b200 as df11
+from dfloat11_b200 import dfloat11 as host
+from dfloat11_b200.placement import infer_device_map, module_bytes
+from oracle import df11_oracle as oracle
+
+LLAMA_PATTERNS = {
+    r"model\.embed_tokens": [],
+    r"model\.layers\.\d+": ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+                             "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj"],
+    r"lm_head": [],
+}
+
+
+def tiny_llama(seed=0):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=704, num_hidden_layers=3, num_attention_heads=8,
+                      num_key_value_heads=2, vocab_size=1024, max_position_embeddings=256,
+                      tie_word_embeddings=False)
+    torch.manual_seed(seed)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 2:
+                p.copy_((torch.randn(p.shape) * (1.0 if "embed" in name else 0.02)).to(torch.bfloat16))
+    return model
+
+
+@pytest.fixture(scope="module")
+def saved(tmp_path_factory):
+    model = tiny_llama()
+    reference = copy.deepcopy(model)
+    path = str(tmp_path_factory.mktemp("df11_llama"))
+    df11.compress_model(model, LLAMA_PATTERNS, path, save_single_file=False, check_correctness=False)
+    return path, reference
+
+
+def test_compress_model_writes_the_reference_layout(saved):
+    path, reference = saved
+    files = sorted(f for f in os.listdir(path) if f.endswith(".safetensors"))
+    assert "model_layers_0.safetensors" in files and "lm_head.safetensors" in files
+    with open(os.path.join(path, "config.json")) as f:
+        cfg = json.load(f)["dfloat11_config"]
+    assert cfg["bytes_per_thread"] == 8 and list(cfg["threads_per_block"]) == [512]
+    assert set(cfg["pattern_dict"]) == set(LLAMA_PATTERNS)
+    from safetensors.torch import load_file
+    t = load_file(os.path.join(path, "model_layers_1.safetensors"))
+    direct = {k[len("model.layers.1."):] for k in t if k.count(".") == 3}
+    assert direct == {"luts", "encoded_exponent", "sign_mantissa", "output_positions", "gaps", "split_positions"}
+    assert "model.layers.1.input_layernorm.weight" in t          # the block's own small tensors travel with it
+    assert not any(k.endswith("proj.weight") for k in t)
+    assert t["model.layers.1.output_positions"].dtype == torch.uint8
+    assert t["model.layers.1.split_positions"].dtype == torch.int64
+    # the stored unit decodes (CPU oracle) to the original seven matrices, in order
+    out = oracle.decode_c(*(t[f"model.layers.1.{k}"].numpy() for k in
+                            ("luts", "encoded_exponent", "sign_mantissa", "output_positions", "gaps")))
+    layer = reference.model.layers[1]
+    want = torch.cat([layer.get_submodule(a).weight.detach().flatten() for a in LLAMA_PATTERNS[r"model\.layers\.\d+"]])
+    assert np.array_equal(out, want.view(torch.int16).numpy().view(np.uint16))
+
+
+def test_loader_arms_units_on_cpu(saved):
+    path, reference = saved
+    model = df11.DFloat11Model.from_pretrained(path, device="cpu", bfloat16_model=tiny_llama(seed=7))
+    layer = model.model.layers[0]
+    for name in ("luts", "encoded_exponent", "sign_mantissa", "output_positions", "gaps"):
+        assert name in dict(layer.named_buffers(recurse=False))
+    assert isinstance(layer.split_positions, list) and len(layer.split_positions) == 6
+    assert len(layer.weight_injection_modules) == 7
+    assert not hasattr(layer.self_attn.q_proj, "weight")
+    assert not hasattr(model.lm_head, "weight") and not hasattr(model.model.embed_tokens, "weight")
+    assert layer.max_block_elems > 0 and layer.shared_mem_size == 2052 + 2 * layer.max_block_elems
+    # uncompressed tensors (norms) were copied from the file, not left at the skeleton's values
+    assert torch.equal(model.model.norm.weight, reference.model.norm.weight)
+    # without a GPU the hook refuses to run instead of falling back to something else
+    with pytest.raises(RuntimeError):
+        model(torch.zeros(1, 4, dtype=torch.long))
+
+
+def test_loader_offload_keeps_big_tensors_on_host(saved):
+    path, _ = saved
+    model = df11.DFloat11Model.from_pretrained(path, device="cpu", bfloat16_model=tiny_llama(seed=7),
+                                               cpu_offload=True, cpu_offload_blocks=2, pin_memory=False)
+    offloaded = [m for m in model.modules() if hasattr(m, "offloaded_tensors")]
+    assert len(offloaded) == 2                                   # cpu_offload_blocks limits the count
+    for m in offloaded:
+        assert set(m.offloaded_tensors) == {"encoded_exponent", "sign_mantissa"}
+        assert "encoded_exponent" not in dict(m.named_buffers(recurse=False))
+        assert m.df11_next_offloaded in offloaded
+
+
+def test_loader_rejects_corrupt_units(saved, tmp_path):
+    path, _ = saved
+    from safetensors.torch import load_file, save_file
+    t = load_file(os.path.join(path, "lm_head.safetensors"))
+    t["lm_head.luts"] = t["lm_head.luts"].clone()
+    t["lm_head.luts"][-1] = 0                                     # zero code lengths
+    bad = str(tmp_path / "bad.safetensors")
+    save_file(t, bad)
+    skeleton = nn.Module()
+    skeleton.lm_head = nn.Linear(256, 1024, bias=False).to(torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        df11.DFloat11Model.from_single_file(bad, pattern_dict={r"lm_head": []}, bfloat16_model=skeleton, device="cpu")
+
+
+def test_missing_config_and_paths(tmp_path, saved):
+    with pytest.raises(FileNotFoundError):
+        df11.DFloat11Model.from_pretrained(str(tmp_path / "nope.safetensors"), from_single_file=True,
+                                           bfloat16_model=nn.Linear(2, 2))
+    with pytest.raises(IsADirectoryError):
+        df11.DFloat11Model.from_pretrained(str(tmp_path), from_single_file=True, bfloat16_model=nn.Linear(2, 2))
+    (tmp_path / "config.json").write_text("{}")
+    with pytest.raises(AttributeError):
+        df11.DFloat11Model.from_pretrained(str(tmp_path), bfloat16_model=nn.Linear(2, 2), device="cpu")
+
+
+def test_get_hook_rejects_other_layouts():
+    with pytest.raises(ValueError):
+        host.get_hook((256,), 8)
+
+
+def test_no_split_classes_and_device_map(saved):
+    path, _ = saved
+    model = df11.DFloat11Model.from_pretrained(path, device="cpu", bfloat16_model=tiny_llama(seed=7))
+    classes = df11.get_no_split_classes(model, LLAMA_PATTERNS)
+    assert "LlamaDecoderLayer" in classes and "Linear" in classes and "Embedding" in classes
+    mapping = infer_device_map(model, classes, devices=[0, 1])
+    assert {str(d) for d in mapping.values()} == {"cuda:0", "cuda:1"}
+    # a compressed block is never divided and blocks fill devices in order
+    layer_devs = [mapping[f"model.layers.{i}"] for i in range(3)]
+    assert layer_devs == sorted(layer_devs, key=lambda d: d.index)
+    assert not any(k.startswith("model.layers.0.") for k in mapping)
+    assert module_bytes(model) == sum(module_bytes(model.get_submodule(k)) for k in mapping)
+
+
+def test_tensor_manager_reuses_and_grows():
+    host.TensorManager.release()
+    a = host.TensorManager.allocate_bfloat16("cpu", 100)
+    b = host.TensorManager.allocate_bfloat16("cpu", 60)
+    assert b.data_ptr() == a.data_ptr() and b.numel() == 60
+    c = host.TensorManager.allocate_bfloat16("cpu", 500)
+    assert c.numel() == 500 and host.TensorManager._tensors[torch.device("cpu")].numel() == 500
+    host.TensorManager.release()
+
+
+# ------------------------------------------------------------------ GPU
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["resident", "offload", "offload_some", "two_pass", "auto_map"])
+def test_logits_identical_to_bf16_model(saved, mode, monkeypatch):
+    path, reference = saved
+    kwargs = dict(device="cuda:0")
+    if mode == "offload":
+        kwargs["cpu_offload"] = True
+    elif mode == "offload_some":
+        kwargs.update(cpu_offload=True, cpu_offload_blocks=2)
+    elif mode == "two_pass":
+        monkeypatch.setenv("DF11_PREPARED", "0")
+    elif mode == "auto_map":
+        kwargs = dict(device=None, device_map="auto")
+    model = df11.DFloat11Model.from_pretrained(path, bfloat16_model=tiny_llama(seed=7), **kwargs)
+    ref = copy.deepcopy(reference).to("cuda:0")
+    ids = torch.randint(0, 1024, (2, 33), generator=torch.Generator().manual_seed(3)).to("cuda:0")
+    with torch.no_grad():
+        for _ in range(3):                      # several forwards: scratch and staging slots are reused
+            got = model(input_ids=ids).logits
+            want = ref(input_ids=ids).logits
+            assert torch.equal(got, want)
+        out_a = model.generate(ids[:1, :8], max_new_tokens=12, do_sample=False)
+        out_b = ref.generate(ids[:1, :8], max_new_tokens=12, do_sample=False)
+    assert torch.equal(out_a, out_b)
+    if mode.startswith("offload"):
+        stager = host._OffloadStager.get(torch.device("cuda:0"))
+        assert stager.stats["prefetch_hits"] > 0 and stager.stats["h2d_bytes"] > 0
+
+
+@pytest.mark.gpu
+def test_compress_model_self_check_and_single_file(tmp_path):
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = nn.Linear(384, 640, bias=True)
+            self.b = nn.Linear(640, 384, bias=False)
+
+        def forward(self, x):
+            return self.b(torch.relu(self.a(x)))
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.blocks = nn.ModuleList([Block() for _ in range(2)])
+            self.head = nn.Linear(384, 10)
+
+        def forward(self, x):
+            for blk in self.blocks:
+                x = x + blk(x)
+            return self.head(x)
+
+    torch.manual_seed(1)
+    net = Net().to(torch.bfloat16).eval()
+    reference = copy.deepcopy(net).to("cuda:0")
+    patterns = {r"blocks\.\d+": ["a", "b"], r"head": []}
+    df11.compress_model(net, patterns, str(tmp_path), save_single_file=True, check_correctness=True)
+    torch.manual_seed(2)
+    loaded = df11.DFloat11Model.from_single_file(os.path.join(str(tmp_path), "model.safetensors"), patterns,
+                                                 Net().to(torch.bfloat16).eval(), device="cuda:0")
+    x = torch.randn(5, 384, dtype=torch.bfloat16, device="cuda:0")
+    with torch.no_grad():
+        assert torch.equal(loaded(x), reference(x))
