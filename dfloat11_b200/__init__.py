@@ -5,12 +5,13 @@ a missing or stale library is an ImportError -- there is no CPU or pure-PyTorch 
 """
 from . import _lib  # noqa: F401  (fails loudly when the native library is absent)
 from .codec import UnrepresentableError, encode_weights, get_codec, get_luts, split_bf16, validate_unit
-from .dfloat11 import (DFloat11Model, TensorManager, compress_model, get_hook, get_no_split_classes,
+from .dfloat11 import (DFloat11Model, TensorManager, compress_in_place, compress_model, get_hook,
+                       get_no_split_classes,
                        load_and_replace_tensors)
 from .ops import aux_bytes, decode, decode_prepared, prepare
 
 __all__ = [
-    "DFloat11Model", "TensorManager", "compress_model", "get_hook", "get_no_split_classes",
+    "DFloat11Model", "TensorManager", "compress_in_place", "compress_model", "get_hook", "get_no_split_classes",
     "load_and_replace_tensors",
     "UnrepresentableError", "encode_weights", "get_codec", "get_luts", "split_bf16", "validate_unit",
     "aux_bytes", "decode", "decode_prepared", "prepare",

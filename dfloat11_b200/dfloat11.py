@@ -606,3 +606,41 @@ def compress_model(
             existing["dfloat11_config"] = dfloat11_config
             with open(config_path, "w", encoding="utf-8") as f:
                 json.dump(existing, f, indent=2)
+
+
+def compress_in_place(model, pattern_dict: Dict[str, List[str]], cpu_offload: bool = False,
+                      pin_memory: bool = True):
+    """Turns the matched modules of a BF16 model into armed DF11 units without going through
+    files: what ``compress_model`` followed by ``DFloat11Model.from_pretrained`` leaves behind,
+    on the devices the modules are already on.  (No counterpart in the reference, which always
+    saves and reloads; used by the benchmark and handy for experiments.)"""
+    hook = get_hook(threads_per_block, bytes_per_thread)
+    for pattern, attr_names in pattern_dict.items():
+        for full_name, sub_module in list(model.named_modules()):
+            if not re.fullmatch(pattern, full_name):
+                continue
+            device = next(sub_module.parameters()).device
+            weights = _unit_weights(full_name, sub_module, attr_names)
+            tensors = codec.encode_weights(weights)
+            del weights
+            sub_module.split_positions = tensors.pop("split_positions").tolist()
+            for key, value in tensors.items():
+                if cpu_offload and key in offloaded_tensor_names:
+                    if not hasattr(sub_module, "offloaded_tensors"):
+                        sub_module.offloaded_tensors = {}
+                    sub_module.offloaded_tensors[key] = value.pin_memory() if pin_memory else value
+                else:
+                    sub_module.register_buffer(key, value.to(device), persistent=False)
+            if not isinstance(sub_module, (nn.Linear, nn.Embedding)):
+                sub_module.weight_injection_modules = []
+                for attr_path in attr_names:
+                    target = sub_module
+                    for part in attr_path.split("."):
+                        target = getattr(target, part)
+                    sub_module.weight_injection_modules.append(target)
+            _finish_unit(sub_module, full_name)
+            sub_module.register_forward_pre_hook(hook)
+    offloaded = [m for m in model.modules() if hasattr(m, "offloaded_tensors")]
+    for a, b in zip(offloaded, offloaded[1:] + offloaded[:1]):
+        a.__dict__["df11_next_offloaded"] = b
+    return model

@@ -74,8 +74,9 @@ def _u8(a):
 
 
 def decode_c(luts, codes, sign_mantissa, output_positions, gaps, n_threads: int = 1,
-             strict: bool = True) -> np.ndarray:
-    """Decode one DF11 unit on the CPU.  Returns the BF16 bit patterns as uint16."""
+             strict: bool = True, out: np.ndarray | None = None) -> np.ndarray:
+    """Decode one DF11 unit on the CPU.  Returns the BF16 bit patterns as uint16 (written into
+    ``out`` when given, which keeps page faults of a fresh buffer out of a timing)."""
     luts = _u8(luts).reshape(-1, 256)
     codes = _u8(codes)
     sm = _u8(sign_mantissa)
@@ -84,7 +85,9 @@ def decode_c(luts, codes, sign_mantissa, output_positions, gaps, n_threads: int 
     if pos.dtype == np.uint8:       # stored as a byte view on disk (dfloat11.py:596)
         pos = pos.view(np.uint32)
     assert pos.dtype == np.uint32
-    out = np.zeros(sm.size, dtype=np.uint16)
+    if out is None:
+        out = np.zeros(sm.size, dtype=np.uint16)
+    assert out.dtype == np.uint16 and out.size >= sm.size and out.flags.c_contiguous
     rc = _load().df11_oracle_decode(
         luts.ctypes.data, luts.shape[0], codes.ctypes.data, codes.size,
         sm.ctypes.data, sm.size, pos.ctypes.data, gaps.ctypes.data, gaps.size,
