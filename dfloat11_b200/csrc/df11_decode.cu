@@ -17,7 +17,7 @@
 //
 // df11_decode_kernel (behind df11_decode): needs nothing but the six DF11 tensors.
 // Persistent CTAs walk the format blocks; every global read is a TMA bulk copy
-// (cp.async.bulk with mbarrier completion, no multicast): the next block's bitstream and
+// (cp.async.bulk with mbarrier completion, each CTA fetching for itself): the next block's bitstream and
 // gap bytes arrive in a double buffer while the current block is decoded, and the block's
 // sign/mantissa bytes arrive while its exponents are decoded.  One window per thread in
 // three registers; output slots from a counting pass and a warp-shuffle scan (2 barriers
@@ -108,7 +108,7 @@ __device__ __forceinline__ void sts8(uint32_t a, uint32_t v)
     asm volatile("st.shared.u8 [%0+%2], %1;" ::"r"(a), "r"(v), "n"(OFF) : "memory");
 }
 
-// ---- TMA bulk copy global -> shared with mbarrier completion (no multicast) ---------------
+// ---- TMA bulk copy global -> shared with mbarrier completion, one CTA as target ---------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -380,13 +380,27 @@ class DFloat11Model:
         pin_memory: bool = True,
         from_single_file: bool = False,
         pattern_dict: Optional[Dict[str, List[str]]] = None,
+        *,
+        tp_size: int = 1,
+        tp_rank: int = 0,
+        tp_group=None,
         **kwargs,
     ):
         """Same arguments and behaviour as the reference's ``from_pretrained`` (dfloat11.py:343-464):
         resolve the path, build the model skeleton (or take ``bfloat16_model``), read
         ``dfloat11_config``, load and arm the compressed units, place the model on ``device``
-        or spread whole units over the visible GPUs."""
+        or spread whole units over the visible GPUs.
+
+        ``tp_size`` / ``tp_rank`` / ``tp_group`` (keyword-only, not in the reference) select the
+        partitioned mode of ``dfloat11_b200.tp``: the directory must have been written by
+        ``compress_model_tp`` with the same ``tp_size``; this rank loads ``rank{r}-of-{T}/``,
+        its Linear layers take the shard shapes and row-parallel layers all-reduce over
+        ``tp_group``."""
         path = _resolve_path(dfloat11_model_name_or_path, from_single_file)
+        if tp_size > 1:
+            from .tp import rank_directory
+            if os.path.isdir(rank_directory(path, tp_size, tp_rank)):
+                path = rank_directory(path, tp_size, tp_rank)
 
         if bfloat16_model is not None:
             if from_single_file:
@@ -419,6 +433,10 @@ class DFloat11Model:
         else:
             raise AttributeError('"dfloat11_config" not found: it is expected to be found in the config file or '
                                  "passed as an argument.")
+
+        if tp_size > 1:
+            from .tp import apply_tensor_parallel
+            apply_tensor_parallel(model, dfloat11_config["pattern_dict"], tp_size, tp_rank, group=tp_group)
 
         load_and_replace_tensors(model, path, dfloat11_config, cpu_offload=cpu_offload,
                                  cpu_offload_blocks=cpu_offload_blocks, pin_memory=pin_memory,
