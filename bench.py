@@ -46,7 +46,11 @@ QWEN3_8B = dict(name="qwen3-8b-shape", layers=36, hidden=4096, kv=1024, inter=12
 LLAMA_8B = dict(name="llama3.1-8b-shape", layers=32, hidden=4096, kv=1024, inter=14336, vocab=128256)
 SMALL = dict(name="small-smoke", layers=2, hidden=1024, kv=256, inter=3072, vocab=8192)
 ONE_BLOCK = dict(name="one-llama-block", layers=1, hidden=4096, kv=1024, inter=14336, vocab=0)
-WORKLOADS = {"qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "small": SMALL, "block": ONE_BLOCK}
+# Llama-3.1-405B shapes, tensor-parallel over the ranks of the job: every rank holds 1/T of each
+# block's seven matrices as one unit and decodes only that; two activation all-reduces per layer.
+LLAMA_405B_TP = dict(name="llama3.1-405b-shape-tp", layers=126, hidden=16384, kv=1024, inter=53248, vocab=0, tp=True)
+WORKLOADS = {"qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "small": SMALL, "block": ONE_BLOCK,
+             "llama-405b-tp": LLAMA_405B_TP}
 
 
 def block_shapes(cfg):
@@ -296,6 +300,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen3-8b", choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--batch", type=int, default=1, help="activation rows all-reduced per layer (TP workload)")
     ap.add_argument("--skip-extras", action="store_true", help="no CPU baseline / reference-kernel / e2e legs")
     ap.add_argument("--generation", action="store_true",
                     help="only: batch-1 greedy generation, DF11 vs uncompressed BF16, on the workload's model shape")
@@ -323,9 +328,23 @@ def main():
     t_setup = time.time()
     plan = unit_plan(cfg)
     units = []
-    for i, (name, n, std) in enumerate(plan):
-        keep = (name == "layers.0" and rank == 0)   # the first transformer block also feeds the CPU baseline
-        units.append(make_unit(n, std, seed=1000 * (1 + rank) + i, device=device, keep_host=keep))
+    activations = None
+    if cfg.get("tp"):
+        # One block-shard per rank (1/world of the block's elements; shards of i.i.d. weights are
+        # i.i.d.), compressed once and cloned for the other layers: same traffic, distinct
+        # allocations, far larger than L2.  As many of the 126 layers as fit in 150 GB.
+        n_shard = plan[0][1] // world
+        first = make_unit(n_shard, 0.02, seed=1000 * (1 + rank), device=device, keep_host=(rank == 0))
+        per_layer = first["n_bytes"] + first["n_elements"] + first["n_elements"] // 7
+        layers = int(min(cfg["layers"], (150e9 - 2 * n_shard) // per_layer))
+        units = [first] + [dict(first, enc=first["enc"].clone(), sm=first["sm"].clone(),
+                                pos=first["pos"].clone(), gaps=first["gaps"].clone()) for _ in range(layers - 1)]
+        plan = [(f"layers.{i}", n_shard, 0.02) for i in range(layers)]
+        activations = torch.zeros(args.batch, cfg["hidden"], dtype=torch.bfloat16, device=device)
+    else:
+        for i, (name, n, std) in enumerate(plan):
+            keep = (name == "layers.0" and rank == 0)   # the first transformer block also feeds the CPU baseline
+            units.append(make_unit(n, std, seed=1000 * (1 + rank) + i, device=device, keep_host=keep))
     scratch = torch.empty(max(u["n_elements"] for u in units), dtype=torch.bfloat16, device=device)
     status = torch.zeros(1, dtype=torch.int32, device=device)
     for u in units:   # once per unit, at load time
@@ -342,6 +361,10 @@ def main():
             else:
                 ops.decode(u["luts"], u["enc"], u["sm"], u["pos"], u["gaps"], out=out,
                            max_block_elems=u["widest"], status=status)
+            if activations is not None and world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(activations)       # after o_proj
+                dist.all_reduce(activations)       # after down_proj
 
     # parity inside the bench: every unit's decode must reproduce its original checksum
     for u in units:
@@ -397,6 +420,9 @@ def main():
             "algorithmic_bytes_per_step": step_bytes, "bytes_per_element": round(step_bytes / step_elems, 4),
             "path": "df11_decode_prepared", "l2": "inputs larger than L2 (every unit >= 600 MB of traffic)",
             "per_gpu_GBps": round(value / world, 1), "setup_s": round(setup_s, 1),
+            **({"parallelism": f"tp{world}", "layers_resident": len(units), "all_reduces_per_step": 2 * len(units),
+                "all_reduce_shape": [args.batch, cfg["hidden"]],
+                "note": "one block-shard per rank compressed once and cloned per layer"} if cfg.get("tp") else {}),
         },
         "gpu_launches": len(units) * args.steps,
         "two_pass": {"path": "df11_decode", "ms_per_step": round(ms_two_pass, 4),
