@@ -74,6 +74,10 @@ struct Params {
     int64_t n_elements;
     int64_t n_blocks;
     int64_t n_chunks;          // ceil(number of groups / 32)
+    const int64_t *rows;       // row-wise decode: the rows to produce, else null
+    uint32_t chunks_per_row;   // row-wise decode: 512-element chunks per row
+    uint32_t n_tasks;          // row-wise decode: rows wanted * chunks_per_row
+    uint32_t n_rows_total;     // row-wise decode: rows the unit holds
     int n_luts;
     int ept;          // elements per seek point (16 or 32)
     int stage_bytes;  // shared staging area (and sign/mantissa tile), multiple of 16
@@ -376,7 +380,7 @@ __device__ __forceinline__ void probe_loop(uint32_t &acc, uint32_t &q, Exp16 &E,
 // contiguous run of 32*EPT outputs; a thread decodes its group 16 codes at a time.
 // Shared memory: the decode table and `luts` (for the rare full walk).
 // ---------------------------------------------------------------------------------------
-template <int K, int EPT>
+template <int K, int EPT, bool ROWS>
 __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_kernel(const Params p)
 {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -426,14 +430,27 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
         w2 = __funnelshift_l(d, c, bit);
     };
 
-    const uint32_t n_chunks = (uint32_t)p.n_chunks;
+    // A task is one chunk of 32 groups.  Whole-unit decode: task t is chunk t and writes where it
+    // reads.  Row-wise decode (ROWS): task t is chunk t % chunks_per_row of row rows[t / chunks_per_row]
+    // and writes to the t-th chunk of the output.
+    const uint32_t n_tasks = ROWS ? p.n_tasks : (uint32_t)p.n_chunks;
     const uint32_t n_elements = (uint32_t)p.n_elements;  // the host side rejects units too close to 2^32
     const uint32_t warps = gridDim.x * (kFastThreads / 32);
+    auto chunk_of = [&](uint32_t task) -> uint32_t {
+        if (!ROWS) return task;
+        const uint32_t r = task / p.chunks_per_row;
+        int64_t row = __ldg(p.rows + r);
+        if (row < 0 || row >= (int64_t)p.n_rows_total) {
+            bad |= DF11_STATUS_BAD_POSITIONS;  // an index outside the table: decode row 0 instead
+            row = 0;
+        }
+        return (uint32_t)row * p.chunks_per_row + (task - r * p.chunks_per_row);
+    };
 
     // What a task needs before it can run: where its first code starts, the stream words
     // there and its first sixteen sign/mantissa bytes.  Loaded one task ahead.
     struct Inputs {
-        uint32_t wi, bit;
+        uint32_t wi, bit, chunk;
         uint4 words, sm;
     };
     // Stage 1 of the pipeline: the raw seek point of a chunk (16 low bits per group, the high
@@ -447,6 +464,7 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
         if (lo < lo0) lo += 65536u;
         in.wi = (hi << 11) + (lo >> 5);  // (hi << 16 | lo) >> 5
         in.bit = lo & 31u;
+        in.chunk = chunk;
         const uint32_t first = (chunk * 32u + lane) * EPT;
         if (first < n_elements) {
             load_words(in.wi, in.words);
@@ -454,24 +472,33 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
         }
     };
 
-    uint32_t chunk = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
-    Inputs cur = {0, 0, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-    uint32_t lo_next = 0, hi_next = 0;
-    if (chunk < n_chunks) {
+    uint32_t task = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
+    Inputs cur = {0, 0, 0, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    uint32_t lo_next = 0, hi_next = 0, chunk_next = 0;
+    if (task < n_tasks) {
         uint32_t lo, hi;
+        const uint32_t chunk = chunk_of(task);
         load_seek(chunk, lo, hi);
         issue_inputs(chunk, lo, hi, cur);
-        if (chunk + warps < n_chunks) load_seek(chunk + warps, lo_next, hi_next);
+        if (task + warps < n_tasks) {
+            chunk_next = chunk_of(task + warps);
+            load_seek(chunk_next, lo_next, hi_next);
+        }
     }
-    for (; chunk < n_chunks; chunk += warps) {
+    for (; task < n_tasks; task += warps) {
         // keep the pipeline full: inputs of the next task, seek point of the one after it
-        Inputs nxt = {0, 0, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-        if (chunk + warps < n_chunks) {
-            issue_inputs(chunk + warps, lo_next, hi_next, nxt);
-            if (chunk + 2u * warps < n_chunks) load_seek(chunk + 2u * warps, lo_next, hi_next);
+        Inputs nxt = {0, 0, 0, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        if (task + warps < n_tasks) {
+            issue_inputs(chunk_next, lo_next, hi_next, nxt);
+            if (task + 2u * warps < n_tasks) {
+                chunk_next = chunk_of(task + 2u * warps);
+                load_seek(chunk_next, lo_next, hi_next);
+            }
         }
 
-        uint32_t first = (chunk * 32u + lane) * EPT;  // my next output element
+        uint32_t first = (cur.chunk * 32u + lane) * EPT;  // the element my next code decodes to
+        // where it goes: its own place, or (row-wise) the matching place of the gathered output
+        const uint32_t shift = ROWS ? (task * 32u + lane) * EPT - first : 0u;
         uint32_t wi = cur.wi, bit = cur.bit;
         uint32_t acc = 0, q = 0;  // acc: see kFastEscape; q = pending exponents
 #pragma unroll
@@ -541,13 +568,14 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
                 df11_merge4(E.e1, m.y, &r0.z, &r0.w);
                 df11_merge4(E.e2, m.z, &r1.x, &r1.y);
                 df11_merge4(E.e3, m.w, &r1.z, &r1.w);
-                uint4 *dst = reinterpret_cast<uint4 *>(p.out + first);
+                uint4 *dst = reinterpret_cast<uint4 *>(p.out + (first + shift));
                 dst[0] = r0;
                 dst[1] = r1;
             } else {  // the last, partial piece of the unit, or unaligned tensors
                 const uint32_t e[4] = {E.e0, E.e1, E.e2, E.e3};
                 for (uint32_t k = 0; k < 16u && first + k < n_elements; ++k)
-                    p.out[first + k] = df11_merge1((e[k >> 2] >> (8u * (k & 3u))) & 255u, __ldg(p.sm + first + k));
+                    p.out[first + shift + k] =
+                        df11_merge1((e[k >> 2] >> (8u * (k & 3u))) & 255u, __ldg(p.sm + first + k));
             }
         }
         cur = nxt;
@@ -769,7 +797,7 @@ struct DeviceInfo {
 };
 std::mutex g_mutex;
 DeviceInfo g_devices[64];
-bool g_attr_set[64][4] = {};
+bool g_attr_set[64][6] = {};
 
 struct DeviceGuard {
     int prev = -1;
@@ -1026,10 +1054,56 @@ extern "C" int df11_decode_prepared(const void *luts, const void *codes, const v
     const int64_t cta_items = (a.n_chunks + kFastThreads / 32 - 1) / (kFastThreads / 32);
     if (ept == 32) {
         const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
-        return launch(df11_fast_kernel<kFastTableBits, 32>, kFastThreads, 3, smem, cta_items, p, device, (cudaStream_t)stream);
+        return launch(df11_fast_kernel<kFastTableBits, 32, false>, kFastThreads, 3, smem, cta_items, p, device, (cudaStream_t)stream);
     }
     const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
-    return launch(df11_fast_kernel<kFastTableBits, 16>, kFastThreads, 2, smem, cta_items, p, device, (cudaStream_t)stream);
+    return launch(df11_fast_kernel<kFastTableBits, 16, false>, kFastThreads, 2, smem, cta_items, p, device, (cudaStream_t)stream);
+}
+
+extern "C" int df11_decode_rows_prepared(const void *luts, const void *codes, const void *sign_mantissa,
+                                         const void *aux, const void *rows, int64_t n_rows, int64_t row_elements,
+                                         void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                                         void *status, int32_t device, void *stream)
+{
+    // output_positions and gaps are not read by the fast decoder; any non-null pointer passes the check
+    int rc = check_common(luts, codes, luts, luts, n_luts, n_bytes, n_elements);
+    if (rc != DF11_OK) return rc;
+    if (n_rows < 0 || row_elements <= 0) return df11_fail(DF11_ERR_BADARG, "bad row count or row length");
+    if (n_rows == 0 || n_bytes == 0 || n_elements == 0) return DF11_OK;
+    if (!sign_mantissa || !out_bf16 || !rows || !aux || ((uintptr_t)aux & 15))
+        return df11_fail(DF11_ERR_BADARG, "null tensor pointer or misaligned aux buffer");
+    if (n_elements > kMaxPreparedElements) return df11_fail(DF11_ERR_BADARG, "unit too large for the prepared form");
+    const int ept = elements_per_seek_point();
+    const int64_t chunk_elems = 32 * ept;
+    if (row_elements % chunk_elems || n_elements % row_elements)
+        return df11_fail(DF11_ERR_BADARG,
+                         "row-wise decode needs rows of a multiple of %lld elements that tile the unit exactly "
+                         "(row length %lld, unit %lld)",
+                         (long long)chunk_elems, (long long)row_elements, (long long)n_elements);
+    if (n_rows * (row_elements / chunk_elems) > 0x7FFFFFFFll || n_rows * row_elements > 0xFFFFFFFFll)
+        return df11_fail(DF11_ERR_BADARG, "too many rows for one call");
+    const AuxLayout a = aux_layout(n_elements, ept);
+    Params p = base_params(luts, codes, luts, luts, n_luts, n_bytes, n_elements, status);
+    p.sm = (const uint8_t *)sign_mantissa;
+    p.out = (uint16_t *)out_bf16;
+    p.table_g = (const Df11Entry *)aux;
+    p.sync_hi = (uint32_t *)((uint8_t *)aux + a.hi_off);
+    p.sync_lo = (uint16_t *)((uint8_t *)aux + a.lo_off);
+    p.n_chunks = a.n_chunks;
+    p.ept = ept;
+    p.rows = (const int64_t *)rows;
+    p.chunks_per_row = (uint32_t)(row_elements / chunk_elems);
+    p.n_tasks = (uint32_t)(n_rows * p.chunks_per_row);
+    p.n_rows_total = (uint32_t)(n_elements / row_elements);
+    p.sm_aligned = ((uintptr_t)sign_mantissa & 15) == 0;
+    p.out_aligned = ((uintptr_t)out_bf16 & 15) == 0;
+    const int64_t cta_items = ((int64_t)p.n_tasks + kFastThreads / 32 - 1) / (kFastThreads / 32);
+    const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
+    if (ept == 32)
+        return launch(df11_fast_kernel<kFastTableBits, 32, true>, kFastThreads, 5, smem, cta_items, p, device,
+                      (cudaStream_t)stream);
+    return launch(df11_fast_kernel<kFastTableBits, 16, true>, kFastThreads, 4, smem, cta_items, p, device,
+                  (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -172,6 +172,17 @@ def _inject_weights(module: nn.Module, reconstructed: torch.Tensor) -> None:
             sub_module.weight = weight.view(sub_module.out_features, sub_module.in_features)
 
 
+def _sparse_embedding(module: nn.Module, inputs, n_elements: int) -> bool:
+    """Whether this forward of an ``nn.Embedding`` unit can decode just the looked-up rows."""
+    if not isinstance(module, nn.Embedding) or os.environ.get("DF11_SPARSE_EMBEDDING", "1") == "0":
+        return False
+    if not inputs or not isinstance(inputs[0], torch.Tensor) or inputs[0].is_floating_point():
+        return False
+    if module.max_norm is not None or module.embedding_dim % ops.chunk_elements():
+        return False
+    return 0 < inputs[0].numel() * module.embedding_dim < n_elements      # else the whole table is cheaper
+
+
 def get_hook(threads_per_block, bytes_per_thread):
     """Forward pre-hook that decompresses a unit's weights right before its forward
     (dfloat11.py:103-176).  The two arguments are the format constants; only 512 / 8 exist."""
@@ -180,7 +191,7 @@ def get_hook(threads_per_block, bytes_per_thread):
         raise ValueError("DF11 files are laid out for 512 threads per block and 8 bytes per thread "
                          f"(got {threads_per_block[0]} / {bytes_per_thread})")
 
-    def decode_hook(module, _):
+    def decode_hook(module, inputs):
         device = module.luts.device
         if device.type != "cuda":
             raise RuntimeError("DF11 weights can only be decompressed on a CUDA device; move the model to "
@@ -205,6 +216,19 @@ def get_hook(threads_per_block, bytes_per_thread):
                 # once per unit and device: decode table + seek points (derived data, never saved)
                 aux = ops.prepare(module.luts, encoded_exponent, module.output_positions, module.gaps, n_elements)
                 module.df11_aux = aux
+            if _sparse_embedding(module, inputs, n_elements):
+                # a lookup table: decompress only the rows that are asked for (the reference
+                # decodes the whole table on every forward, dfloat11.py:158-161) and look them
+                # up by their position in that small result
+                ids = inputs[0]
+                rows = ops.decode_rows_prepared(module.luts, encoded_exponent, sign_mantissa, aux,
+                                                ids.reshape(-1).to(torch.int64), module.embedding_dim,
+                                                out=TensorManager.allocate_bfloat16(
+                                                    device, ids.numel() * module.embedding_dim))
+                module.weight = rows
+                if stager is not None:
+                    stager.done(module)
+                return (torch.arange(ids.numel(), device=device).view(ids.shape),) + tuple(inputs[1:])
             ops.decode_prepared(module.luts, encoded_exponent, sign_mantissa, module.output_positions,
                                 module.gaps, aux, out=reconstructed, max_block_elems=widest)
         else:

@@ -98,3 +98,32 @@ def decode_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_man
         luts.shape[0], encoded_exponent.numel(), n_elements, int(max_block_elems),
         status.data_ptr() if status is not None else None, device.index, _stream(device)))
     return out
+
+
+def chunk_elements() -> int:
+    """Elements per independently decodable chunk of the prepared form (32 groups)."""
+    import os
+    return 32 * (32 if os.environ.get("DF11_EPT") == "32" else 16)
+
+
+def decode_rows_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_mantissa: torch.Tensor,
+                         aux: torch.Tensor, rows: torch.Tensor, row_elements: int,
+                         out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decompress only the given rows of a unit viewed as ``[n_elements / row_elements, row_elements]``.
+
+    ``rows`` is an int64 CUDA tensor; the result has one row per entry, in that order.  Needs the
+    buffer made by ``prepare`` and a row length that is a multiple of ``chunk_elements()``."""
+    device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, sign_mantissa=sign_mantissa,
+                           aux=aux, rows=rows, out=out, status=status)
+    if rows.dtype != torch.int64:
+        raise RuntimeError("`rows` must be an int64 tensor")
+    n_rows = rows.numel()
+    if out is None:
+        out = torch.empty(n_rows * row_elements, dtype=torch.bfloat16, device=device)
+    if out.dtype != torch.bfloat16 or out.numel() < n_rows * row_elements:
+        raise RuntimeError("`out` must be a bfloat16 tensor with at least n_rows * row_elements elements")
+    _lib.check(_lib.lib.df11_decode_rows_prepared(
+        luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(), aux.data_ptr(),
+        rows.data_ptr(), n_rows, int(row_elements), out.data_ptr(), luts.shape[0], encoded_exponent.numel(),
+        sign_mantissa.numel(), status.data_ptr() if status is not None else None, device.index, _stream(device)))
+    return out[:n_rows * row_elements].view(n_rows, row_elements)

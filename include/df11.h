@@ -111,6 +111,24 @@ int df11_decode_prepared(const void *luts, const void *codes, const void *sign_m
                          int32_t max_block_elems, void *status, int32_t device, void *stream);
 
 /*
+ * Row-wise decode for lookup tables (nn.Embedding): decompress only the rows that are
+ * looked up instead of the whole unit, which the reference decodes on every forward
+ * (dfloat11/dfloat11.py:158-161).  The seek points of the prepared form make any 512-element
+ * chunk of a unit decodable on its own.
+ *
+ *   aux           the buffer filled by df11_prepare for this unit
+ *   rows          device, int64 [n_rows]     row indices, in the order wanted; repeats allowed
+ *   row_elements  elements per row: a multiple of 512 that divides n_elements
+ *   out_bf16      device, uint16 [n_rows * row_elements]
+ * An index outside the table sets DF11_STATUS_BAD_POSITIONS and yields row 0.
+ * No counterpart in the reference.
+ */
+int df11_decode_rows_prepared(const void *luts, const void *codes, const void *sign_mantissa,
+                              const void *aux, const void *rows, int64_t n_rows,
+                              int64_t row_elements, void *out_bf16, int32_t n_luts, int64_t n_bytes,
+                              int64_t n_elements, void *status, int32_t device, void *stream);
+
+/*
  * Decode for callers that cannot allocate device memory at all and have nobody to do it
  * for them: code running inside a CUDA-graph capture or a stream callback, a plug-in
  * called from a serving loop whose memory pool is already carved up, a host runtime

@@ -273,3 +273,25 @@ def test_synthetic_distributions(case):
     assert st.item() == 0
     assert np.array_equal(_bits(out), w)
     assert np.array_equal(_bits(out2), w)
+
+
+def test_row_wise_decode_matches_rows_of_the_full_decode():
+    g = torch.Generator().manual_seed(31)
+    table = torch.randn(300, 1024, generator=g).to(torch.bfloat16)          # rows of two 512-element chunks
+    t, d, widest = _unit_from_weights([table.flatten()])
+    st = _status()
+    aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], table.numel(), status=st)
+    rows = torch.tensor([299, 0, 7, 7, 150, 298, 1], dtype=torch.int64, device=DEV)
+    got = ops.decode_rows_prepared(d["luts"], d["enc"], d["sm"], aux, rows, 1024, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert torch.equal(got.cpu().view(torch.int16), table[rows.cpu()].view(torch.int16))
+    # an index outside the table is flagged and decodes row 0 instead of reading elsewhere
+    bad = torch.tensor([5, 300, -1], dtype=torch.int64, device=DEV)
+    got = ops.decode_rows_prepared(d["luts"], d["enc"], d["sm"], aux, bad, 1024, status=st)
+    torch.cuda.synchronize()
+    assert st.item() & _lib.STATUS_BAD_POSITIONS
+    assert torch.equal(got[0].cpu().view(torch.int16), table[5].view(torch.int16))
+    assert torch.equal(got[1].cpu().view(torch.int16), table[0].view(torch.int16))
+    with pytest.raises(_lib.DF11Error):
+        ops.decode_rows_prepared(d["luts"], d["enc"], d["sm"], aux, rows, 1000)      # not a multiple of 512

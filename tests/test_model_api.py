@@ -221,3 +221,31 @@ def test_compress_model_self_check_and_single_file(tmp_path):
     x = torch.randn(5, 384, dtype=torch.bfloat16, device="cuda:0")
     with torch.no_grad():
         assert torch.equal(loaded(x), reference(x))
+
+
+@pytest.mark.gpu
+def test_embedding_unit_decodes_only_looked_up_rows(tmp_path, monkeypatch):
+    torch.manual_seed(5)
+    emb = nn.Embedding(2000, 512).to(torch.bfloat16)
+    reference = copy.deepcopy(emb).to("cuda:0")
+    holder = nn.Module()
+    holder.emb = emb
+    ref_holder = nn.Module()
+    df11.compress_model(holder, {r"emb": []}, str(tmp_path), save_single_file=True, check_correctness=True)
+    skeleton = nn.Module()
+    skeleton.emb = nn.Embedding(2000, 512).to(torch.bfloat16)
+    loaded = df11.DFloat11Model.from_single_file(os.path.join(str(tmp_path), "model.safetensors"), {r"emb": []},
+                                                 skeleton, device="cuda:0")
+    ids = torch.randint(0, 2000, (3, 9), device="cuda:0")
+    with torch.no_grad():
+        got = loaded.emb(ids)
+        assert loaded.emb.weight.shape == (27, 512)               # only the looked-up rows were decoded
+        assert torch.equal(got, reference(ids))
+        big = torch.randint(0, 2000, (4, 600), device="cuda:0")   # more lookups than rows: whole table
+        got = loaded.emb(big)
+        assert loaded.emb.weight.shape == (2000, 512)
+        assert torch.equal(got, reference(big))
+        monkeypatch.setenv("DF11_SPARSE_EMBEDDING", "0")
+        assert torch.equal(loaded.emb(ids), reference(ids))
+        assert loaded.emb.weight.shape == (2000, 512)
+    del ref_holder
