@@ -304,13 +304,29 @@ struct FastTables {
     __device__ __forceinline__ uint32_t lut(uint32_t i) const { return lds8(luts_addr + i); }
 };
 
-// Sixteen exponents of a group, four per word, lowest byte first.  A completed word enters
-// at e3 and pushes the others down, so after four completions e0..e3 are in order.
-struct Exp16 {
-    uint32_t e0, e1, e2, e3;
-    __device__ __forceinline__ void push(uint32_t w)
+// The exponents a thread has decoded, as a 20-byte shift register x0 (lowest) .. x4: every
+// table probe shifts it right by as many bytes as the entry has symbols and enters them at the
+// top, first symbol lowest.  After c codes (16 <= c <= 19: the last probe may run up to three
+// codes past the sixteenth) code k sits at byte 20 - c + k, so the sixteen wanted bytes are the
+// register shifted right by 20 - c bytes, and the c - 16 extra codes stay at the top of x4.
+struct ExpShift {
+    uint32_t x0, x1, x2, x3, x4;
+    __device__ __forceinline__ void push(uint32_t syms, uint32_t bits)  // bits = 8 * symbols, 0..32
     {
-        e0 = e1, e1 = e2, e2 = e3, e3 = w;
+        x0 = __funnelshift_rc(x0, x1, bits);
+        x1 = __funnelshift_rc(x1, x2, bits);
+        x2 = __funnelshift_rc(x2, x3, bits);
+        x3 = __funnelshift_rc(x3, x4, bits);
+        x4 = __funnelshift_rc(x4, syms, bits);
+    }
+    // the sixteen exponents, four per word, lowest byte first; acc as described below
+    __device__ __forceinline__ void take(uint32_t acc, uint32_t &e0, uint32_t &e1, uint32_t &e2, uint32_t &e3) const
+    {
+        const uint32_t bits = 160u - ((acc >> 16) & 0xFFu);  // 8 * (20 - codes done): 8..32
+        e0 = __funnelshift_rc(x0, x1, bits);
+        e1 = __funnelshift_rc(x1, x2, bits);
+        e2 = __funnelshift_rc(x2, x3, bits);
+        e3 = __funnelshift_rc(x3, x4, bits);
     }
 };
 
@@ -318,9 +334,9 @@ struct Exp16 {
 // 31), eight times the number of symbols in bits 16..23; an entry that needs the full walk is
 // kFastEscape alone.  The running state `acc` of a thread is the sum of the entries it used:
 //   bits 0..7   position in the window (64 and more: window used up)
-//   bits 16..23 8 * codes done (128: the sixteen codes of this pass are done)
-//   bit 28      an escape entry was met
-constexpr uint32_t kFastEscape = 1u << 28;
+//   bit 15      an escape entry was met
+//   bits 16..23 8 * codes done (128 and more: the sixteen codes of this pass are done)
+constexpr uint32_t kFastEscape = 1u << 15;
 constexpr uint32_t kFastDone = 128u << 16;
 constexpr uint32_t kFastLeave = kFastEscape | kFastDone | 64u;
 
@@ -332,46 +348,39 @@ __host__ __device__ constexpr uint32_t fast_meta(uint32_t meta)
 
 // The probe loop of the fast decoder (the device form of df11_decode_group's inner loop,
 // df11_common.h, for 16 codes).  The 96-bit window w0:w1:w2 is kept shifted so that the next
-// code starts at its top bit.  One pass: index the table with the top K bits, append up to
-// four exponents to the pending word q, push q into E when a fourth exponent completes a
-// word, shift the window by the bits consumed.  Shift amounts are taken modulo 32 by the
-// funnel shifter, so `acc >> 16` (8 * codes done) and the entry word itself serve as such.
-// Table index and address are formed with multiply-add instructions to keep them off the
-// integer ALU pipe, which is the busiest unit of this kernel.
+// code starts at its top bit.  One pass: index the table with the top K bits, shift the
+// entry's symbols into the exponent register, shift the window by the bits consumed.  The
+// window shifts take their amount modulo 32 from the entry word itself; the register shift
+// clamps at 32, which is what four symbols need.  Table index, address and the symbol count
+// are formed with multiply instructions to keep them off the integer ALU pipe, which is the
+// busiest unit of this kernel.
 template <int K>
-__device__ __forceinline__ void probe_loop(uint32_t &acc, uint32_t &q, Exp16 &E, uint32_t &w0, uint32_t &w1,
-                                           uint32_t &w2, uint32_t dec_addr)
+__device__ __forceinline__ void probe_loop(uint32_t &acc, ExpShift &X, uint32_t &w0, uint32_t &w1, uint32_t &w2,
+                                           uint32_t dec_addr)
 {
     asm volatile(
         "{\n\t"
-        ".reg .pred pc, pl;\n\t"
-        ".reg .b32 t, i, m, s, sh, t2, lo, hi, nacc, c;\n\t"
+        ".reg .pred pl;\n\t"
+        ".reg .b32 t, i, m, s, n8;\n\t"
         "DF11_PROBE:\n\t"
         "mul.hi.u32 i, %6, %10;\n\t"             // top K bits of the window
         "mad.lo.u32 i, i, 8, %9;\n\t"
         "ld.shared.v2.u32 {m, s}, [i];\n\t"
-        "shr.u32 sh, %0, 16;\n\t"
-        "shf.l.wrap.b32 t2, 0, s, sh;\n\t"       // s << (8 * codes done mod 32)
-        "shf.l.wrap.b32 hi, s, 0, sh;\n\t"       // the exponents that do not fit the word
-        "or.b32 lo, %1, t2;\n\t"
+        "mul.hi.u32 n8, m, 65536;\n\t"           // 8 * symbols of the entry
+        "shf.r.clamp.b32 %1, %1, %2, n8;\n\t"
+        "shf.r.clamp.b32 %2, %2, %3, n8;\n\t"
+        "shf.r.clamp.b32 %3, %3, %4, n8;\n\t"
+        "shf.r.clamp.b32 %4, %4, %5, n8;\n\t"
+        "shf.r.clamp.b32 %5, %5, s, n8;\n\t"
         "shf.l.wrap.b32 %6, %7, %6, m;\n\t"      // window <<= bits consumed
         "shf.l.wrap.b32 %7, %8, %7, m;\n\t"
         "shf.l.wrap.b32 %8, 0, %8, m;\n\t"
-        "add.u32 nacc, %0, m;\n\t"
-        "xor.b32 c, nacc, %0;\n\t"
-        "and.b32 c, c, 0x00E00000;\n\t"
-        "setp.ne.u32 pc, c, 0;\n\t"              // the count crossed a multiple of four
-        "@pc mov.b32 %2, %3;\n\t"
-        "@pc mov.b32 %3, %4;\n\t"
-        "@pc mov.b32 %4, %5;\n\t"
-        "@pc mov.b32 %5, lo;\n\t"
-        "selp.b32 %1, hi, lo, pc;\n\t"
-        "mov.u32 %0, nacc;\n\t"
-        "and.b32 t, nacc, %11;\n\t"
+        "add.u32 %0, %0, m;\n\t"
+        "and.b32 t, %0, %11;\n\t"
         "setp.eq.u32 pl, t, 0;\n\t"
         "@pl bra DF11_PROBE;\n\t"
         "}"
-        : "+r"(acc), "+r"(q), "+r"(E.e0), "+r"(E.e1), "+r"(E.e2), "+r"(E.e3), "+r"(w0), "+r"(w1), "+r"(w2)
+        : "+r"(acc), "+r"(X.x0), "+r"(X.x1), "+r"(X.x2), "+r"(X.x3), "+r"(X.x4), "+r"(w0), "+r"(w1), "+r"(w2)
         : "r"(dec_addr), "n"(1 << K), "n"(kFastLeave));
 }
 
@@ -500,14 +509,15 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
         // where it goes: its own place, or (row-wise) the matching place of the gathered output
         const uint32_t shift = ROWS ? (task * 32u + lane) * EPT - first : 0u;
         uint32_t wi = cur.wi, bit = cur.bit;
-        uint32_t acc = 0, q = 0;  // acc: see kFastEscape; q = pending exponents
+        uint32_t acc = 0;  // see kFastEscape
+        ExpShift X = {0, 0, 0, 0, 0};
 #pragma unroll
         for (int part = 0; part < EPT / 16; ++part, first += 16u) {
             if (first >= n_elements) break;
             const bool whole = n_elements - first >= 16u;
             uint4 m = cur.sm;
             // 96-bit window whose top bit is my next code.  A later part continues where the
-            // previous one stopped: codes it decoded beyond its sixteenth are already in q.
+            // previous one stopped: codes it decoded beyond its sixteenth are at the top of X.
             uint32_t w0, w1, w2;
             if (part == 0) {
                 make_window(cur.words, bit, w0, w1, w2);
@@ -521,9 +531,8 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
                 load_words(wi, r);
                 make_window(r, bit, w0, w1, w2);
             }
-            Exp16 E = {0, 0, 0, 0};
             for (;;) {
-                if ((acc & kFastLeave) == 0u) probe_loop<K>(acc, q, E, w0, w1, w2, tab.dec_addr);
+                if ((acc & kFastLeave) == 0u) probe_loop<K>(acc, X, w0, w1, w2, tab.dec_addr);
                 if ((acc & (kFastEscape | 64u)) == 0u) break;  // 16 codes done, nothing special
                 if (acc & kFastEscape) {
                     // the table could not resolve this code from K bits: full walk for one symbol
@@ -532,15 +541,8 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
                     int tbad = 0;
                     const uint32_t sym = df11_walk_m(tab, p.n_luts, w0, &len, &tbad);
                     if (tbad) bad |= DF11_STATUS_BAD_TABLE;
-                    const uint32_t word_now = q | (sym << ((acc >> 16) & 24u));
-                    const uint32_t nacc = acc + (len | (8u << 16));
-                    if ((nacc ^ acc) & 0x00E00000u) {
-                        E.push(word_now);
-                        q = 0;
-                    } else {
-                        q = word_now;
-                    }
-                    acc = nacc;
+                    X.push(sym, 8u);
+                    acc += len | (8u << 16);
                     if (len < 32u) {  // window <<= len
                         w0 = __funnelshift_l(w1, w0, len);
                         w1 = __funnelshift_l(w2, w1, len);
@@ -562,17 +564,19 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
                 }
             }
 
+            uint32_t e0, e1, e2, e3;
+            X.take(acc, e0, e1, e2, e3);
             if (whole && vec) {
                 uint4 r0, r1;
-                df11_merge4(E.e0, m.x, &r0.x, &r0.y);
-                df11_merge4(E.e1, m.y, &r0.z, &r0.w);
-                df11_merge4(E.e2, m.z, &r1.x, &r1.y);
-                df11_merge4(E.e3, m.w, &r1.z, &r1.w);
+                df11_merge4(e0, m.x, &r0.x, &r0.y);
+                df11_merge4(e1, m.y, &r0.z, &r0.w);
+                df11_merge4(e2, m.z, &r1.x, &r1.y);
+                df11_merge4(e3, m.w, &r1.z, &r1.w);
                 uint4 *dst = reinterpret_cast<uint4 *>(p.out + (first + shift));
                 dst[0] = r0;
                 dst[1] = r1;
             } else {  // the last, partial piece of the unit, or unaligned tensors
-                const uint32_t e[4] = {E.e0, E.e1, E.e2, E.e3};
+                const uint32_t e[4] = {e0, e1, e2, e3};
                 for (uint32_t k = 0; k < 16u && first + k < n_elements; ++k)
                     p.out[first + shift + k] =
                         df11_merge1((e[k >> 2] >> (8u * (k & 3u))) & 255u, __ldg(p.sm + first + k));
