@@ -411,6 +411,7 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
     const uint32_t *codes32 = reinterpret_cast<const uint32_t *>(p.codes);
     // words that can be loaded whole; 0 sends every word of an unaligned stream the slow way
     const uint32_t n_words = (p.codes_aligned & 4) ? (uint32_t)(p.n_bytes >> 2) : 0u;
+    const uint32_t n_whole = n_words > 3u ? n_words - 3u : 0u;  // word indices with three whole words after them
     const bool vec = p.sm_aligned && p.out_aligned;  // 16-byte loads and stores allowed
     int bad = 0;
 
@@ -424,7 +425,7 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
         r = make_uint4(v[0], v[1], v[2], v[3]);
     };
     auto load_words = [&](uint32_t wi, uint4 &r) {
-        if (wi + 3u < n_words) {  // the common case: four whole words, one bounds check
+        if (wi < n_whole) {  // the common case: four whole words, one bounds check
             const uint32_t *src = codes32 + wi;
             r = make_uint4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3));
         } else {
@@ -482,6 +483,100 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
     };
 
     uint32_t task = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
+
+    // Lean loop: whole-unit decode of aligned tensors, for every chunk but the last two.  Such a
+    // chunk is full, and at least 512 further codes (16 stream words or more) follow it, so no
+    // load of its tasks needs a bounds check; a word index is only clamped (a foreign
+    // auxiliary buffer gives wrong output, never a fault).  Indices of the tasks fetched ahead
+    // are clamped to the last lean chunk instead of being branched around, and the loop is
+    // unrolled twice so that the two input sets swap roles without register moves.
+    if (EPT == 16 && !ROWS && vec && n_words >= 4u && p.n_chunks > 2) {
+        const uint32_t n_lean = (uint32_t)p.n_chunks - 2u, last_lean = n_lean - 1u;
+        const uint32_t last_wi = n_words - 4u;
+        struct Lean {
+            uint32_t wi, bit;
+            uint4 words, sm;
+        };
+        uint32_t lo_n, hi_n;  // seek point of the task after the next
+        auto lean_seek = [&](uint32_t t) {
+            const uint32_t chunk = min(t, last_lean);
+            lo_n = (uint32_t)__ldg(p.sync_lo + chunk * 32u + lane);
+            hi_n = __ldg(p.sync_hi + chunk);
+        };
+        auto lean_issue = [&](uint32_t t, Lean &in) {  // uses the seek point fetched for task t
+            const uint32_t chunk = min(t, last_lean);
+            uint32_t lo = lo_n;
+            const uint32_t lo0 = __shfl_sync(0xffffffffu, lo, 0);
+            if (lo < lo0) lo += 65536u;
+            in.wi = min((hi_n << 11) + (lo >> 5), last_wi);
+            in.bit = lo & 31u;
+            const uint32_t *src = codes32 + in.wi;
+            in.words = make_uint4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3));
+            in.sm = __ldg(reinterpret_cast<const uint4 *>(p.sm) + (chunk * 32u + lane));
+        };
+        ExpShift X = {0, 0, 0, 0, 0};
+        auto lean_task = [&](uint32_t t, const Lean &cur, Lean &nxt) {
+            lean_issue(t + warps, nxt);
+            lean_seek(t + 2u * warps);
+            uint32_t wi = cur.wi, bit = cur.bit, acc = 0, w0, w1, w2;
+            make_window(cur.words, bit, w0, w1, w2);
+            for (;;) {
+                probe_loop<K>(acc, X, w0, w1, w2, tab.dec_addr);
+                if (acc & kFastDone) break;  // the usual exit
+                if (acc & kFastEscape) {     // full walk for one symbol
+                    acc -= kFastEscape;
+                    uint32_t len;
+                    int tbad = 0;
+                    const uint32_t sym = df11_walk_m(tab, p.n_luts, w0, &len, &tbad);
+                    if (tbad) bad |= DF11_STATUS_BAD_TABLE;
+                    X.push(sym, 8u);
+                    acc += len | (8u << 16);
+                    if (len < 32u) {
+                        w0 = __funnelshift_l(w1, w0, len);
+                        w1 = __funnelshift_l(w2, w1, len);
+                        w2 <<= len;
+                    } else {
+                        w0 = w1, w1 = w2, w2 = 0;
+                    }
+                    if (acc & kFastDone) break;
+                }
+                if (acc & 64u) {  // position 64..127: reload the window where the position has got to
+                    const uint32_t at = bit + (acc & 0x7Fu);
+                    wi = min(wi + (at >> 5), last_wi);
+                    bit = at & 31u;
+                    const uint32_t *src = codes32 + wi;
+                    make_window(make_uint4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3)), bit, w0, w1, w2);
+                    acc &= ~0xFFu;
+                }
+            }
+            uint32_t e0, e1, e2, e3;
+            X.take(acc, e0, e1, e2, e3);
+            uint4 r0, r1;
+            df11_merge4(e0, cur.sm.x, &r0.x, &r0.y);
+            df11_merge4(e1, cur.sm.y, &r0.z, &r0.w);
+            df11_merge4(e2, cur.sm.z, &r1.x, &r1.y);
+            df11_merge4(e3, cur.sm.w, &r1.z, &r1.w);
+            uint4 *dst = reinterpret_cast<uint4 *>(p.out) + 2u * (t * 32u + lane);
+            dst[0] = r0;
+            dst[1] = r1;
+        };
+        if (task < n_lean) {
+            Lean a, b;
+            lean_seek(task);
+            lean_issue(task, a);
+            lean_seek(task + warps);
+            for (;;) {
+                lean_task(task, a, b);
+                task += warps;
+                if (task >= n_lean) break;
+                lean_task(task, b, a);
+                task += warps;
+                if (task >= n_lean) break;
+            }
+        }
+    }
+
+    // General loop: what the lean loop left (the last chunks), row-wise decode, unaligned tensors.
     Inputs cur = {0, 0, 0, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
     uint32_t lo_next = 0, hi_next = 0, chunk_next = 0;
     if (task < n_tasks) {

@@ -295,3 +295,52 @@ def test_row_wise_decode_matches_rows_of_the_full_decode():
     assert torch.equal(got[1].cpu().view(torch.int16), table[0].view(torch.int16))
     with pytest.raises(_lib.DF11Error):
         ops.decode_rows_prepared(d["luts"], d["enc"], d["sm"], aux, rows, 1000)      # not a multiple of 512
+
+
+@pytest.mark.parametrize("n", [1025, 1536, 1537, 2048, 2049, 2560, 5000, 16 * 4096 + 3])
+@pytest.mark.parametrize("case", ["one_bit_codes", "gaussian"])
+def test_prepared_decode_around_the_last_chunks(n, case):
+    """Units of three and more 512-element chunks: all but the last two take the decoder's
+    unchecked inner loop, the last two its general loop; both must give the oracle's bits."""
+    rng = np.random.default_rng(n)
+    if case == "one_bit_codes":
+        e = (rng.random(n) < 0.97).astype(np.uint16) * 5 + 90
+    else:
+        e = np.clip(np.rint(rng.normal(120, 2.5, size=n)), 1, 239).astype(np.uint16)
+    sm = rng.integers(0, 256, size=n).astype(np.uint16)
+    w = (((sm & 0x80) << 8) | (e << 7) | (sm & 0x7F)).astype(np.uint16)
+    t, d, widest = _unit_from_weights([torch.from_numpy(w.view(np.int16)).view(torch.bfloat16)])
+    want = oracle.decode_c(t["luts"].numpy(), t["encoded_exponent"].numpy(), t["sign_mantissa"].numpy(),
+                           t["output_positions"].numpy(), t["gaps"].numpy())
+    st = _status()
+    aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], n, status=st)
+    buf = torch.full((n + 64,), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.decode_prepared(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], aux, out=buf[:n], status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert np.array_equal(_bits(buf[:n]), want)
+    assert np.array_equal(want, w)
+    assert torch.all(buf[n:] == 7.0)
+
+
+def test_prepared_decode_of_inconsistent_inputs_stays_in_bounds():
+    """A stream of random bytes, and seek points that belong to another stream: the output is
+    meaningless, but every read and write stays inside the tensors and the launch returns."""
+    rng = np.random.default_rng(5)
+    n = 300_000
+    e = np.clip(np.rint(rng.normal(120, 2.5, size=n)), 1, 239).astype(np.uint16)
+    sm = rng.integers(0, 256, size=n).astype(np.uint16)
+    w = (((sm & 0x80) << 8) | (e << 7) | (sm & 0x7F)).astype(np.uint16)
+    t, d, widest = _unit_from_weights([torch.from_numpy(w.view(np.int16)).view(torch.bfloat16)])
+    good_aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], n)
+    noise = torch.randint(0, 256, (d["enc"].numel(),), dtype=torch.uint8, device=DEV)
+    st = _status()
+    for stream, aux in ((noise, good_aux),
+                        (noise, ops.prepare(d["luts"], noise, d["pos"], d["gaps"], n, status=st)),
+                        (d["enc"], torch.randint(0, 256, (good_aux.numel(),), dtype=torch.uint8, device=DEV))):
+        aux = aux.clone()
+        aux[:32768] = good_aux[:32768]                       # the decode table stays a valid one
+        buf = torch.full((n + 64,), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops.decode_prepared(d["luts"], stream, d["sm"], d["pos"], d["gaps"], aux, out=buf[:n], status=st)
+        torch.cuda.synchronize()
+        assert torch.all(buf[n:] == 7.0)
