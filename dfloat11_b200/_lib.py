@@ -29,6 +29,11 @@ SIGNATURES = {
     "df11_aux_bytes": (c_int64, [c_int64, c_int64]),
     "df11_prepare": (c_int32, [c_void_p] * 5 + [c_int64, c_int32, c_int64, c_int64, c_void_p, c_int32, c_void_p]),
     "df11_decode_prepared": (c_int32, [c_void_p] * 7 + [c_int32, c_int64, c_int64, c_int32, c_void_p, c_int32, c_void_p]),
+    "df11_decode_prepared_shared": (c_int32, [c_void_p] * 7 + [c_int32, c_int64, c_int64, c_int32, c_void_p, c_int32,
+                                              c_void_p]),
+    "df11_gemv_partials_bytes": (c_int64, [c_int64, c_int64, c_int32]),
+    "df11_gemv_prepared": (c_int32, [c_void_p] * 8 + [c_int64, c_int64, c_int64, c_int32, c_int32, c_int64, c_int64,
+                                     c_void_p, c_int32, c_void_p]),
     "df11_decode_rows_prepared": (c_int32, [c_void_p] * 5 + [c_int64, c_int64, c_void_p, c_int32, c_int64, c_int64,
                                             c_void_p, c_int32, c_void_p]),
     "df11_decode_static": (c_int32, [c_void_p] * 6 + [c_int32, c_int64, c_int64, c_void_p, c_int32, c_void_p]),

@@ -51,6 +51,9 @@ constexpr int kWarps = kThreads / 32;
 #ifndef DF11_FAST_MIN_CTAS
 #define DF11_FAST_MIN_CTAS 4
 #endif
+#ifndef DF11_GEMV_MIN_CTAS
+#define DF11_GEMV_MIN_CTAS 3
+#endif
 constexpr int kTableBits = DF11_TABLE_BITS;           // K of the self-contained decoder and the seek-point pass
 constexpr int kFastTableBits = DF11_FAST_TABLE_BITS;  // K of the fast decoder (its table is larger, its CTAs smaller)
 
@@ -384,6 +387,131 @@ __device__ __forceinline__ void probe_loop(uint32_t &acc, ExpShift &X, uint32_t 
         : "r"(dec_addr), "n"(1 << K), "n"(kFastLeave));
 }
 
+// Four raw stream words starting at word `wi`, byte by byte: for the end of the stream (bytes past
+// it read as 0) and for any word index, however wrong.
+__device__ __noinline__ uint4 stream_words_slow(const uint8_t *codes, int64_t n_bytes, uint32_t wi)
+{
+    uint32_t v[4] = {0, 0, 0, 0};
+    const int64_t off = (int64_t)wi * 4;
+    for (int k = 0; k < 16; ++k)
+        if (off + k < n_bytes) v[k >> 2] |= (uint32_t)__ldg(codes + off + k) << (8 * (k & 3));
+    return make_uint4(v[0], v[1], v[2], v[3]);
+}
+
+// The 96-bit window four raw words give once byte-swapped and shifted left by `bit`.
+__device__ __forceinline__ void stream_window(const uint4 &r, uint32_t bit, uint32_t &w0, uint32_t &w1, uint32_t &w2)
+{
+    const uint32_t a = __byte_perm(r.x, 0, 0x0123), b = __byte_perm(r.y, 0, 0x0123);
+    const uint32_t c = __byte_perm(r.z, 0, 0x0123), d = __byte_perm(r.w, 0, 0x0123);
+    w0 = __funnelshift_l(b, a, bit);
+    w1 = __funnelshift_l(c, b, bit);
+    w2 = __funnelshift_l(d, c, bit);
+}
+
+// The inner loop of the fast decoder for tasks that are known to be whole chunks of 512
+// elements of aligned tensors (seek point every 16 elements).  This warp runs tasks `task`,
+// `task + step`, ... below `n_tasks`; task t is chunk `chunk_base + t`.  For every task the
+// sink gets the task number, the sixteen exponents of this lane's group (four per word,
+// lowest byte first) and the group's sixteen sign/mantissa bytes.
+//
+// Three stages run ahead of each other: the seek point of the task after the next is being
+// loaded while the stream words and sign/mantissa bytes of the next task are being loaded
+// while the current task is decoded.  Task numbers fetched ahead are clamped to the last
+// task instead of being branched around, and the loop is unrolled twice so that the two
+// input sets swap roles without register moves.
+//
+// CHECKED = false: the caller guarantees that at least 16 whole stream words follow the
+// start of every task's last group (true for every chunk but the last two of a unit), so a
+// word index is only clamped: a foreign auxiliary buffer gives wrong output, never a fault.
+// CHECKED = true: any chunk of the unit; word loads near the end of the stream go byte by byte.
+template <int K, bool CHECKED, class Sink>
+__device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &tab, uint32_t lane, uint32_t task,
+                                           uint32_t step, uint32_t n_tasks, uint32_t chunk_base, uint32_t n_words,
+                                           int &bad, Sink &&sink)
+{
+    if (task >= n_tasks) return;
+    const uint32_t *codes32 = reinterpret_cast<const uint32_t *>(p.codes);
+    const uint32_t last_task = n_tasks - 1u;
+    const uint32_t last_wi = n_words - 4u;  // callers make sure of n_words >= 4
+    struct Inputs {
+        uint32_t wi, bit;
+        uint4 words, sm;
+    };
+    auto words_at = [&](uint32_t wi) -> uint4 {
+        if (CHECKED && wi > last_wi) return stream_words_slow(p.codes, p.n_bytes, wi);
+        const uint32_t *src = codes32 + wi;
+        return make_uint4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3));
+    };
+    uint32_t lo_n, hi_n;  // seek point of the task after the next
+    auto fetch_seek = [&](uint32_t t) {
+        const uint32_t chunk = chunk_base + min(t, last_task);
+        lo_n = (uint32_t)__ldg(p.sync_lo + chunk * 32u + lane);
+        hi_n = __ldg(p.sync_hi + chunk);
+    };
+    auto fetch_inputs = [&](uint32_t t, Inputs &in) {  // uses the seek point fetched for task t
+        const uint32_t chunk = chunk_base + min(t, last_task);
+        uint32_t lo = lo_n;
+        const uint32_t lo0 = __shfl_sync(0xffffffffu, lo, 0);
+        if (lo < lo0) lo += 65536u;
+        in.wi = (hi_n << 11) + (lo >> 5);
+        if (!CHECKED) in.wi = min(in.wi, last_wi);
+        in.bit = lo & 31u;
+        in.words = words_at(in.wi);
+        in.sm = __ldg(reinterpret_cast<const uint4 *>(p.sm) + (chunk * 32u + lane));
+    };
+    ExpShift X = {0, 0, 0, 0, 0};
+    auto run_task = [&](uint32_t t, const Inputs &cur, Inputs &nxt) {
+        fetch_inputs(t + step, nxt);
+        fetch_seek(t + 2u * step);
+        uint32_t wi = cur.wi, bit = cur.bit, acc = 0, w0, w1, w2;
+        stream_window(cur.words, bit, w0, w1, w2);
+        for (;;) {
+            probe_loop<K>(acc, X, w0, w1, w2, tab.dec_addr);
+            if (acc & kFastDone) break;  // the usual exit
+            if (acc & kFastEscape) {     // full walk for one symbol
+                acc -= kFastEscape;
+                uint32_t len;
+                int tbad = 0;
+                const uint32_t sym = df11_walk_m(tab, p.n_luts, w0, &len, &tbad);
+                if (tbad) bad |= DF11_STATUS_BAD_TABLE;
+                X.push(sym, 8u);
+                acc += len | (8u << 16);
+                if (len < 32u) {
+                    w0 = __funnelshift_l(w1, w0, len);
+                    w1 = __funnelshift_l(w2, w1, len);
+                    w2 <<= len;
+                } else {
+                    w0 = w1, w1 = w2, w2 = 0;
+                }
+                if (acc & kFastDone) break;
+            }
+            if (acc & 64u) {  // position 64..127: reload the window where the position has got to
+                const uint32_t at = bit + (acc & 0x7Fu);
+                wi += at >> 5;
+                if (!CHECKED) wi = min(wi, last_wi);
+                bit = at & 31u;
+                stream_window(words_at(wi), bit, w0, w1, w2);
+                acc &= ~0xFFu;
+            }
+        }
+        uint32_t e0, e1, e2, e3;
+        X.take(acc, e0, e1, e2, e3);
+        sink(t, e0, e1, e2, e3, cur.sm);
+    };
+    Inputs a, b;
+    fetch_seek(task);
+    fetch_inputs(task, a);
+    fetch_seek(task + step);
+    for (;;) {
+        run_task(task, a, b);
+        task += step;
+        if (task >= n_tasks) break;
+        run_task(task, b, a);
+        task += step;
+        if (task >= n_tasks) break;
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Fast decoder (behind df11_decode_prepared).  A warp handles 32 consecutive groups, i.e. one
 // contiguous run of 32*EPT outputs; a thread decodes its group 16 codes at a time.
@@ -484,96 +612,22 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
 
     uint32_t task = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
 
-    // Lean loop: whole-unit decode of aligned tensors, for every chunk but the last two.  Such a
-    // chunk is full, and at least 512 further codes (16 stream words or more) follow it, so no
-    // load of its tasks needs a bounds check; a word index is only clamped (a foreign
-    // auxiliary buffer gives wrong output, never a fault).  Indices of the tasks fetched ahead
-    // are clamped to the last lean chunk instead of being branched around, and the loop is
-    // unrolled twice so that the two input sets swap roles without register moves.
+    // Whole-unit decode of aligned tensors: every chunk but the last two takes the lean loop
+    // (such a chunk is full, and at least 512 further codes, 16 stream words or more, follow it).
     if (EPT == 16 && !ROWS && vec && n_words >= 4u && p.n_chunks > 2) {
-        const uint32_t n_lean = (uint32_t)p.n_chunks - 2u, last_lean = n_lean - 1u;
-        const uint32_t last_wi = n_words - 4u;
-        struct Lean {
-            uint32_t wi, bit;
-            uint4 words, sm;
-        };
-        uint32_t lo_n, hi_n;  // seek point of the task after the next
-        auto lean_seek = [&](uint32_t t) {
-            const uint32_t chunk = min(t, last_lean);
-            lo_n = (uint32_t)__ldg(p.sync_lo + chunk * 32u + lane);
-            hi_n = __ldg(p.sync_hi + chunk);
-        };
-        auto lean_issue = [&](uint32_t t, Lean &in) {  // uses the seek point fetched for task t
-            const uint32_t chunk = min(t, last_lean);
-            uint32_t lo = lo_n;
-            const uint32_t lo0 = __shfl_sync(0xffffffffu, lo, 0);
-            if (lo < lo0) lo += 65536u;
-            in.wi = min((hi_n << 11) + (lo >> 5), last_wi);
-            in.bit = lo & 31u;
-            const uint32_t *src = codes32 + in.wi;
-            in.words = make_uint4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3));
-            in.sm = __ldg(reinterpret_cast<const uint4 *>(p.sm) + (chunk * 32u + lane));
-        };
-        ExpShift X = {0, 0, 0, 0, 0};
-        auto lean_task = [&](uint32_t t, const Lean &cur, Lean &nxt) {
-            lean_issue(t + warps, nxt);
-            lean_seek(t + 2u * warps);
-            uint32_t wi = cur.wi, bit = cur.bit, acc = 0, w0, w1, w2;
-            make_window(cur.words, bit, w0, w1, w2);
-            for (;;) {
-                probe_loop<K>(acc, X, w0, w1, w2, tab.dec_addr);
-                if (acc & kFastDone) break;  // the usual exit
-                if (acc & kFastEscape) {     // full walk for one symbol
-                    acc -= kFastEscape;
-                    uint32_t len;
-                    int tbad = 0;
-                    const uint32_t sym = df11_walk_m(tab, p.n_luts, w0, &len, &tbad);
-                    if (tbad) bad |= DF11_STATUS_BAD_TABLE;
-                    X.push(sym, 8u);
-                    acc += len | (8u << 16);
-                    if (len < 32u) {
-                        w0 = __funnelshift_l(w1, w0, len);
-                        w1 = __funnelshift_l(w2, w1, len);
-                        w2 <<= len;
-                    } else {
-                        w0 = w1, w1 = w2, w2 = 0;
-                    }
-                    if (acc & kFastDone) break;
-                }
-                if (acc & 64u) {  // position 64..127: reload the window where the position has got to
-                    const uint32_t at = bit + (acc & 0x7Fu);
-                    wi = min(wi + (at >> 5), last_wi);
-                    bit = at & 31u;
-                    const uint32_t *src = codes32 + wi;
-                    make_window(make_uint4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3)), bit, w0, w1, w2);
-                    acc &= ~0xFFu;
-                }
-            }
-            uint32_t e0, e1, e2, e3;
-            X.take(acc, e0, e1, e2, e3);
-            uint4 r0, r1;
-            df11_merge4(e0, cur.sm.x, &r0.x, &r0.y);
-            df11_merge4(e1, cur.sm.y, &r0.z, &r0.w);
-            df11_merge4(e2, cur.sm.z, &r1.x, &r1.y);
-            df11_merge4(e3, cur.sm.w, &r1.z, &r1.w);
-            uint4 *dst = reinterpret_cast<uint4 *>(p.out) + 2u * (t * 32u + lane);
-            dst[0] = r0;
-            dst[1] = r1;
-        };
-        if (task < n_lean) {
-            Lean a, b;
-            lean_seek(task);
-            lean_issue(task, a);
-            lean_seek(task + warps);
-            for (;;) {
-                lean_task(task, a, b);
-                task += warps;
-                if (task >= n_lean) break;
-                lean_task(task, b, a);
-                task += warps;
-                if (task >= n_lean) break;
-            }
-        }
+        const uint32_t n_lean = (uint32_t)p.n_chunks - 2u;
+        lean_tasks<K, false>(p, tab, lane, task, warps, n_lean, 0u, n_words, bad,
+                             [&](uint32_t t, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &m) {
+                                 uint4 r0, r1;
+                                 df11_merge4(e0, m.x, &r0.x, &r0.y);
+                                 df11_merge4(e1, m.y, &r0.z, &r0.w);
+                                 df11_merge4(e2, m.z, &r1.x, &r1.y);
+                                 df11_merge4(e3, m.w, &r1.z, &r1.w);
+                                 uint4 *dst = reinterpret_cast<uint4 *>(p.out) + 2u * (t * 32u + lane);
+                                 dst[0] = r0;
+                                 dst[1] = r1;
+                             });
+        if (task < n_lean) task += (n_lean - 1u - task) / warps * warps + warps;  // this warp's first task after them
     }
 
     // General loop: what the lean loop left (the last chunks), row-wise decode, unaligned tensors.
@@ -680,6 +734,130 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
         cur = nxt;
     }
     if (bad && p.status != nullptr) atomicOr(p.status, bad);
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode fused with a matrix-vector product (behind df11_gemv_prepared): y = W x for one
+// [n_rows, in_features] matrix that lies inside a unit, for up to four activation vectors,
+// without ever writing W.  Batch-1 generation is bound by memory traffic: decode-then-GEMV
+// reads the compressed weights, writes 2 bytes per weight and reads them again; this reads
+// the compressed weights only.
+//
+// Tasks are the matrix's 512-element chunks in order (a row is chunks_per_row of them), so
+// the work is balanced whatever the matrix shape.  A lane multiplies its sixteen decoded
+// weights with the sixteen activations of the same columns (bf16 x bf16 products are exact
+// in fp32; fp32 accumulation), the warp adds the 32 results up and stores one partial sum
+// per (row, chunk).  A second, small kernel adds each row's partials in chunk order, adds
+// the bias and rounds to bf16, so the result does not depend on timing.
+// ---------------------------------------------------------------------------------------
+struct GemvArgs {
+    const uint16_t *x;     // [m][in_features] bf16
+    uint16_t *y;           // [m][n_rows] bf16
+    const uint16_t *bias;  // [n_rows] bf16, or null
+    float *partial;        // [m][chunks_per_row][n_rows]
+    uint32_t first_chunk, chunks_per_row, n_rows;
+};
+
+__device__ __forceinline__ float bf16_dot2(uint32_t w, uint32_t x, float acc)
+{
+    asm("{\n\t"
+        ".reg .b16 wl, wh, xl, xh;\n\t"
+        "mov.b32 {wl, wh}, %1;\n\t"
+        "mov.b32 {xl, xh}, %2;\n\t"
+        "fma.rn.f32.bf16 %0, wl, xl, %0;\n\t"
+        "fma.rn.f32.bf16 %0, wh, xh, %0;\n\t"
+        "}"
+        : "+f"(acc)
+        : "r"(w), "r"(x));
+    return acc;
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float f)  // round to nearest even; NaN stays NaN
+{
+    uint32_t u = __float_as_uint(f);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40u);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+template <int K, int M>
+__global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_kernel(const Params p, const GemvArgs g)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
+    constexpr uint32_t luts_off = 8u << K;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u;
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.table_g);
+        uint4 *dst = reinterpret_cast<uint4 *>(smem);
+        for (int i = tid; i < (1 << K) / 2; i += kFastThreads) dst[i] = __ldg(src + i);
+        for (int i = tid; i < p.n_luts * 256; i += kFastThreads) smem[luts_off + i] = __ldg(p.luts + i);
+    }
+    __syncthreads();
+    FastTables tab;
+    tab.dec_addr = smem_addr;
+    tab.luts_addr = smem_addr + luts_off;
+
+    const uint32_t n_words = (uint32_t)(p.n_bytes >> 2);
+    const uint32_t warps = gridDim.x * (kFastThreads / 32);
+    const uint32_t cpr = g.chunks_per_row, n_tasks = g.n_rows * cpr;
+    const uint32_t in_features = cpr * 512u;
+    const uint32_t step_rows = warps / cpr, step_chunks = warps - step_rows * cpr;
+    uint32_t task = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
+    uint32_t row = task / cpr, c = task - row * cpr;  // of the task the sink sees next
+    int bad = 0;
+
+    lean_tasks<K, true>(
+        p, tab, lane, task, warps, n_tasks, g.first_chunk, n_words, bad,
+        [&](uint32_t, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &sm) {
+            uint32_t w[8];
+            df11_merge4(e0, sm.x, &w[0], &w[1]);
+            df11_merge4(e1, sm.y, &w[2], &w[3]);
+            df11_merge4(e2, sm.z, &w[4], &w[5]);
+            df11_merge4(e3, sm.w, &w[6], &w[7]);
+            float sum[M];
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                const uint4 *xp = reinterpret_cast<const uint4 *>(g.x + (size_t)m * in_features + c * 512u) + 2u * lane;
+                const uint4 xa = __ldg(xp), xb = __ldg(xp + 1);
+                float s0 = 0.f, s1 = 0.f;
+                s0 = bf16_dot2(w[0], xa.x, s0);
+                s1 = bf16_dot2(w[1], xa.y, s1);
+                s0 = bf16_dot2(w[2], xa.z, s0);
+                s1 = bf16_dot2(w[3], xa.w, s1);
+                s0 = bf16_dot2(w[4], xb.x, s0);
+                s1 = bf16_dot2(w[5], xb.y, s1);
+                s0 = bf16_dot2(w[6], xb.z, s0);
+                s1 = bf16_dot2(w[7], xb.w, s1);
+                float s = s0 + s1;
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+                sum[m] = s;
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int m = 0; m < M; ++m) g.partial[((size_t)m * cpr + c) * g.n_rows + row] = sum[m];
+            }
+            row += step_rows;
+            c += step_chunks;
+            if (c >= cpr) c -= cpr, ++row;
+        });
+    if (bad && p.status != nullptr) atomicOr(p.status, bad);
+}
+
+// One thread per output: the row's partial sums in chunk order, bias, one rounding to bf16.
+__global__ void __launch_bounds__(256) df11_gemv_finish_kernel(const GemvArgs g, int m_count)
+{
+    const uint32_t i = blockIdx.x * 256u + threadIdx.x;
+    if (i >= g.n_rows * (uint32_t)m_count) return;
+    const uint32_t m = i / g.n_rows, row = i - m * g.n_rows;
+    const float *part = g.partial + (size_t)m * g.chunks_per_row * g.n_rows + row;
+    float total = 0.f;
+    for (uint32_t k = 0; k < g.chunks_per_row; ++k) total += part[(size_t)k * g.n_rows];
+    if (g.bias) total += bf16_bits_to_float(g.bias[row]);
+    g.y[i] = float_to_bf16_bits(total);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -896,7 +1074,7 @@ struct DeviceInfo {
 };
 std::mutex g_mutex;
 DeviceInfo g_devices[64];
-bool g_attr_set[64][6] = {};
+bool g_attr_set[64][10] = {};
 
 struct DeviceGuard {
     int prev = -1;
@@ -930,7 +1108,7 @@ int device_info(int device, DeviceInfo *out)
 
 template <class Kernel>
 int launch(Kernel kernel, int threads, int slot, size_t smem, int64_t work_items, const Params &p, int device,
-           cudaStream_t stream)
+           cudaStream_t stream, int max_ctas_per_sm = 0)
 {
     DeviceInfo info;
     int rc = device_info(device, &info);
@@ -954,10 +1132,49 @@ int launch(Kernel kernel, int threads, int slot, size_t smem, int64_t work_items
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
     if (e != cudaSuccess || per_sm < 1)
         return df11_fail(DF11_ERR_CUDA, "occupancy query failed (%s, %d CTAs/SM)", cudaGetErrorString(e), per_sm);
+    if (max_ctas_per_sm > 0 && per_sm > max_ctas_per_sm) per_sm = max_ctas_per_sm;  // leave room for other kernels
     int64_t grid = (int64_t)info.sm_count * per_sm;
     if (grid > work_items) grid = work_items;
     if (grid < 1) grid = 1;
     kernel<<<(unsigned)grid, threads, smem, stream>>>(p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+    return DF11_OK;
+}
+
+// The same for the fused product kernels, which take a second argument block.
+template <class Kernel>
+int launch_gemv(Kernel kernel, int slot, int m_count, size_t smem, int64_t work_items, const Params &p,
+                const GemvArgs &g, int device, cudaStream_t stream)
+{
+    DeviceInfo info;
+    int rc = device_info(device, &info);
+    if (rc != DF11_OK) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return df11_fail(DF11_ERR_CUDA, "cudaSetDevice(%d) failed", device);
+    if (smem > (size_t)info.max_smem_optin)
+        return df11_fail(DF11_ERR_BADARG, "needs %zu bytes of shared memory, device allows %d", smem,
+                         info.max_smem_optin);
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (!g_attr_set[device][slot]) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 info.max_smem_optin);
+            if (e != cudaSuccess)
+                return df11_fail(DF11_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+            g_attr_set[device][slot] = true;
+        }
+    }
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFastThreads, smem);
+    if (e != cudaSuccess || per_sm < 1)
+        return df11_fail(DF11_ERR_CUDA, "occupancy query failed (%s, %d CTAs/SM)", cudaGetErrorString(e), per_sm);
+    int64_t grid = (int64_t)info.sm_count * per_sm;
+    if (grid > work_items) grid = work_items;
+    if (grid < 1) grid = 1;
+    kernel<<<(unsigned)grid, kFastThreads, smem, stream>>>(p, g);
+    const unsigned outputs = g.n_rows * (unsigned)m_count;
+    df11_gemv_finish_kernel<<<(outputs + 255u) / 256u, 256, 0, stream>>>(g, m_count);
     e = cudaGetLastError();
     if (e != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     return DF11_OK;
@@ -1123,12 +1340,11 @@ extern "C" int df11_prepare(const void *luts, const void *codes, const void *out
     return launch(df11_sync_kernel<kTableBits>, kThreads, 1, smem, p.n_blocks, p, device, (cudaStream_t)stream);
 }
 
-extern "C" int df11_decode_prepared(const void *luts, const void *codes, const void *sign_mantissa,
-                                    const void *output_positions, const void *gaps, const void *aux,
-                                    void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
-                                    int32_t max_block_elems, void *status, int32_t device, void *stream)
+namespace {
+int decode_prepared(const void *luts, const void *codes, const void *sign_mantissa, const void *output_positions,
+                    const void *gaps, const void *aux, void *out_bf16, int32_t n_luts, int64_t n_bytes,
+                    int64_t n_elements, void *status, int32_t device, void *stream, int max_ctas_per_sm)
 {
-    (void)max_block_elems;  // sizes the shared staging of df11_decode only
     int rc = check_common(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements);
     if (rc != DF11_OK) return rc;
     if (n_bytes == 0 || n_elements == 0) return DF11_OK;
@@ -1153,10 +1369,33 @@ extern "C" int df11_decode_prepared(const void *luts, const void *codes, const v
     const int64_t cta_items = (a.n_chunks + kFastThreads / 32 - 1) / (kFastThreads / 32);
     if (ept == 32) {
         const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
-        return launch(df11_fast_kernel<kFastTableBits, 32, false>, kFastThreads, 3, smem, cta_items, p, device, (cudaStream_t)stream);
+        return launch(df11_fast_kernel<kFastTableBits, 32, false>, kFastThreads, 3, smem, cta_items, p, device,
+                      (cudaStream_t)stream, max_ctas_per_sm);
     }
     const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
-    return launch(df11_fast_kernel<kFastTableBits, 16, false>, kFastThreads, 2, smem, cta_items, p, device, (cudaStream_t)stream);
+    return launch(df11_fast_kernel<kFastTableBits, 16, false>, kFastThreads, 2, smem, cta_items, p, device,
+                  (cudaStream_t)stream, max_ctas_per_sm);
+}
+}  // namespace
+
+extern "C" int df11_decode_prepared(const void *luts, const void *codes, const void *sign_mantissa,
+                                    const void *output_positions, const void *gaps, const void *aux,
+                                    void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                                    int32_t max_block_elems, void *status, int32_t device, void *stream)
+{
+    (void)max_block_elems;  // sizes the shared staging of df11_decode only
+    return decode_prepared(luts, codes, sign_mantissa, output_positions, gaps, aux, out_bf16, n_luts, n_bytes,
+                           n_elements, status, device, stream, 0);
+}
+
+extern "C" int df11_decode_prepared_shared(const void *luts, const void *codes, const void *sign_mantissa,
+                                           const void *output_positions, const void *gaps, const void *aux,
+                                           void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                                           int32_t ctas_per_sm, void *status, int32_t device, void *stream)
+{
+    if (ctas_per_sm < 0) return df11_fail(DF11_ERR_BADARG, "ctas_per_sm = %d", ctas_per_sm);
+    return decode_prepared(luts, codes, sign_mantissa, output_positions, gaps, aux, out_bf16, n_luts, n_bytes,
+                           n_elements, status, device, stream, ctas_per_sm);
 }
 
 extern "C" int df11_decode_rows_prepared(const void *luts, const void *codes, const void *sign_mantissa,
@@ -1204,6 +1443,70 @@ extern "C" int df11_decode_rows_prepared(const void *luts, const void *codes, co
     return launch(df11_fast_kernel<kFastTableBits, 16, true>, kFastThreads, 4, smem, cta_items, p, device,
                   (cudaStream_t)stream);
 }
+
+extern "C" int64_t df11_gemv_partials_bytes(int64_t n_rows, int64_t in_features, int32_t m)
+{
+    if (n_rows < 0 || in_features <= 0 || in_features % 512 || m < 1 || m > 4)
+        return df11_fail(DF11_ERR_BADARG, "df11_gemv_partials_bytes(%lld, %lld, %d)", (long long)n_rows,
+                         (long long)in_features, m);
+    return (int64_t)m * n_rows * (in_features / 512) * 4;
+}
+
+extern "C" int df11_gemv_prepared(const void *luts, const void *codes, const void *sign_mantissa, const void *aux,
+                                  const void *x_bf16, void *y_bf16, const void *bias_bf16, void *partials,
+                                  int64_t first_element, int64_t n_rows, int64_t in_features,
+                                  int32_t m, int32_t n_luts, int64_t n_bytes, int64_t n_elements, void *status,
+                                  int32_t device, void *stream)
+{
+    if (!luts || !codes || !sign_mantissa || !aux || !x_bf16 || !y_bf16 || !partials)
+        return df11_fail(DF11_ERR_BADARG, "null pointer");
+    if (n_luts < 2 || n_luts > DF11_MAX_LUTS) return df11_fail(DF11_ERR_BADARG, "n_luts = %d", n_luts);
+    if (n_bytes < 16 || n_elements <= 0 || n_elements > kMaxPreparedElements)
+        return df11_fail(DF11_ERR_BADARG, "unit sizes out of range");
+    if (m < 1 || m > 4) return df11_fail(DF11_ERR_BADARG, "m = %d: one to four activation vectors", m);
+    if (elements_per_seek_point() != 16)
+        return df11_fail(DF11_ERR_BADARG, "the fused product needs a seek point every 16 elements (DF11_EPT unset)");
+    if (in_features <= 0 || in_features % 512 || first_element < 0 || first_element % 512 || n_rows < 0 ||
+        n_rows > 0x7FFFFFFF / (in_features / 512) || first_element + n_rows * in_features > n_elements)
+        return df11_fail(DF11_ERR_BADARG,
+                         "matrix [%lld, %lld] at element %lld: rows must be multiples of 512 elements inside the unit",
+                         (long long)n_rows, (long long)in_features, (long long)first_element);
+    if (((uintptr_t)codes & 3) || ((uintptr_t)sign_mantissa & 15) || ((uintptr_t)aux & 15) || ((uintptr_t)x_bf16 & 15) ||
+        ((uintptr_t)partials & 3) || ((uintptr_t)y_bf16 & 1))
+        return df11_fail(DF11_ERR_BADARG, "misaligned pointer (stream 4, sign_mantissa / aux / x 16 bytes)");
+    if (n_rows == 0) return DF11_OK;
+    const AuxLayout a = aux_layout(n_elements, 16);
+    Params p = {};
+    p.luts = (const uint8_t *)luts;
+    p.codes = (const uint8_t *)codes;
+    p.sm = (const uint8_t *)sign_mantissa;
+    p.table_g = (const Df11Entry *)aux;
+    p.sync_hi = (uint32_t *)((uint8_t *)aux + a.hi_off);
+    p.sync_lo = (uint16_t *)((uint8_t *)aux + a.lo_off);
+    p.status = (int *)status;
+    p.n_bytes = n_bytes;
+    p.n_elements = n_elements;
+    p.n_chunks = a.n_chunks;
+    p.n_luts = n_luts;
+    p.ept = 16;
+    GemvArgs g;
+    g.x = (const uint16_t *)x_bf16;
+    g.y = (uint16_t *)y_bf16;
+    g.bias = (const uint16_t *)bias_bf16;
+    g.partial = (float *)partials;
+    g.first_chunk = (uint32_t)(first_element / 512);
+    g.chunks_per_row = (uint32_t)(in_features / 512);
+    g.n_rows = (uint32_t)n_rows;
+    const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
+    const int64_t cta_items = (n_rows * g.chunks_per_row + kFastThreads / 32 - 1) / (kFastThreads / 32);
+    switch (m) {
+    case 1: return launch_gemv(df11_gemv_kernel<kFastTableBits, 1>, 6, 1, smem, cta_items, p, g, device, (cudaStream_t)stream);
+    case 2: return launch_gemv(df11_gemv_kernel<kFastTableBits, 2>, 7, 2, smem, cta_items, p, g, device, (cudaStream_t)stream);
+    case 3: return launch_gemv(df11_gemv_kernel<kFastTableBits, 3>, 8, 3, smem, cta_items, p, g, device, (cudaStream_t)stream);
+    default: return launch_gemv(df11_gemv_kernel<kFastTableBits, 4>, 9, 4, smem, cta_items, p, g, device, (cudaStream_t)stream);
+    }
+}
+
 
 // ---------------------------------------------------------------------------------------
 // Decode without any allocation by anybody: the auxiliary buffer of the prepared form lives

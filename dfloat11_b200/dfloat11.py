@@ -49,32 +49,36 @@ def _use_prepared() -> bool:
 
 
 class TensorManager:
-    """One BF16 scratch tensor per device, shared by every compressed unit (dfloat11.py:52-100).
+    """BF16 scratch tensors per device, shared by every compressed unit (dfloat11.py:52-100).
 
-    A unit's decode overwrites what the previous unit left there; correctness rests on stream
-    order alone, as in the reference.
+    The reference keeps one tensor per device, and a unit's decode overwrites what the previous
+    unit left there; correctness rests on stream order alone.  Here a device has a few such
+    tensors ("slots"): slot 0 is the reference's; decode-ahead alternates between slots 0 and 1
+    so that the next unit can be decompressed while the current one still computes, and the
+    rows of a sparsely decoded lookup table live in slot 2.
     """
 
-    _tensors: Dict[torch.device, torch.Tensor] = {}
+    _tensors: Dict[tuple, torch.Tensor] = {}
 
     @staticmethod
-    def allocate_bfloat16(device, n_elements: int) -> torch.Tensor:
+    def allocate_bfloat16(device, n_elements: int, slot: int = 0) -> torch.Tensor:
         """A BF16 tensor of exactly ``n_elements`` on ``device``: a slice of the device's scratch,
         which is replaced by a larger one when it is too small."""
         device = torch.device(device)
         if device.type == "cuda" and device.index is None:
             device = torch.device("cuda", torch.cuda.current_device())
-        existing = TensorManager._tensors.get(device)
+        key = (device, slot)
+        existing = TensorManager._tensors.get(key)
         if existing is not None:
             if existing.numel() >= n_elements:
                 return existing[:n_elements]
-            del TensorManager._tensors[device]
+            del TensorManager._tensors[key]
             del existing
             if device.type == "cuda":
                 torch.cuda.empty_cache()
         new_tensor = torch.empty(n_elements, dtype=torch.bfloat16, device=device)
-        log.info("Allocated %d bf16 on device %s", n_elements, device)
-        TensorManager._tensors[device] = new_tensor
+        log.info("Allocated %d bf16 on device %s (slot %d)", n_elements, device, slot)
+        TensorManager._tensors[key] = new_tensor
         return new_tensor
 
     @staticmethod
@@ -83,7 +87,9 @@ class TensorManager:
         if device is None:
             TensorManager._tensors.clear()
         else:
-            TensorManager._tensors.pop(torch.device(device), None)
+            device = torch.device(device)
+            for key in [k for k in TensorManager._tensors if k[0] == device]:
+                del TensorManager._tensors[key]
 
 
 class _OffloadStager:
@@ -160,6 +166,131 @@ class _OffloadStager:
                 s["owner"] = None
 
 
+def _use_decode_ahead() -> bool:
+    return os.environ.get("DF11_DECODE_AHEAD", "0") == "1"
+
+
+def _sparse_enabled() -> bool:
+    return os.environ.get("DF11_SPARSE_EMBEDDING", "1") != "0"
+
+
+class _DecodeAhead:
+    """Per device: decompress the unit that is expected next on a second stream while the
+    current unit computes (the reference decodes in the stream of the forward pass, so the
+    GPU does nothing else meanwhile, dfloat11.py:119-151).
+
+    The order of the units is learned from the hooks themselves: every hook notes which unit
+    ran before it in the same forward.  After a unit's own decode is queued, the unit that
+    followed it last time is decoded on the side stream into the other scratch slot, by a
+    launch that leaves part of every SM to the kernels of the forward pass
+    (``df11_decode_prepared_shared``).  Its hook then only waits for that decode.  A wrong guess
+    costs the wasted decode and nothing else: the hook decodes in-stream as usual.
+    Batch-1 generation spends most of its time in small latency-bound kernels; this is where
+    the decode hides.
+    """
+
+    _by_device: Dict[torch.device, "_DecodeAhead"] = {}
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.stream = torch.cuda.Stream(device=device)
+        self.prev: Optional[nn.Module] = None      # unit whose hook ran last in this forward
+        self.pending = None                        # (module, slot, done event, tensor)
+        self.slot = 0                              # slot that holds the weights of `prev`
+        self.stats = dict(hits=0, misses=0, wasted=0, launched=0)
+
+    @classmethod
+    def get(cls, device: torch.device) -> "_DecodeAhead":
+        if device not in cls._by_device:
+            cls._by_device[device] = cls(device)
+        return cls._by_device[device]
+
+    @classmethod
+    def end_of_forward(cls) -> None:
+        """Joins whatever is still in flight and forgets the last unit, so that "last unit of
+        one forward -> first unit of the next" is never learned as an order."""
+        for ahead in cls._by_device.values():
+            if ahead.pending is not None:
+                torch.cuda.current_stream(ahead.device).wait_event(ahead.pending[2])
+                ahead.pending = None
+                ahead.stats["wasted"] += 1
+            ahead.prev = None
+
+    @staticmethod
+    def eligible(unit: nn.Module, device: torch.device) -> bool:
+        """Resident on this device, auxiliary buffer already built, decoded as a whole."""
+        if hasattr(unit, "offloaded_tensors"):
+            return False
+        aux = unit.__dict__.get("df11_aux")
+        if aux is None or aux.device != device or unit.luts.device != device:
+            return False
+        return not (isinstance(unit, nn.Embedding) and _sparse_enabled())
+
+    def claim(self, module: nn.Module, n_elements: int) -> Optional[torch.Tensor]:
+        """The decoded weights of ``module`` if they were decoded ahead (valid for work queued on
+        the current stream after this call), else None."""
+        pending, self.pending = self.pending, None
+        if pending is None:
+            self.stats["misses"] += 1
+            return None
+        unit, slot, done, tensor = pending
+        torch.cuda.current_stream(self.device).wait_event(done)    # nobody writes a slot after this
+        if unit is module and tensor.numel() == n_elements:
+            self.stats["hits"] += 1
+            self.slot = slot
+            return tensor
+        self.stats["wasted"] += 1
+        self.stats["misses"] += 1
+        return None
+
+    def fresh_slot(self) -> int:
+        self.slot ^= 1
+        return self.slot
+
+    def after(self, module: nn.Module, light: bool = False) -> None:
+        """Call when ``module``'s own decode has been queued: learn the order, start the next.
+        ``light``: this unit's forward is too short to hide anything behind."""
+        if self.pending is not None:                   # a guess nobody claimed: join it before going on
+            torch.cuda.current_stream(self.device).wait_event(self.pending[2])
+            self.pending = None
+            self.stats["wasted"] += 1
+        if self.prev is not None and self.prev is not module:
+            self.prev.__dict__["df11_next_unit"] = module
+        self.prev = module
+        nxt = module.__dict__.get("df11_next_unit")
+        if nxt is None or nxt is module or not self.eligible(nxt, self.device):
+            return
+        n_next = nxt.sign_mantissa.numel()
+        n_this = module.sign_mantissa.numel() if not hasattr(module, "offloaded_tensors") else n_next
+        ctas = int(os.environ.get("DF11_AHEAD_CTAS", "2"))
+        if light or n_next > 2 * n_this:
+            ctas = 0                                   # nothing to share the GPU with: full speed
+        slot = self.slot ^ 1
+        tensor = TensorManager.allocate_bfloat16(self.device, n_next, slot=slot)
+        main = torch.cuda.current_stream(self.device)
+        queued = torch.cuda.Event()
+        queued.record(main)                            # the slot's previous reader has been queued before this
+        self.stream.wait_event(queued)
+        with torch.cuda.stream(self.stream):
+            ops.decode_prepared(nxt.luts, nxt.encoded_exponent, nxt.sign_mantissa, nxt.output_positions,
+                                nxt.gaps, nxt.df11_aux, out=tensor, ctas_per_sm=ctas)
+            done = torch.cuda.Event()
+            done.record(self.stream)
+        self.pending = (nxt, slot, done, tensor)
+        self.stats["launched"] += 1
+
+
+def _end_of_forward_hook(_module, _inputs, _output):
+    _DecodeAhead.end_of_forward()
+
+
+def _mark_root(model: nn.Module) -> None:
+    """Lets decode-ahead see where a forward pass of the whole model ends."""
+    if not model.__dict__.get("df11_root_hooked"):
+        model.register_forward_hook(_end_of_forward_hook)
+        model.__dict__["df11_root_hooked"] = True
+
+
 def _inject_weights(module: nn.Module, reconstructed: torch.Tensor) -> None:
     """Hand the decoded BF16 buffer to the layers as views (dfloat11.py:154-166)."""
     if isinstance(module, nn.Linear):
@@ -174,13 +305,79 @@ def _inject_weights(module: nn.Module, reconstructed: torch.Tensor) -> None:
 
 def _sparse_embedding(module: nn.Module, inputs, n_elements: int) -> bool:
     """Whether this forward of an ``nn.Embedding`` unit can decode just the looked-up rows."""
-    if not isinstance(module, nn.Embedding) or os.environ.get("DF11_SPARSE_EMBEDDING", "1") == "0":
+    if not isinstance(module, nn.Embedding) or not _sparse_enabled():
         return False
     if not inputs or not isinstance(inputs[0], torch.Tensor) or inputs[0].is_floating_point():
         return False
     if module.max_norm is not None or module.embedding_dim % ops.chunk_elements():
         return False
     return 0 < inputs[0].numel() * module.embedding_dim < n_elements      # else the whole table is cheaper
+
+
+def _use_fused_gemv() -> bool:
+    return os.environ.get("DF11_FUSED_GEMV", "0") == "1"
+
+
+FUSED_MAX_ROWS = 4          # activation vectors one fused product takes (df11_gemv_prepared)
+
+
+def _fused_layers(module: nn.Module):
+    """(layer, first element of its weight inside the unit) for every Linear of a unit, or None
+    when the unit cannot take the fused product (a lookup table, rows that are not multiples
+    of 512 elements, tensors kept on the host)."""
+    if hasattr(module, "offloaded_tensors") or isinstance(module, nn.Embedding):
+        return None
+    layers = [module] if isinstance(module, nn.Linear) else list(getattr(module, "weight_injection_modules", []))
+    if not layers or not all(isinstance(l, nn.Linear) and l.in_features % 512 == 0 for l in layers):
+        return None
+    starts = [0] + list(module.split_positions)
+    if len(starts) != len(layers):
+        return None
+    return list(zip(layers, starts))
+
+
+def _install_fused(module: nn.Module) -> bool:
+    """Gives every Linear of the unit a forward that multiplies straight from the compressed
+    weights when it is called with at most FUSED_MAX_ROWS activation vectors, and otherwise
+    decompresses the unit (once per forward of the unit) and calls the ordinary product."""
+    state = module.__dict__.get("df11_fused")
+    if state is not None:
+        return bool(state)
+    layers = _fused_layers(module)
+    module.__dict__["df11_fused"] = layers or []
+    if not layers:
+        return False
+    import torch.nn.functional as F
+
+    def make_forward(layer: nn.Linear, first: int):
+        def forward(x):
+            rows = x.numel() // layer.in_features
+            if (module.__dict__.get("df11_undecoded") and 0 < rows <= FUSED_MAX_ROWS and x.is_cuda
+                    and x.dtype == torch.bfloat16 and _use_fused_gemv()):
+                bias = getattr(layer, "bias", None)
+                y = ops.gemv_prepared(module.luts, module.encoded_exponent, module.sign_mantissa, module.df11_aux,
+                                      x.reshape(rows, layer.in_features).contiguous(), first, layer.out_features,
+                                      layer.in_features, bias=bias)
+                return y.view(*x.shape[:-1], layer.out_features)
+            if module.__dict__.get("df11_undecoded"):
+                _decode_whole_unit(module, module.luts.device)
+            return F.linear(x, layer.weight, getattr(layer, "bias", None))
+        return forward
+
+    for layer, first in layers:
+        layer.forward = make_forward(layer, first)
+    return True
+
+
+def _decode_whole_unit(module: nn.Module, device: torch.device) -> None:
+    """Decompress a resident, prepared unit into the scratch tensor and hand out the views."""
+    n_elements = module.sign_mantissa.numel()
+    reconstructed = TensorManager.allocate_bfloat16(device, n_elements)
+    ops.decode_prepared(module.luts, module.encoded_exponent, module.sign_mantissa, module.output_positions,
+                        module.gaps, module.df11_aux, out=reconstructed,
+                        max_block_elems=getattr(module, "max_block_elems", 0))
+    _inject_weights(module, reconstructed)
+    module.__dict__["df11_undecoded"] = False
 
 
 def get_hook(threads_per_block, bytes_per_thread):
@@ -207,15 +404,26 @@ def get_hook(threads_per_block, bytes_per_thread):
             encoded_exponent, sign_mantissa = module.encoded_exponent, module.sign_mantissa
 
         n_elements = sign_mantissa.numel()
-        reconstructed = TensorManager.allocate_bfloat16(device, n_elements)
         widest = getattr(module, "max_block_elems", 0)
+        module.__dict__["df11_undecoded"] = False
 
         if _use_prepared():
-            aux = getattr(module, "df11_aux", None)
+            aux = module.__dict__.get("df11_aux")
             if aux is None or aux.device != device:
                 # once per unit and device: decode table + seek points (derived data, never saved)
                 aux = ops.prepare(module.luts, encoded_exponent, module.output_positions, module.gaps, n_elements)
                 module.df11_aux = aux
+            if _use_fused_gemv() and stager is None:
+                # decode lazily: the unit's Linear layers multiply straight from the compressed
+                # weights while they are called with a few activation vectors (generation), and
+                # decompress the whole unit the first time one of them is not (prefill).  A unit
+                # that is itself the Linear runs its first such call the ordinary way: torch has
+                # already picked that call's forward when this hook installs the new one.
+                fresh = module.__dict__.get("df11_fused") is None
+                if _install_fused(module) and not (fresh and isinstance(module, nn.Linear)):
+                    module.__dict__["df11_undecoded"] = True
+                    return None
+            ahead = _DecodeAhead.get(device) if _use_decode_ahead() else None
             if _sparse_embedding(module, inputs, n_elements):
                 # a lookup table: decompress only the rows that are asked for (the reference
                 # decodes the whole table on every forward, dfloat11.py:158-161) and look them
@@ -224,17 +432,29 @@ def get_hook(threads_per_block, bytes_per_thread):
                 rows = ops.decode_rows_prepared(module.luts, encoded_exponent, sign_mantissa, aux,
                                                 ids.reshape(-1).to(torch.int64), module.embedding_dim,
                                                 out=TensorManager.allocate_bfloat16(
-                                                    device, ids.numel() * module.embedding_dim))
+                                                    device, ids.numel() * module.embedding_dim, slot=2))
                 module.weight = rows
                 if stager is not None:
                     stager.done(module)
+                if ahead is not None:
+                    ahead.after(module, light=True)
                 return (torch.arange(ids.numel(), device=device).view(ids.shape),) + tuple(inputs[1:])
-            ops.decode_prepared(module.luts, encoded_exponent, sign_mantissa, module.output_positions,
-                                module.gaps, aux, out=reconstructed, max_block_elems=widest)
-        else:
-            ops.decode(module.luts, encoded_exponent, sign_mantissa, module.output_positions, module.gaps,
-                       out=reconstructed, max_block_elems=widest)
+            reconstructed = ahead.claim(module, n_elements) if ahead is not None else None
+            if reconstructed is None:
+                slot = ahead.fresh_slot() if ahead is not None else 0
+                reconstructed = TensorManager.allocate_bfloat16(device, n_elements, slot=slot)
+                ops.decode_prepared(module.luts, encoded_exponent, sign_mantissa, module.output_positions,
+                                    module.gaps, aux, out=reconstructed, max_block_elems=widest)
+            _inject_weights(module, reconstructed)
+            if stager is not None:
+                stager.done(module)
+            if ahead is not None:
+                ahead.after(module)
+            return None
 
+        reconstructed = TensorManager.allocate_bfloat16(device, n_elements)
+        ops.decode(module.luts, encoded_exponent, sign_mantissa, module.output_positions, module.gaps,
+                   out=reconstructed, max_block_elems=widest)
         _inject_weights(module, reconstructed)
         if stager is not None:
             stager.done(module)
@@ -347,6 +567,7 @@ def load_and_replace_tensors(
     offloaded = [m for m in modules.values() if hasattr(m, "offloaded_tensors")]
     for a, b in zip(offloaded, offloaded[1:] + offloaded[:1]):
         a.__dict__["df11_next_offloaded"] = b          # a plain reference, not a registered submodule
+    _mark_root(model)
     return model
 
 
@@ -685,4 +906,5 @@ def compress_in_place(model, pattern_dict: Dict[str, List[str]], cpu_offload: bo
     offloaded = [m for m in model.modules() if hasattr(m, "offloaded_tensors")]
     for a, b in zip(offloaded, offloaded[1:] + offloaded[:1]):
         a.__dict__["df11_next_offloaded"] = b
+    _mark_root(model)
     return model

@@ -83,8 +83,11 @@ def prepare(luts: torch.Tensor, encoded_exponent: torch.Tensor, output_positions
 def decode_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_mantissa: torch.Tensor,
                     output_positions: torch.Tensor, gaps: torch.Tensor, aux: torch.Tensor,
                     out: Optional[torch.Tensor] = None, max_block_elems: int = 0,
-                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Single-pass decode using the buffer made by ``prepare`` for the same unit."""
+                    status: Optional[torch.Tensor] = None, ctas_per_sm: int = 0) -> torch.Tensor:
+    """Single-pass decode using the buffer made by ``prepare`` for the same unit.
+
+    ``ctas_per_sm`` > 0 caps the CTAs the persistent kernel places on an SM, for a launch that
+    should leave room for kernels of other streams (``df11_decode_prepared_shared``)."""
     device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, sign_mantissa=sign_mantissa,
                            output_positions=output_positions, gaps=gaps, aux=aux, out=out, status=status)
     n_elements = sign_mantissa.numel()
@@ -92,6 +95,13 @@ def decode_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_man
         out = torch.empty(n_elements, dtype=torch.bfloat16, device=device)
     if out.dtype != torch.bfloat16 or out.numel() < n_elements:
         raise RuntimeError("`out` must be a bfloat16 tensor with at least n_elements elements")
+    if ctas_per_sm:
+        _lib.check(_lib.lib.df11_decode_prepared_shared(
+            luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(),
+            output_positions.data_ptr(), gaps.data_ptr(), aux.data_ptr(), out.data_ptr(),
+            luts.shape[0], encoded_exponent.numel(), n_elements, int(ctas_per_sm),
+            status.data_ptr() if status is not None else None, device.index, _stream(device)))
+        return out
     _lib.check(_lib.lib.df11_decode_prepared(
         luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(),
         output_positions.data_ptr(), gaps.data_ptr(), aux.data_ptr(), out.data_ptr(),
@@ -127,3 +137,44 @@ def decode_rows_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sig
         rows.data_ptr(), n_rows, int(row_elements), out.data_ptr(), luts.shape[0], encoded_exponent.numel(),
         sign_mantissa.numel(), status.data_ptr() if status is not None else None, device.index, _stream(device)))
     return out[:n_rows * row_elements].view(n_rows, row_elements)
+
+
+_gemv_scratch = {}          # device -> float32 tensor for the partial sums
+
+
+def _gemv_workspace(device: torch.device, n_rows: int, in_features: int, m: int) -> torch.Tensor:
+    need = _lib.check(_lib.lib.df11_gemv_partials_bytes(n_rows, in_features, m)) // 4
+    buf = _gemv_scratch.get(device)
+    if buf is None or buf.numel() < need:
+        buf = _gemv_scratch[device] = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=device)
+    return buf
+
+
+def gemv_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_mantissa: torch.Tensor,
+                  aux: torch.Tensor, x: torch.Tensor, first_element: int, n_rows: int, in_features: int,
+                  bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                  status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ W.T (+ bias)`` for the ``[n_rows, in_features]`` matrix that starts at element
+    ``first_element`` of a prepared unit, decoding the weights on the fly (never written).
+
+    ``x`` is a contiguous BF16 tensor of 1..4 rows of ``in_features``; the result is
+    ``[rows, n_rows]`` BF16.  Launches on one device share a scratch area, so they must be
+    queued on one stream (or otherwise kept from overlapping)."""
+    device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, sign_mantissa=sign_mantissa, aux=aux,
+                           x=x, bias=bias, out=out, status=status)
+    if x.dtype != torch.bfloat16 or (bias is not None and bias.dtype != torch.bfloat16):
+        raise RuntimeError("`x` and `bias` must be bfloat16")
+    if x.numel() % in_features:
+        raise RuntimeError("`x` does not hold whole rows of in_features elements")
+    m = x.numel() // in_features
+    if out is None:
+        out = torch.empty(m, n_rows, dtype=torch.bfloat16, device=device)
+    if out.dtype != torch.bfloat16 or out.numel() < m * n_rows:
+        raise RuntimeError("`out` must be a bfloat16 tensor of m * n_rows elements")
+    partials = _gemv_workspace(device, n_rows, in_features, m)
+    _lib.check(_lib.lib.df11_gemv_prepared(
+        luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(), aux.data_ptr(), x.data_ptr(),
+        out.data_ptr(), bias.data_ptr() if bias is not None else None, partials.data_ptr(),
+        int(first_element), int(n_rows), int(in_features), int(m), luts.shape[0], encoded_exponent.numel(),
+        sign_mantissa.numel(), status.data_ptr() if status is not None else None, device.index, _stream(device)))
+    return out

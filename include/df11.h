@@ -129,6 +129,44 @@ int df11_decode_rows_prepared(const void *luts, const void *codes, const void *s
                               int64_t n_elements, void *status, int32_t device, void *stream);
 
 /*
+ * Decode fused with a matrix-vector product: y[j][r] = sum_c W[r][c] * x[j][c] + bias[r] for
+ * one [n_rows, in_features] matrix W that lies inside a prepared unit (its first weight is
+ * element `first_element` of the unit) and m = 1..4 activation vectors, without writing W
+ * anywhere.  It replaces, for batch-1 generation, the pair "decode the block, then
+ * F.linear on the injected weight views" (dfloat11.py:139-166 plus torch's GEMV), which
+ * writes 2 bytes per weight and reads them again.  x is [m][in_features] bf16, y is
+ * [m][n_rows] bf16, bias is [n_rows] bf16 or NULL; products are exact and accumulated in
+ * fp32 in a fixed order (bit-reproducible run to run; not the order of a library GEMV, so
+ * not bit-identical to one).  in_features and first_element must be multiples of 512,
+ * `codes` 4-byte and sign_mantissa / aux / x 16-byte aligned, and the unit prepared with
+ * a seek point every 16 elements (the default).  `partials` is caller-owned device scratch
+ * of df11_gemv_partials_bytes() bytes whose contents do not matter; launches that share it
+ * must not overlap.  Two kernels are queued: the products, then a small one that adds each
+ * row's partial sums.  No counterpart in the reference.
+ */
+int64_t df11_gemv_partials_bytes(int64_t n_rows, int64_t in_features, int32_t m);
+
+int df11_gemv_prepared(const void *luts, const void *codes, const void *sign_mantissa, const void *aux,
+                       const void *x_bf16, void *y_bf16, const void *bias_bf16, void *partials,
+                       int64_t first_element, int64_t n_rows, int64_t in_features,
+                       int32_t m, int32_t n_luts, int64_t n_bytes, int64_t n_elements, void *status,
+                       int32_t device, void *stream);
+
+/*
+ * df11_decode_prepared for a launch that is meant to run BESIDE other kernels: the decode
+ * of the next transformer block on a second stream while the current block computes.  The
+ * fast decoder is a persistent kernel that otherwise fills every SM (4 CTAs of 256 threads),
+ * so kernels of other streams would wait for it to end; `ctas_per_sm` (1..4, 0 = all) caps
+ * the CTAs it places per SM and leaves the rest of each SM to them.  Same arguments, result
+ * and bits as df11_decode_prepared.  No counterpart in the reference, which decodes in the
+ * stream of the forward pass and overwrites one buffer (dfloat11.py:119-151).
+ */
+int df11_decode_prepared_shared(const void *luts, const void *codes, const void *sign_mantissa,
+                                const void *output_positions, const void *gaps, const void *aux,
+                                void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                                int32_t ctas_per_sm, void *status, int32_t device, void *stream);
+
+/*
  * Decode for callers that cannot allocate device memory at all and have nobody to do it
  * for them: code running inside a CUDA-graph capture or a stream callback, a plug-in
  * called from a serving loop whose memory pool is already carved up, a host runtime

@@ -344,3 +344,32 @@ def test_prepared_decode_of_inconsistent_inputs_stays_in_bounds():
         ops.decode_prepared(d["luts"], stream, d["sm"], d["pos"], d["gaps"], aux, out=buf[:n], status=st)
         torch.cuda.synchronize()
         assert torch.all(buf[n:] == 7.0)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
+def test_fused_matrix_vector_product(m):
+    """df11_gemv_prepared against an fp32 product with the decoded weights: one BF16 rounding of
+    the exact-product, fp32-accumulated sum (tolerance: one BF16 unit in the last place of the
+    result plus fp32 accumulation noise), for two matrices inside one unit, with and without
+    bias, including the unit's last chunks; reproducible bit for bit."""
+    g = torch.Generator().manual_seed(40 + m)
+    a = (torch.randn(1536, 2048, generator=g) * 0.02).to(torch.bfloat16)
+    b = (torch.randn(520, 1024, generator=g) * 0.02).to(torch.bfloat16)          # ends the unit
+    t, d, widest = _unit_from_weights([a.flatten(), b.flatten()])
+    n = a.numel() + b.numel()
+    st = _status()
+    aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], n, status=st)
+    for w, first, bias in ((a, 0, None), (b, a.numel(), (torch.randn(520, generator=g) * 0.1).to(torch.bfloat16))):
+        x = torch.randn(m, w.shape[1], generator=g).to(torch.bfloat16).to(DEV)
+        bias_d = bias.to(DEV) if bias is not None else None
+        y = ops.gemv_prepared(d["luts"], d["enc"], d["sm"], aux, x, first, w.shape[0], w.shape[1], bias=bias_d, status=st)
+        y2 = ops.gemv_prepared(d["luts"], d["enc"], d["sm"], aux, x, first, w.shape[0], w.shape[1], bias=bias_d, status=st)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        want = x.double().cpu() @ w.double().T + (bias.double() if bias is not None else 0.0)
+        err = (y.double().cpu() - want).abs()
+        assert torch.all(err <= want.abs() * 2.0 ** -8 + 1e-5), float(err.max())
+        assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+        assert y.shape == (m, w.shape[0])
+    with pytest.raises(_lib.DF11Error):
+        ops.gemv_prepared(d["luts"], d["enc"], d["sm"], aux, x[:, :1000].contiguous(), 0, 16, 1000)   # not a multiple of 512

@@ -154,19 +154,28 @@ def test_tensor_manager_reuses_and_grows():
     b = host.TensorManager.allocate_bfloat16("cpu", 60)
     assert b.data_ptr() == a.data_ptr() and b.numel() == 60
     c = host.TensorManager.allocate_bfloat16("cpu", 500)
-    assert c.numel() == 500 and host.TensorManager._tensors[torch.device("cpu")].numel() == 500
-    host.TensorManager.release()
+    assert c.numel() == 500 and host.TensorManager._tensors[(torch.device("cpu"), 0)].numel() == 500
+    d = host.TensorManager.allocate_bfloat16("cpu", 40, slot=1)            # slots are separate tensors
+    assert d.data_ptr() != c.data_ptr() and host.TensorManager.allocate_bfloat16("cpu", 10).data_ptr() == c.data_ptr()
+    host.TensorManager.release("cpu")
+    assert not host.TensorManager._tensors
 
 
 # ------------------------------------------------------------------ GPU
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["resident", "offload", "offload_some", "two_pass", "auto_map"])
+@pytest.mark.parametrize("mode", ["resident", "ahead", "ahead_3_ctas", "offload", "offload_some_ahead", "two_pass",
+                                  "auto_map"])
 def test_logits_identical_to_bf16_model(saved, mode, monkeypatch):
     path, reference = saved
     kwargs = dict(device="cuda:0")
+    host._DecodeAhead._by_device.clear()
+    if "ahead" in mode:
+        monkeypatch.setenv("DF11_DECODE_AHEAD", "1")             # next unit decoded on a second stream
+    if mode == "ahead_3_ctas":
+        monkeypatch.setenv("DF11_AHEAD_CTAS", "3")
     if mode == "offload":
         kwargs["cpu_offload"] = True
-    elif mode == "offload_some":
+    elif mode.startswith("offload_some"):
         kwargs.update(cpu_offload=True, cpu_offload_blocks=2)
     elif mode == "two_pass":
         monkeypatch.setenv("DF11_PREPARED", "0")
@@ -186,6 +195,12 @@ def test_logits_identical_to_bf16_model(saved, mode, monkeypatch):
     if mode.startswith("offload"):
         stager = host._OffloadStager.get(torch.device("cuda:0"))
         assert stager.stats["prefetch_hits"] > 0 and stager.stats["h2d_bytes"] > 0
+    ahead = host._DecodeAhead._by_device.get(torch.device("cuda:0"))
+    if "ahead" in mode:
+        # from the second forward on, resident units are decompressed while their predecessor computes
+        assert ahead is not None and ahead.stats["hits"] > 0 and ahead.pending is None
+    else:
+        assert ahead is None or ahead.stats["launched"] == 0
 
 
 @pytest.mark.gpu
@@ -249,3 +264,47 @@ def test_embedding_unit_decodes_only_looked_up_rows(tmp_path, monkeypatch):
         assert torch.equal(loaded.emb(ids), reference(ids))
         assert loaded.emb.weight.shape == (2000, 512)
     del ref_holder
+
+
+@pytest.mark.gpu
+def test_fused_products_for_single_token_steps(monkeypatch):
+    """DF11_FUSED_GEMV=1: a forward over a few tokens multiplies straight from the compressed
+    weights (same exact products, fp32 sums in another order than the library GEMV: logits
+    agree to BF16 rounding, not bit for bit); a longer forward decompresses as usual and stays
+    bit-identical."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                      num_key_value_heads=2, vocab_size=1024, max_position_embeddings=256, tie_word_embeddings=False)
+    torch.manual_seed(11)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 2:
+                p.copy_((torch.randn(p.shape) * (1.0 if "embed" in name else 0.03)).to(torch.bfloat16))
+    reference = copy.deepcopy(model).to("cuda:0")
+    model = model.to("cuda:0")
+    df11.compress_in_place(model, LLAMA_PATTERNS)
+    monkeypatch.setenv("DF11_FUSED_GEMV", "1")
+    calls = []
+    real = host.ops.gemv_prepared
+    monkeypatch.setattr(host.ops, "gemv_prepared", lambda *a, **k: (calls.append(a[5:8]), real(*a, **k))[1])
+    ids = torch.randint(0, 1024, (1, 21), generator=torch.Generator().manual_seed(5)).to("cuda:0")
+    with torch.no_grad():
+        want = reference(input_ids=ids).logits
+        got = model(input_ids=ids).logits                         # 21 tokens: ordinary decode
+        assert torch.equal(got, want) and not calls
+        cache_a = model(input_ids=ids, use_cache=True).past_key_values
+        cache_b = reference(input_ids=ids, use_cache=True).past_key_values
+        tok = ids[:, -1:]
+        got1 = model(input_ids=tok, past_key_values=cache_a, use_cache=True).logits
+        want1 = reference(input_ids=tok, past_key_values=cache_b, use_cache=True).logits
+    assert len(calls) == 2 * 7 + 1                                # seven products per block and the head
+    assert not hasattr(model.lm_head, "offloaded_tensors")
+    assert (0, 512, 512) in calls and (0, 1024, 512) in calls     # q_proj of a block, the head
+    scale = float(want1.float().abs().max())
+    assert float((got1.float() - want1.float()).abs().max()) <= 0.03 * scale
+    assert torch.equal(got1.argmax(-1), want1.argmax(-1))
+    monkeypatch.setenv("DF11_FUSED_GEMV", "0")
+    with torch.no_grad():                                         # switched off again: the usual path, bit-identical
+        again = model(input_ids=ids).logits
+    assert torch.equal(again, want)
