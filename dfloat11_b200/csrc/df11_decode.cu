@@ -409,10 +409,10 @@ __device__ __forceinline__ void stream_window(const uint4 &r, uint32_t bit, uint
 }
 
 // The inner loop of the fast decoder for tasks that are known to be whole chunks of 512
-// elements of aligned tensors (seek point every 16 elements).  This warp runs tasks `task`,
-// `task + step`, ... below `n_tasks`; task t is chunk `chunk_base + t`.  For every task the
-// sink gets the task number, the sixteen exponents of this lane's group (four per word,
-// lowest byte first) and the group's sixteen sign/mantissa bytes.
+// elements of aligned tensors (seek point every 16 elements).  This warp runs `n_seq` tasks,
+// numbered 0 .. n_seq-1 in the order it runs them; task j is chunk `chunk_of(j)`.  For every
+// task the sink gets the task's number, the sixteen exponents of this lane's group (four per
+// word, lowest byte first) and the group's sixteen sign/mantissa bytes.
 //
 // Three stages run ahead of each other: the seek point of the task after the next is being
 // loaded while the stream words and sign/mantissa bytes of the next task are being loaded
@@ -424,14 +424,13 @@ __device__ __forceinline__ void stream_window(const uint4 &r, uint32_t bit, uint
 // start of every task's last group (true for every chunk but the last two of a unit), so a
 // word index is only clamped: a foreign auxiliary buffer gives wrong output, never a fault.
 // CHECKED = true: any chunk of the unit; word loads near the end of the stream go byte by byte.
-template <int K, bool CHECKED, class Sink>
-__device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &tab, uint32_t lane, uint32_t task,
-                                           uint32_t step, uint32_t n_tasks, uint32_t chunk_base, uint32_t n_words,
-                                           int &bad, Sink &&sink)
+template <int K, bool CHECKED, class ChunkOf, class Sink>
+__device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &tab, uint32_t lane, uint32_t n_seq,
+                                           ChunkOf &&chunk_of, uint32_t n_words, int &bad, Sink &&sink)
 {
-    if (task >= n_tasks) return;
+    if (n_seq == 0u) return;
     const uint32_t *codes32 = reinterpret_cast<const uint32_t *>(p.codes);
-    const uint32_t last_task = n_tasks - 1u;
+    const uint32_t last_task = n_seq - 1u;
     const uint32_t last_wi = n_words - 4u;  // callers make sure of n_words >= 4
     struct Inputs {
         uint32_t wi, bit;
@@ -444,12 +443,12 @@ __device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &ta
     };
     uint32_t lo_n, hi_n;  // seek point of the task after the next
     auto fetch_seek = [&](uint32_t t) {
-        const uint32_t chunk = chunk_base + min(t, last_task);
+        const uint32_t chunk = chunk_of(min(t, last_task));
         lo_n = (uint32_t)__ldg(p.sync_lo + chunk * 32u + lane);
         hi_n = __ldg(p.sync_hi + chunk);
     };
     auto fetch_inputs = [&](uint32_t t, Inputs &in) {  // uses the seek point fetched for task t
-        const uint32_t chunk = chunk_base + min(t, last_task);
+        const uint32_t chunk = chunk_of(min(t, last_task));
         uint32_t lo = lo_n;
         const uint32_t lo0 = __shfl_sync(0xffffffffu, lo, 0);
         if (lo < lo0) lo += 65536u;
@@ -461,8 +460,8 @@ __device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &ta
     };
     ExpShift X = {0, 0, 0, 0, 0};
     auto run_task = [&](uint32_t t, const Inputs &cur, Inputs &nxt) {
-        fetch_inputs(t + step, nxt);
-        fetch_seek(t + 2u * step);
+        fetch_inputs(t + 1u, nxt);
+        fetch_seek(t + 2u);
         uint32_t wi = cur.wi, bit = cur.bit, acc = 0, w0, w1, w2;
         stream_window(cur.words, bit, w0, w1, w2);
         for (;;) {
@@ -499,16 +498,14 @@ __device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &ta
         sink(t, e0, e1, e2, e3, cur.sm);
     };
     Inputs a, b;
-    fetch_seek(task);
-    fetch_inputs(task, a);
-    fetch_seek(task + step);
-    for (;;) {
-        run_task(task, a, b);
-        task += step;
-        if (task >= n_tasks) break;
-        run_task(task, b, a);
-        task += step;
-        if (task >= n_tasks) break;
+    fetch_seek(0u);
+    fetch_inputs(0u, a);
+    fetch_seek(1u);
+    for (uint32_t j = 0;;) {
+        run_task(j, a, b);
+        if (++j >= n_seq) break;
+        run_task(j, b, a);
+        if (++j >= n_seq) break;
     }
 }
 
@@ -616,18 +613,21 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
     // (such a chunk is full, and at least 512 further codes, 16 stream words or more, follow it).
     if (EPT == 16 && !ROWS && vec && n_words >= 4u && p.n_chunks > 2) {
         const uint32_t n_lean = (uint32_t)p.n_chunks - 2u;
-        lean_tasks<K, false>(p, tab, lane, task, warps, n_lean, 0u, n_words, bad,
-                             [&](uint32_t t, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &m) {
-                                 uint4 r0, r1;
-                                 df11_merge4(e0, m.x, &r0.x, &r0.y);
-                                 df11_merge4(e1, m.y, &r0.z, &r0.w);
-                                 df11_merge4(e2, m.z, &r1.x, &r1.y);
-                                 df11_merge4(e3, m.w, &r1.z, &r1.w);
-                                 uint4 *dst = reinterpret_cast<uint4 *>(p.out) + 2u * (t * 32u + lane);
-                                 dst[0] = r0;
-                                 dst[1] = r1;
-                             });
-        if (task < n_lean) task += (n_lean - 1u - task) / warps * warps + warps;  // this warp's first task after them
+        const uint32_t mine = task < n_lean ? (n_lean - 1u - task) / warps + 1u : 0u;  // this warp's lean tasks
+        const uint32_t task0 = task;
+        lean_tasks<K, false>(
+            p, tab, lane, mine, [&](uint32_t j) { return task0 + j * warps; }, n_words, bad,
+            [&](uint32_t j, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &m) {
+                uint4 r0, r1;
+                df11_merge4(e0, m.x, &r0.x, &r0.y);
+                df11_merge4(e1, m.y, &r0.z, &r0.w);
+                df11_merge4(e2, m.z, &r1.x, &r1.y);
+                df11_merge4(e3, m.w, &r1.z, &r1.w);
+                uint4 *dst = reinterpret_cast<uint4 *>(p.out) + 2u * ((task0 + j * warps) * 32u + lane);
+                dst[0] = r0;
+                dst[1] = r1;
+            });
+        task += mine * warps;  // this warp's first task after them
     }
 
     // General loop: what the lean loop left (the last chunks), row-wise decode, unaligned tensors.
@@ -743,19 +743,22 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
 // reads the compressed weights, writes 2 bytes per weight and reads them again; this reads
 // the compressed weights only.
 //
-// Tasks are the matrix's 512-element chunks in order (a row is chunks_per_row of them), so
-// the work is balanced whatever the matrix shape.  A lane multiplies its sixteen decoded
-// weights with the sixteen activations of the same columns (bf16 x bf16 products are exact
-// in fp32; fp32 accumulation), the warp adds the 32 results up and stores one partial sum
-// per (row, chunk).  A second, small kernel adds each row's partials in chunk order, adds
-// the bias and rounds to bf16, so the result does not depend on timing.
+// A work item is a run of consecutive 512-element chunks of one row (1, 2, 4 or 8 of them,
+// chosen per launch: as long as the items still spread evenly over the warps); items go
+// round the warps, so the work is balanced whatever the matrix shape.  A lane multiplies its
+// sixteen decoded weights with the sixteen activations of the same columns (bf16 x bf16
+// products are exact in fp32; fp32 accumulation) and keeps the sum over the run; at the end
+// of a run the warp adds its 32 lanes up.  A run that is a whole row is the output: bias,
+// one rounding to bf16, stored.  Otherwise the run's sum is stored and a second, small
+// kernel adds each row's sums in order.  Either way the result does not depend on timing.
 // ---------------------------------------------------------------------------------------
 struct GemvArgs {
     const uint16_t *x;     // [m][in_features] bf16
     uint16_t *y;           // [m][n_rows] bf16
     const uint16_t *bias;  // [n_rows] bf16, or null
-    float *partial;        // [m][chunks_per_row][n_rows]
+    float *partial;        // [m][runs per row][n_rows]
     uint32_t first_chunk, chunks_per_row, n_rows;
+    uint32_t run_log;      // a work item is 1 << run_log consecutive chunks of a row
 };
 
 __device__ __forceinline__ float bf16_dot2(uint32_t w, uint32_t x, float acc)
@@ -800,29 +803,40 @@ __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
     tab.dec_addr = smem_addr;
     tab.luts_addr = smem_addr + luts_off;
 
+    // Work items are runs of `run` consecutive chunks of one row (run = 1 << run_log divides
+    // chunks_per_row); items go round the warps.  A lane keeps its products of a run in a
+    // register, so the warp adds its 32 lanes up once per run, not once per chunk.
     const uint32_t n_words = (uint32_t)(p.n_bytes >> 2);
     const uint32_t warps = gridDim.x * (kFastThreads / 32);
-    const uint32_t cpr = g.chunks_per_row, n_tasks = g.n_rows * cpr;
+    const uint32_t gw = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
+    const uint32_t cpr = g.chunks_per_row, run_log = g.run_log, run = 1u << run_log;
+    const uint32_t parts = cpr >> run_log;  // runs per row
+    const uint32_t n_items = g.n_rows * parts;
+    const uint32_t my_items = gw < n_items ? (n_items - 1u - gw) / warps + 1u : 0u;
     const uint32_t in_features = cpr * 512u;
-    const uint32_t step_rows = warps / cpr, step_chunks = warps - step_rows * cpr;
-    uint32_t task = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
-    uint32_t row = task / cpr, c = task - row * cpr;  // of the task the sink sees next
+    const uint32_t step_rows = warps / parts, step_parts = warps - step_rows * parts;
+    uint32_t row = gw / parts, part = gw - row * parts;  // of the item the sink is in
     int bad = 0;
+    float sum[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) sum[m] = 0.f;
 
     lean_tasks<K, true>(
-        p, tab, lane, task, warps, n_tasks, g.first_chunk, n_words, bad,
-        [&](uint32_t, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &sm) {
+        p, tab, lane, my_items << run_log,
+        [&](uint32_t j) { return g.first_chunk + ((gw + (j >> run_log) * warps) << run_log) + (j & (run - 1u)); },
+        n_words, bad, [&](uint32_t j, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &sm) {
             uint32_t w[8];
             df11_merge4(e0, sm.x, &w[0], &w[1]);
             df11_merge4(e1, sm.y, &w[2], &w[3]);
             df11_merge4(e2, sm.z, &w[4], &w[5]);
             df11_merge4(e3, sm.w, &w[6], &w[7]);
-            float sum[M];
+            const uint32_t sub = j & (run - 1u);
+            const uint32_t column = ((part << run_log) + sub) * 512u + 16u * lane;
 #pragma unroll
             for (int m = 0; m < M; ++m) {
-                const uint4 *xp = reinterpret_cast<const uint4 *>(g.x + (size_t)m * in_features + c * 512u) + 2u * lane;
+                const uint4 *xp = reinterpret_cast<const uint4 *>(g.x + (size_t)m * in_features + column);
                 const uint4 xa = __ldg(xp), xb = __ldg(xp + 1);
-                float s0 = 0.f, s1 = 0.f;
+                float s0 = sum[m], s1 = 0.f;
                 s0 = bf16_dot2(w[0], xa.x, s0);
                 s1 = bf16_dot2(w[1], xa.y, s1);
                 s0 = bf16_dot2(w[2], xa.z, s0);
@@ -831,31 +845,42 @@ __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
                 s1 = bf16_dot2(w[5], xb.y, s1);
                 s0 = bf16_dot2(w[6], xb.z, s0);
                 s1 = bf16_dot2(w[7], xb.w, s1);
-                float s = s0 + s1;
-#pragma unroll
-                for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-                sum[m] = s;
+                sum[m] = s0 + s1;
             }
-            if (lane == 0) {
+            if (sub != run - 1u) return;
+            // end of the run: add the lanes up; a run that is a whole row gives the output itself
 #pragma unroll
-                for (int m = 0; m < M; ++m) g.partial[((size_t)m * cpr + c) * g.n_rows + row] = sum[m];
+            for (int m = 0; m < M; ++m) {
+                float t = sum[m];
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
+                if (lane == 0) {
+                    if (parts == 1u) {
+                        if (g.bias) t += bf16_bits_to_float(g.bias[row]);
+                        g.y[(size_t)m * g.n_rows + row] = float_to_bf16_bits(t);
+                    } else {
+                        g.partial[((size_t)m * parts + part) * g.n_rows + row] = t;
+                    }
+                }
+                sum[m] = 0.f;
             }
             row += step_rows;
-            c += step_chunks;
-            if (c >= cpr) c -= cpr, ++row;
+            part += step_parts;
+            if (part >= parts) part -= parts, ++row;
         });
     if (bad && p.status != nullptr) atomicOr(p.status, bad);
 }
 
-// One thread per output: the row's partial sums in chunk order, bias, one rounding to bf16.
+// One thread per output: the row's partial sums in order, bias, one rounding to bf16.
 __global__ void __launch_bounds__(256) df11_gemv_finish_kernel(const GemvArgs g, int m_count)
 {
     const uint32_t i = blockIdx.x * 256u + threadIdx.x;
     if (i >= g.n_rows * (uint32_t)m_count) return;
     const uint32_t m = i / g.n_rows, row = i - m * g.n_rows;
-    const float *part = g.partial + (size_t)m * g.chunks_per_row * g.n_rows + row;
+    const uint32_t parts = g.chunks_per_row >> g.run_log;
+    const float *part = g.partial + (size_t)m * parts * g.n_rows + row;
     float total = 0.f;
-    for (uint32_t k = 0; k < g.chunks_per_row; ++k) total += part[(size_t)k * g.n_rows];
+    for (uint32_t k = 0; k < parts; ++k) total += part[(size_t)k * g.n_rows];
     if (g.bias) total += bf16_bits_to_float(g.bias[row]);
     g.y[i] = float_to_bf16_bits(total);
 }
@@ -1172,9 +1197,24 @@ int launch_gemv(Kernel kernel, int slot, int m_count, size_t smem, int64_t work_
     int64_t grid = (int64_t)info.sm_count * per_sm;
     if (grid > work_items) grid = work_items;
     if (grid < 1) grid = 1;
-    kernel<<<(unsigned)grid, kFastThreads, smem, stream>>>(p, g);
-    const unsigned outputs = g.n_rows * (unsigned)m_count;
-    df11_gemv_finish_kernel<<<(outputs + 255u) / 256u, 256, 0, stream>>>(g, m_count);
+    // longest run (8, 4, 2, 1 chunks, dividing the row) whose items still fill the warps' rounds to 85 %
+    GemvArgs args = g;
+    const int64_t warps = grid * (kFastThreads / 32);
+    args.run_log = 0;
+    for (int log = 3; log > 0; --log) {
+        if (g.chunks_per_row % (1u << log)) continue;
+        const int64_t items = (int64_t)g.n_rows * (g.chunks_per_row >> log);
+        const int64_t rounds = (items + warps - 1) / warps;
+        if (items * 100 >= rounds * warps * 85) {
+            args.run_log = (uint32_t)log;
+            break;
+        }
+    }
+    kernel<<<(unsigned)grid, kFastThreads, smem, stream>>>(p, args);
+    if ((g.chunks_per_row >> args.run_log) > 1u) {
+        const unsigned outputs = g.n_rows * (unsigned)m_count;
+        df11_gemv_finish_kernel<<<(outputs + 255u) / 256u, 256, 0, stream>>>(args, m_count);
+    }
     e = cudaGetLastError();
     if (e != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     return DF11_OK;

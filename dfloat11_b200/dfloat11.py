@@ -336,6 +336,28 @@ def _fused_layers(module: nn.Module):
     return list(zip(layers, starts))
 
 
+# Layers that are fed the same activations and lie next to each other in a unit: one fused
+# product over their stacked rows serves all of them (three launches become one).
+FUSED_FAMILIES = (("q_proj", "k_proj", "v_proj"), ("gate_proj", "up_proj"), ("to_q", "to_k", "to_v"))
+
+
+def _fused_groups(module: nn.Module, layers):
+    """Splits ``layers`` [(layer, first element)] into runs that one product can serve."""
+    leaf = {id(m): name.rsplit(".", 1)[-1] for name, m in module.named_modules()}
+    groups, i = [], 0
+    while i < len(layers):
+        first_layer = layers[i][0]
+        family = next((f for f in FUSED_FAMILIES if leaf.get(id(first_layer)) in f), ())
+        j = i + 1
+        while (j < len(layers) and leaf.get(id(layers[j][0])) in family
+               and layers[j][0].in_features == first_layer.in_features
+               and (layers[j][0].bias is None) == (first_layer.bias is None)):
+            j += 1
+        groups.append(layers[i:j])
+        i = j
+    return groups
+
+
 def _install_fused(module: nn.Module) -> bool:
     """Gives every Linear of the unit a forward that multiplies straight from the compressed
     weights when it is called with at most FUSED_MAX_ROWS activation vectors, and otherwise
@@ -349,23 +371,54 @@ def _install_fused(module: nn.Module) -> bool:
         return False
     import torch.nn.functional as F
 
-    def make_forward(layer: nn.Linear, first: int):
+    def fused_ok(x, layer):
+        rows = x.numel() // layer.in_features
+        return (module.__dict__.get("df11_undecoded") and 0 < rows <= FUSED_MAX_ROWS and x.is_cuda
+                and x.dtype == torch.bfloat16 and _use_fused_gemv())
+
+    def product(x, first, n_rows, in_features, bias):
+        rows = x.numel() // in_features
+        return ops.gemv_prepared(module.luts, module.encoded_exponent, module.sign_mantissa, module.df11_aux,
+                                 x.reshape(rows, in_features).contiguous(), first, n_rows, in_features, bias=bias)
+
+    def ordinary(x, layer):
+        if module.__dict__.get("df11_undecoded"):
+            _decode_whole_unit(module, module.luts.device)
+        return F.linear(x, layer.weight, getattr(layer, "bias", None))
+
+    def make_forward(group, k):
+        layer, first = group[k]
+        lead_first = group[0][1]
+        total_rows = sum(l.out_features for l, _ in group)
+        offset = sum(l.out_features for l, _ in group[:k])
+        shared = group_state[id(group[0][0])]
+
         def forward(x):
-            rows = x.numel() // layer.in_features
-            if (module.__dict__.get("df11_undecoded") and 0 < rows <= FUSED_MAX_ROWS and x.is_cuda
-                    and x.dtype == torch.bfloat16 and _use_fused_gemv()):
-                bias = getattr(layer, "bias", None)
-                y = ops.gemv_prepared(module.luts, module.encoded_exponent, module.sign_mantissa, module.df11_aux,
-                                      x.reshape(rows, layer.in_features).contiguous(), first, layer.out_features,
-                                      layer.in_features, bias=bias)
+            if not fused_ok(x, layer):
+                return ordinary(x, layer)
+            if len(group) == 1:
+                y = product(x, first, layer.out_features, layer.in_features, getattr(layer, "bias", None))
                 return y.view(*x.shape[:-1], layer.out_features)
-            if module.__dict__.get("df11_undecoded"):
-                _decode_whole_unit(module, module.luts.device)
-            return F.linear(x, layer.weight, getattr(layer, "bias", None))
+            cached = shared.get("result")
+            if k > 0 and cached is not None and cached[0] is x and cached[1] == x._version:
+                y = cached[2]                                   # the leader already multiplied for everybody
+            elif k == 0:
+                if "bias" not in shared:
+                    biases = [l.bias for l, _ in group]
+                    shared["bias"] = None if biases[0] is None else torch.cat([b.detach() for b in biases])
+                y = product(x, lead_first, total_rows, layer.in_features, shared["bias"])
+                shared["result"] = (x, x._version, y)
+            else:                                               # other activations than the leader's: on its own
+                y = product(x, first, layer.out_features, layer.in_features, getattr(layer, "bias", None))
+                return y.view(*x.shape[:-1], layer.out_features)
+            return y[:, offset:offset + layer.out_features].reshape(*x.shape[:-1], layer.out_features)
         return forward
 
-    for layer, first in layers:
-        layer.forward = make_forward(layer, first)
+    group_state = {}
+    for group in _fused_groups(module, layers):
+        group_state[id(group[0][0])] = {}
+        for k in range(len(group)):
+            group[k][0].forward = make_forward(group, k)
     return True
 
 

@@ -373,3 +373,26 @@ def test_fused_matrix_vector_product(m):
         assert y.shape == (m, w.shape[0])
     with pytest.raises(_lib.DF11Error):
         ops.gemv_prepared(d["luts"], d["enc"], d["sm"], aux, x[:, :1000].contiguous(), 0, 16, 1000)   # not a multiple of 512
+
+
+@pytest.mark.parametrize("rows,in_features", [(10656, 1024), (5328, 2048), (7104, 2048), (4096, 4096)])
+def test_fused_product_with_longer_runs(rows, in_features):
+    """Shapes for which the fused kernel keeps sums over runs of 2, 4 or 8 chunks of a row (on a
+    148-SM part with 3 CTAs per SM: whole-row runs for the first and third shape, half-row runs
+    for the second); same tolerance as above, two activation vectors, with bias."""
+    g = torch.Generator().manual_seed(rows)
+    w = (torch.randn(rows, in_features, generator=g) * 0.02).to(torch.bfloat16)
+    pad = (torch.randn(3000, generator=g) * 0.02).to(torch.bfloat16)        # the matrix does not end the unit
+    t, d, widest = _unit_from_weights([w.flatten(), pad])
+    st = _status()
+    aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], w.numel() + pad.numel(), status=st)
+    x = torch.randn(2, in_features, generator=g).to(torch.bfloat16).to(DEV)
+    bias = (torch.randn(rows, generator=g) * 0.1).to(torch.bfloat16)
+    y = ops.gemv_prepared(d["luts"], d["enc"], d["sm"], aux, x, 0, rows, in_features, bias=bias.to(DEV), status=st)
+    y2 = ops.gemv_prepared(d["luts"], d["enc"], d["sm"], aux, x, 0, rows, in_features, bias=bias.to(DEV), status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    want = x.double().cpu() @ w.double().T + bias.double()
+    err = (y.double().cpu() - want).abs()
+    assert torch.all(err <= want.abs() * 2.0 ** -8 + 1e-5), float(err.max())
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
