@@ -115,6 +115,12 @@ __device__ __forceinline__ void sts8(uint32_t a, uint32_t v)
     asm volatile("st.shared.u8 [%0+%2], %1;" ::"r"(a), "r"(v), "n"(OFF) : "memory");
 }
 
+// ---- programmatic dependent launch: a kernel launched with the stream-serialization attribute
+// may start before the kernel ahead of it in the stream has ended; it must not touch that
+// kernel's results before grid_dependency_wait().  Both are no-ops in an ordinary launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA bulk copy global -> shared with mbarrier completion, one CTA as target ---------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
@@ -799,6 +805,9 @@ __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
         for (int i = tid; i < p.n_luts * 256; i += kFastThreads) smem[luts_off + i] = __ldg(p.luts + i);
     }
     __syncthreads();
+    // the tables above belong to the unit; the activations come from the kernel ahead in the stream
+    grid_launch_dependents();
+    grid_dependency_wait();
     FastTables tab;
     tab.dec_addr = smem_addr;
     tab.luts_addr = smem_addr + luts_off;
@@ -874,6 +883,7 @@ __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
 // One thread per output: the row's partial sums in order, bias, one rounding to bf16.
 __global__ void __launch_bounds__(256) df11_gemv_finish_kernel(const GemvArgs g, int m_count)
 {
+    grid_dependency_wait();
     const uint32_t i = blockIdx.x * 256u + threadIdx.x;
     if (i >= g.n_rows * (uint32_t)m_count) return;
     const uint32_t m = i / g.n_rows, row = i - m * g.n_rows;
@@ -1210,12 +1220,26 @@ int launch_gemv(Kernel kernel, int slot, int m_count, size_t smem, int64_t work_
             break;
         }
     }
-    kernel<<<(unsigned)grid, kFastThreads, smem, stream>>>(p, args);
-    if ((g.chunks_per_row >> args.run_log) > 1u) {
+    // Both kernels may start while the kernel ahead of them in the stream drains: the first
+    // loads its tables meanwhile, the second is in place when the first ends.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kFastThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kernel, p, args);
+    if (e == cudaSuccess && (g.chunks_per_row >> args.run_log) > 1u) {
         const unsigned outputs = g.n_rows * (unsigned)m_count;
-        df11_gemv_finish_kernel<<<(outputs + 255u) / 256u, 256, 0, stream>>>(args, m_count);
+        cfg.gridDim = dim3((outputs + 255u) / 256u);
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = 0;
+        e = cudaLaunchKernelEx(&cfg, df11_gemv_finish_kernel, args, m_count);
     }
-    e = cudaGetLastError();
     if (e != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     return DF11_OK;
 }
