@@ -304,6 +304,9 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="no CPU baseline / reference-kernel / e2e legs")
     ap.add_argument("--generation", action="store_true",
                     help="only: batch-1 greedy generation, DF11 vs uncompressed BF16, on the workload's model shape")
+    ap.add_argument("--fused-gemv", action="store_true",
+                    help="only: the matrix-vector products of one block at batch 1, fused with the decode "
+                         "(df11_gemv_prepared) against decode-then-torch GEMV")
     ap.add_argument("--new-tokens", type=int, default=512)
     ap.add_argument("--prompt-tokens", type=int, default=64)
     args = ap.parse_args()
@@ -314,6 +317,9 @@ def main():
         return
     if args.generation:
         run_generation(args, cfg)
+        return
+    if args.fused_gemv:
+        run_fused_gemv(args, cfg)
         return
 
     if not torch.cuda.is_available():
@@ -473,6 +479,75 @@ GEN_PATTERNS = {
                              "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj"],
     r"lm_head": [],
 }
+
+
+def run_fused_gemv(args, cfg):
+    """One block of the workload's shape, one activation vector: the block's products as the
+    package runs them with DF11_FUSED_GEMV=1 (q/k/v stacked, o, gate/up stacked, down: four
+    fused launches) against decode-then-GEMV (one decode, seven torch products).  CUDA events,
+    L2 flushed before every timed pass."""
+    import torch.nn.functional as F
+    from dfloat11_b200 import ops
+    dev = torch.device("cuda", 0)
+    shapes = block_shapes(cfg)
+    n = sum(a * b for a, b in shapes)
+    unit = make_unit(n, 0.02, 7, dev)
+    aux = ops.prepare(unit["luts"], unit["enc"], unit["pos"], unit["gaps"], n)
+    out = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    starts = [0]
+    for a, b in shapes:
+        starts.append(starts[-1] + a * b)
+    g = torch.Generator(device=dev).manual_seed(3)
+    x_h = torch.randn(1, cfg["hidden"], generator=g, device=dev).to(torch.bfloat16)
+    x_i = torch.randn(1, cfg["inter"], generator=g, device=dev).to(torch.bfloat16)
+    h, kv, it = cfg["hidden"], cfg["kv"], cfg["inter"]
+    stacked = [(starts[0], h + 2 * kv, h, x_h), (starts[3], h, h, x_h), (starts[4], 2 * it, h, x_h), (starts[6], h, it, x_i)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def decode():
+        ops.decode_prepared(unit["luts"], unit["enc"], unit["sm"], unit["pos"], unit["gaps"], aux, out=out)
+
+    def products():
+        for i, (a, b) in enumerate(shapes):
+            F.linear(x_i if b == it else x_h, out[starts[i]:starts[i + 1]].view(a, b))
+
+    def fused():
+        return [ops.gemv_prepared(unit["luts"], unit["enc"], unit["sm"], aux, x, first, rows, cols)
+                for first, rows, cols, x in stacked]
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 1)):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(args.steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / args.steps
+
+    decode()
+    ys = fused()
+    torch.cuda.synchronize()
+    worst = 0.0
+    for (first, rows, cols, x), y in zip(stacked, ys):
+        want = x.float() @ out[first:first + rows * cols].view(rows, cols).float().T
+        worst = max(worst, float(((y.float() - want).abs() / (want.abs() + 1e-3)).max()))
+    t_decode, t_products, t_fused = timed(decode), timed(products), timed(fused)
+    t_both = timed(lambda: (decode(), products()))
+    compressed = unit["n_bytes"] + n + aux.numel()
+    print(json.dumps({
+        "metric": "batch1_block_products_ms", "unit": "ms", "workload": cfg["name"], "elements": n,
+        "decode_then_gemv_ms": round(t_both, 4), "decode_ms": round(t_decode, 4), "bf16_gemv_ms": round(t_products, 4),
+        "fused_ms": round(t_fused, 4), "fused_launches": 4, "speedup_vs_decode_then_gemv": round(t_both / t_fused, 3),
+        "fused_vs_bf16_gemv": round(t_fused / t_products, 3),
+        "fused_GBps_of_compressed_bytes_read": round(compressed / t_fused / 1e6, 1),
+        "max_relative_difference_to_fp32_product": round(worst, 5), "steps": args.steps, "data": "synthetic",
+    }))
 
 
 def run_generation(args, cfg):
