@@ -8,11 +8,12 @@ from .codec import UnrepresentableError, encode_weights, get_codec, get_luts, sp
 from .dfloat11 import (DFloat11Model, TensorManager, compress_in_place, compress_model, get_hook,
                        get_no_split_classes,
                        load_and_replace_tensors)
-from .ops import aux_bytes, decode, decode_prepared, prepare
+from . import ops  # noqa: F401
+from .ops import aux_bytes, decode, decode_prepared, decode_rows_prepared, gemv_prepared, prepare
 
 __all__ = [
     "DFloat11Model", "TensorManager", "compress_in_place", "compress_model", "get_hook", "get_no_split_classes",
     "load_and_replace_tensors",
     "UnrepresentableError", "encode_weights", "get_codec", "get_luts", "split_bf16", "validate_unit",
-    "aux_bytes", "decode", "decode_prepared", "prepare",
+    "aux_bytes", "decode", "decode_prepared", "decode_rows_prepared", "gemv_prepared", "prepare", "ops",
 ]
