@@ -610,49 +610,19 @@ def run_generation(args, cfg):
         return total_us / 4 / 1e3
 
     def graph_generate():
-        """The same greedy generation with the host taken out of the loop: a static KV cache and
-        one CUDA graph per single-token step (the decode hooks run at capture time; their
-        launches through the C ABI are recorded like any other kernel).  Wall clock of
-        `new_tokens` replays, and the ids produced.  None when the capture is refused."""
-        from transformers import StaticCache
+        """The same greedy generation through the package's GraphedGreedyDecoder: a static KV
+        cache and one CUDA graph per single-token step (the decode hooks run at capture time).
+        Wall clock of prefill + `new_tokens` - 1 replays, and the ids produced."""
         n_prompt, n_new = ids.shape[1], args.new_tokens
         try:
-            with torch.no_grad():
-                cache = StaticCache(config=model.config, max_cache_len=n_prompt + n_new + 16)
-                logits = model(input_ids=ids, past_key_values=cache, cache_position=torch.arange(n_prompt, device=dev),
-                               use_cache=True).logits
-                tok = logits[:, -1:].argmax(-1)
-                pos = torch.tensor([n_prompt], device=dev)
-                produced = torch.zeros(n_new + 8, dtype=torch.int64, device=dev)
-                count = torch.zeros(1, dtype=torch.int64, device=dev)
-
-                def step():
-                    produced.index_copy_(0, count, tok.view(-1))
-                    lg = model(input_ids=tok, past_key_values=cache, cache_position=pos, use_cache=True).logits
-                    tok.copy_(lg[:, -1:].argmax(-1))
-                    pos.add_(1)
-                    count.add_(1)
-
-                side = torch.cuda.Stream(device=dev)
-                side.wait_stream(torch.cuda.current_stream(dev))
-                with torch.cuda.stream(side):
-                    for _ in range(2):
-                        step()
-                torch.cuda.current_stream(dev).wait_stream(side)
-                torch.cuda.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    step()
-                for _ in range(2):
-                    graph.replay()
-                torch.cuda.synchronize()
-                first = int(count.item())                       # steps taken before the timed ones
-                t0 = time.time()
-                for _ in range(n_new - first):
-                    graph.replay()
-                torch.cuda.synchronize()
-                dt = time.time() - t0
-                return dict(tok_s=(n_new - first) / dt, ids=produced[:n_new].cpu(), steps=n_new - first)
+            decoder = df11.GraphedGreedyDecoder(model, max_cache_len=n_prompt + n_new + 16)
+            decoder.generate(ids, 8)                            # warm-up steps and the capture
+            torch.cuda.synchronize()
+            t0 = time.time()
+            out = decoder.generate(ids, n_new)
+            torch.cuda.synchronize()
+            dt = time.time() - t0
+            return dict(tok_s=n_new / dt, ids=out[0, n_prompt:].cpu(), steps=n_new)
         except Exception as exc:                                # report, do not hide
             return dict(tok_s=None, ids=None, error=f"{type(exc).__name__}: {exc}"[:300])
 

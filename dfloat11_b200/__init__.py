@@ -9,6 +9,7 @@ from .dfloat11 import (DFloat11Model, TensorManager, compress_in_place, compress
                        get_no_split_classes,
                        load_and_replace_tensors)
 from . import ops  # noqa: F401
+from .generation import GraphedGreedyDecoder
 from .ops import aux_bytes, decode, decode_prepared, decode_rows_prepared, gemv_prepared, prepare
 
 __all__ = [
@@ -16,4 +17,5 @@ __all__ = [
     "load_and_replace_tensors",
     "UnrepresentableError", "encode_weights", "get_codec", "get_luts", "split_bf16", "validate_unit",
     "aux_bytes", "decode", "decode_prepared", "decode_rows_prepared", "gemv_prepared", "prepare", "ops",
+    "GraphedGreedyDecoder",
 ]

@@ -308,3 +308,48 @@ def test_fused_products_for_single_token_steps(monkeypatch):
     with torch.no_grad():                                         # switched off again: the usual path, bit-identical
         again = model(input_ids=ids).logits
     assert torch.equal(again, want)
+
+
+def _eager_static_greedy(model, ids, n_new, max_cache_len=64):
+    """The loop the graphed decoder captures, run eagerly: static KV cache, arg-max per step."""
+    from transformers import StaticCache
+    cache = StaticCache(config=model.config, max_cache_len=max_cache_len)
+    out = [ids]
+    with torch.no_grad():
+        logits = model(input_ids=ids, past_key_values=cache, cache_position=torch.arange(ids.shape[1], device=ids.device),
+                       use_cache=True).logits
+        tok = logits[:, -1:].argmax(-1)
+        pos = torch.tensor([ids.shape[1]], device=ids.device)
+        for _ in range(n_new - 1):
+            out.append(tok)
+            logits = model(input_ids=tok, past_key_values=cache, cache_position=pos, use_cache=True).logits
+            tok = logits[:, -1:].argmax(-1)
+            pos = pos + 1
+        out.append(tok)
+    return torch.cat(out, dim=1)
+
+
+@pytest.mark.gpu
+def test_graphed_greedy_decoder(saved):
+    """One CUDA graph per token gives the ids of the same loop run eagerly, for the DF11 model and
+    for the BF16 one (which agree with each other), on repeated calls and with an end-of-sequence id."""
+    path, reference = saved
+    model = df11.DFloat11Model.from_pretrained(path, device="cuda:0", bfloat16_model=tiny_llama(seed=7))
+    ref = copy.deepcopy(reference).to("cuda:0")
+    ids = torch.randint(0, 1024, (1, 9), generator=torch.Generator().manual_seed(8)).to("cuda:0")
+    other = torch.randint(0, 1024, (1, 5), generator=torch.Generator().manual_seed(9)).to("cuda:0")
+    want = _eager_static_greedy(ref, ids, 20)
+    want_other = _eager_static_greedy(ref, other, 7)
+    assert torch.equal(_eager_static_greedy(model, ids, 20), want)
+    for m in (model, ref):
+        decoder = df11.GraphedGreedyDecoder(m, max_cache_len=64)
+        assert torch.equal(decoder.generate(ids, 20), want)
+        assert torch.equal(decoder.generate(ids, 20), want)                  # the captured graph is reused
+        assert torch.equal(decoder.generate(ids, 1), want[:, :10])
+        assert torch.equal(decoder.generate(other, 7), want_other)
+        eos = int(want[0, 9 + 6])
+        got = decoder.generate(ids, 20, eos_token_id=eos, eos_check_every=4)
+        first = int((want[0, 9:] == eos).nonzero()[0])
+        assert torch.equal(got, want[:, :9 + first + 1])
+    with pytest.raises(ValueError):
+        decoder.generate(ids, 100)
