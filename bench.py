@@ -307,6 +307,8 @@ def main():
     ap.add_argument("--fused-gemv", action="store_true",
                     help="only: the matrix-vector products of one block at batch 1, fused with the decode "
                          "(df11_gemv_prepared) against decode-then-torch GEMV")
+    ap.add_argument("--cpu-offload", action="store_true",
+                    help="with --generation: DF11 with cpu_offload=True at --batch sequences against resident BF16")
     ap.add_argument("--new-tokens", type=int, default=512)
     ap.add_argument("--prompt-tokens", type=int, default=64)
     args = ap.parse_args()
@@ -578,7 +580,7 @@ def run_generation(args, cfg):
         for name, p in model.named_parameters():
             if p.dim() == 2:
                 p.normal_(0.0, 1.0 if "embed_tokens" in name else 0.02)
-    ids = torch.randint(0, common["vocab_size"], (1, args.prompt_tokens), device=dev,
+    ids = torch.randint(0, common["vocab_size"], (args.batch if args.cpu_offload else 1, args.prompt_tokens), device=dev,
                         generator=torch.Generator(device=dev).manual_seed(2))
 
     def timed_generate():
@@ -625,6 +627,32 @@ def run_generation(args, cfg):
             return dict(tok_s=n_new / dt, ids=out[0, n_prompt:].cpu(), steps=n_new)
         except Exception as exc:                                # report, do not hide
             return dict(tok_s=None, ids=None, error=f"{type(exc).__name__}: {exc}"[:300])
+
+    if args.cpu_offload:
+        # Compressed tensors in pinned host memory, one block's worth in HBM at a time (the
+        # reference's cpu_offload=True): every generated token moves the whole compressed model
+        # over PCIe, overlapped with decode by the hook's side stream.
+        from dfloat11_b200.dfloat11 import _OffloadStager
+        out_bf16, t_bf16 = timed_generate()
+        mem_bf16 = torch.cuda.max_memory_allocated() / 1e9
+        df11.compress_in_place(model, GEN_PATTERNS, cpu_offload=True)
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+        out_df11, t_df11 = timed_generate()
+        mem_df11 = torch.cuda.max_memory_allocated() / 1e9
+        stats = _OffloadStager.get(dev).stats
+        tokens = args.batch * args.new_tokens
+        print(json.dumps({
+            "metric": "offload_generation_tok_per_s", "unit": "tok/s", "workload": cfg["name"], "batch": args.batch,
+            "prompt_tokens": args.prompt_tokens, "new_tokens": args.new_tokens,
+            "harness": "transformers generate, greedy, eager; DF11 with cpu_offload (compressed tensors in pinned host memory)",
+            "bf16_resident_tok_s": round(tokens / t_bf16, 2), "df11_offload_tok_s": round(tokens / t_df11, 2),
+            "df11_offload_s_per_step": round(t_df11 / args.new_tokens, 4),
+            "identical_tokens": bool(torch.equal(out_bf16, out_df11)),
+            "peak_mem_GB": {"bf16_resident": round(mem_bf16, 2), "df11_offload": round(mem_df11, 2)},
+            "h2d_GB": round(stats["h2d_bytes"] / 1e9, 2), "prefetch_hits": stats["prefetch_hits"], "data": "synthetic",
+        }))
+        return
 
     out_bf16, t_bf16 = timed_generate()
     gpu_bf16 = gpu_ms_per_token()
