@@ -49,7 +49,13 @@ ONE_BLOCK = dict(name="one-llama-block", layers=1, hidden=4096, kv=1024, inter=1
 # Llama-3.1-405B shapes, tensor-parallel over the ranks of the job: every rank holds 1/T of each
 # block's seven matrices as one unit and decodes only that; two activation all-reduces per layer.
 LLAMA_405B_TP = dict(name="llama3.1-405b-shape-tp", layers=126, hidden=16384, kv=1024, inter=53248, vocab=0, tp=True)
-WORKLOADS = {"qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "small": SMALL, "block": ONE_BLOCK,
+# FLUX.1-dev-shaped diffusion transformer (hidden 3072, MLP ratio 4): 19 double-stream units of 14
+# matrices (339.7 M weights) and 38 single-stream units of 6 matrices (141.6 M); one pass over all
+# 57 units is the weight decode of one denoising step.
+FLUX_DIT = dict(name="flux1-dev-shape", layers=57, hidden=3072, kv=3072, inter=12288, vocab=0,
+                unit_sizes=[2 * 3072 * 18432 + 8 * 3072 * 3072 + 4 * 3072 * 12288] * 19
+                + [3072 * 9216 + 3072 * 12288 + 15360 * 3072 + 3 * 3072 * 3072] * 38)
+WORKLOADS = {"flux-dit": FLUX_DIT, "qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "small": SMALL, "block": ONE_BLOCK,
              "llama-405b-tp": LLAMA_405B_TP}
 
 
@@ -60,6 +66,8 @@ def block_shapes(cfg):
 
 def unit_plan(cfg):
     """(name, n_elements, std) of every compressed unit in forward order."""
+    if cfg.get("unit_sizes"):
+        return [(f"layers.{i}", n, 0.02) for i, n in enumerate(cfg["unit_sizes"])]
     n_block = sum(a * b for a, b in block_shapes(cfg))
     plan = [(f"layers.{i}", n_block, 0.02) for i in range(cfg["layers"])]
     if cfg["vocab"]:
