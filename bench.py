@@ -434,7 +434,7 @@ def main():
         "config": {
             "workload": cfg["name"], "units_per_step": len(units), "elements_per_step": step_elems,
             "algorithmic_bytes_per_step": step_bytes, "bytes_per_element": round(step_bytes / step_elems, 4),
-            "path": "df11_decode_prepared", "l2": "inputs larger than L2 (every unit >= 600 MB of traffic)",
+            "path": "df11_decode_prepared", "l2": f"inputs larger than L2 (every unit >= {min(algorithmic_bytes(u) for u in units) // 10**6} MB of traffic)",
             "per_gpu_GBps": round(value / world, 1), "setup_s": round(setup_s, 1),
             **({"parallelism": f"tp{world}", "layers_resident": len(units), "all_reduces_per_step": 2 * len(units),
                 "all_reduce_shape": [args.batch, cfg["hidden"]],
