@@ -805,9 +805,11 @@ __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
         for (int i = tid; i < p.n_luts * 256; i += kFastThreads) smem[luts_off + i] = __ldg(p.luts + i);
     }
     __syncthreads();
-    // the tables above belong to the unit; the activations come from the kernel ahead in the stream
+    // Tables, seek points, stream and sign/mantissa bytes belong to the unit and may be read while
+    // the kernel ahead in the stream still runs; the activations are its result, and the scratch
+    // and the output may still be in use by it: the sink waits before it touches any of them.
     grid_launch_dependents();
-    grid_dependency_wait();
+    bool waited = false;
     FastTables tab;
     tab.dec_addr = smem_addr;
     tab.luts_addr = smem_addr + luts_off;
@@ -834,6 +836,10 @@ __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
         p, tab, lane, my_items << run_log,
         [&](uint32_t j) { return g.first_chunk + ((gw + (j >> run_log) * warps) << run_log) + (j & (run - 1u)); },
         n_words, bad, [&](uint32_t j, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &sm) {
+            if (!waited) {
+                grid_dependency_wait();
+                waited = true;
+            }
             uint32_t w[8];
             df11_merge4(e0, sm.x, &w[0], &w[1]);
             df11_merge4(e1, sm.y, &w[2], &w[3]);
