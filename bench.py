@@ -400,22 +400,28 @@ def main():
     step_bytes = sum(algorithmic_bytes(u) for u in units)
     step_elems = sum(u["n_elements"] for u in units)
 
-    def timed(fn, steps, warmup):
+    step_spread = {}
+
+    def timed(fn, steps, warmup, spread_key=None):
         for _ in range(warmup):
             fn()
         barrier(world, device)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(steps):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        marks[0].record()
+        for i in range(steps):
             fn()
-        b.record()
+            marks[i + 1].record()
         barrier(world, device)
-        return all_max(a.elapsed_time(b) / steps, world, device)
+        if spread_key:                                  # per-step times on this rank, for median and min
+            per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+            step_spread[spread_key] = {"min": round(per_step[0], 4), "median": round(per_step[len(per_step) // 2], 4),
+                                       "max": round(per_step[-1], 4)}
+        return all_max(marks[0].elapsed_time(marks[-1]) / steps, world, device)
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms = timed(lambda: step(True), args.steps, args.warmup)
+    ms = timed(lambda: step(True), args.steps, args.warmup, spread_key="prepared")
     clocks = sampler.stop() if rank == 0 else None
     ms_two_pass = timed(lambda: step(False), max(1, args.steps // 2), max(3, args.warmup))
     total_bytes = all_sum(step_bytes, world, device)
@@ -429,6 +435,7 @@ def main():
     result = {
         "metric": "df11_bf16_decompress_GBps", "value": round(value, 1), "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "ms_per_step_spread": step_spread.get("prepared"),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8/u16 integer",
         "data": "synthetic",
         "config": {
