@@ -39,6 +39,11 @@ SIGNATURES = {
     "df11_decode_static": (c_int32, [c_void_p] * 6 + [c_int32, c_int64, c_int64, c_void_p, c_int32, c_void_p]),
     "df11_validate_host": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "df11_encode_size": (c_int64, [c_void_p, c_int64, c_void_p]),
+    "df11_encode_device_workspace_bytes": (c_int64, [c_int64]),
+    "df11_encode_device_count": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                           c_int32, c_void_p]),
+    "df11_encode_device_pack": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_int32, c_uint32, c_void_p, c_void_p,
+                                          c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p]),
     "df11_encode_host": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_int32, c_uint32, c_void_p, c_int64,
                                    c_void_p, c_int64, c_void_p, c_int64, c_int32]),
 }

@@ -226,6 +226,33 @@ int df11_encode_host(const void *exponents, int64_t n_elements, const void *code
                      int64_t n_bytes, void *gaps, int64_t n_gap_bytes, void *output_positions,
                      int64_t n_positions, int32_t n_threads);
 
+/*
+ * The same bit packer on the GPU, for exponent bytes that are already in device memory
+ * (a freshly loaded BF16 model): same outputs, byte for byte, as df11_encode_host.
+ * Two steps, because the size of the stream is only known after a first pass:
+ *   df11_encode_device_count()  queues the size pass and copies the total number of stream
+ *                               BITS to *total_bits_host (8 bytes, host memory); synchronise
+ *                               the stream before reading it;
+ *   df11_encode_device_pack()   fills codes (4-byte aligned, room for n_bytes rounded up to a
+ *                               multiple of 4), gaps and output_positions (4-byte aligned),
+ *                               all caller-owned DEVICE buffers sized from that total.
+ * `exponents` is device memory; `code_len` / `code_val` are HOST arrays of 256 entries, as for
+ * df11_encode_host; `workspace` is caller-owned device memory of
+ * df11_encode_device_workspace_bytes() bytes, 8-byte aligned, kept untouched between the two
+ * steps.  A value that occurs but has no code sets DF11_STATUS_BAD_TABLE in `status`.
+ * No counterpart in the reference, which packs on the CPU in Python.
+ */
+int64_t df11_encode_device_workspace_bytes(int64_t n_elements);
+
+int df11_encode_device_count(const void *exponents, int64_t n_elements, const void *code_len,
+                             const void *code_val, void *workspace, int64_t workspace_bytes,
+                             void *total_bits_host, void *status, int32_t device, void *stream);
+
+int df11_encode_device_pack(const void *exponents, int64_t n_elements, const void *code_len,
+                            const void *code_val, int32_t pad_len, uint32_t pad_val, void *workspace,
+                            void *codes, int64_t n_bytes, void *gaps, int64_t n_gap_bytes,
+                            void *positions, int64_t n_positions, int32_t device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -396,3 +396,43 @@ def test_fused_product_with_longer_runs(rows, in_features):
     err = (y.double().cpu() - want).abs()
     assert torch.all(err <= want.abs() * 2.0 ** -8 + 1e-5), float(err.max())
     assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+
+
+@pytest.mark.parametrize("n", [1, 15, 4095, 4096, 4097, 100_003, (1 << 20) + 5])
+@pytest.mark.parametrize("case", ["gaussian", "one_bit_codes", "eight_bit_codes", "deep_codes"])
+def test_gpu_bit_packer_is_byte_identical_to_the_host_packer(n, case):
+    """df11_encode_device_* against df11_encode_host (itself pinned to the reference's `encode`
+    by the CPU tests): stream, gaps and output positions, with and without a padding code."""
+    rng = np.random.default_rng(n + len(case))
+    if case == "gaussian":
+        e = np.clip(np.rint(rng.normal(120, 2.5, size=n)), 1, 239).astype(np.uint8)
+    elif case == "one_bit_codes":
+        e = ((rng.random(n) < 0.9).astype(np.uint8) * 3 + 100).astype(np.uint8)
+    elif case == "eight_bit_codes":
+        e = rng.integers(0, 240, size=n).astype(np.uint8)
+    else:
+        p = 0.5 ** np.arange(1, 41)
+        e = rng.choice(np.arange(60, 100), size=n, p=p / p.sum()).astype(np.uint8)
+    hist = np.bincount(e, minlength=256)
+    if (hist > 0).sum() < 2:                                   # a one-symbol alphabet still needs a code
+        hist[(int(e[0]) + 1) % 240] += 1
+    lens = codec.code_lengths(hist)
+    vals = codec.canonical_codes(lens)
+    for pad in ((0, 0), (5, 0b10110), (2, 3), (32, 0xDEADBEEF)):
+        enc_h, gaps_h, pos_h = codec.pack_exponents(e, lens, vals, n_threads=3, pad=pad)
+        enc_d, gaps_d, pos_d = codec.pack_exponents_gpu(torch.from_numpy(e).to(DEV), lens, vals, pad=pad)
+        assert np.array_equal(enc_d.cpu().numpy(), enc_h)
+        assert np.array_equal(gaps_d.cpu().numpy(), gaps_h)
+        assert np.array_equal(pos_d.cpu().numpy().view(np.uint32), pos_h)
+
+
+def test_encode_weights_on_the_gpu_round_trips():
+    g = torch.Generator().manual_seed(77)
+    w = (torch.randn(700_001, generator=g) * 0.02).to(torch.bfloat16)
+    on_host = codec.encode_weights([w])
+    on_gpu = codec.encode_weights([w.to(DEV)])
+    for k in on_host:
+        assert torch.equal(on_host[k], on_gpu[k]), k
+    d = {k: v.to(DEV) for k, v in on_gpu.items() if k != "split_positions"}
+    out = ops.decode(d["luts"], d["encoded_exponent"], d["sign_mantissa"], d["output_positions"], d["gaps"])
+    assert torch.equal(out.cpu().view(torch.int16), w.view(torch.int16))
