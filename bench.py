@@ -96,17 +96,18 @@ def make_unit(n_elements, std, seed, device, keep_host=False, n_threads=None):
     lens = codec.code_lengths(hist)
     vals = codec.canonical_codes(lens)
     luts = codec.build_luts(lens, vals)
-    encoded, gaps, positions = codec.pack_exponents(exponent.cpu().numpy(), lens, vals, n_threads)
+    enc_d, gaps_d, pos_d = codec.pack_exponents_gpu(exponent, lens, vals)      # the package's GPU bit packer
     del exponent
+    positions = pos_d.cpu().numpy().view(np.uint32)
     unit = dict(
-        luts=torch.from_numpy(luts).to(device), enc=torch.from_numpy(encoded).to(device),
-        sm=sign_mantissa, pos=torch.from_numpy(positions.view(np.uint8).copy()).to(device),
-        gaps=torch.from_numpy(gaps).to(device), n_elements=n_elements, n_bytes=int(encoded.size),
+        luts=torch.from_numpy(luts).to(device), enc=enc_d, sm=sign_mantissa, pos=pos_d.view(torch.uint8),
+        gaps=gaps_d, n_elements=n_elements, n_bytes=int(enc_d.numel()),
         widest=int(np.diff(positions.astype(np.int64)).max()),
         checksum=int(w.view(torch.int16).to(torch.int64).sum().item()),
     )
     if keep_host:
-        unit["host"] = dict(luts=luts, enc=encoded, sm=sign_mantissa.cpu().numpy(), pos=positions, gaps=gaps)
+        unit["host"] = dict(luts=luts, enc=enc_d.cpu().numpy(), sm=sign_mantissa.cpu().numpy(), pos=positions,
+                            gaps=gaps_d.cpu().numpy())
     return unit
 
 

@@ -876,6 +876,8 @@ def compress_model(
                 break
 
             weights = _unit_weights(full_name, sub_module, attr_names)
+            if torch.cuda.is_available() and os.environ.get("DF11_HOST_ENCODER", "0") != "1":
+                weights = [w.to("cuda:0") for w in weights]      # packed there: same bytes, far less time
             tensors = codec.encode_weights(weights)
             n = tensors["sign_mantissa"].numel()
             stored = sum(tensors[k].numel() for k in ("encoded_exponent", "sign_mantissa", "output_positions", "gaps"))
