@@ -817,7 +817,7 @@ def _unit_weights(full_name: str, sub_module: nn.Module, attr_names) -> List[tor
         assert target.weight.data.dtype == torch.bfloat16, \
             f"Expected weights to be in bfloat16 format for compression, but '{where}' has dtype " \
             f"{target.weight.data.dtype}"
-        weights.append(target.weight.data.detach().cpu().flatten())
+        weights.append(target.weight.data.detach().flatten())        # stays where it is: a GPU packs there
         delattr(target, "weight")
     return weights
 
@@ -831,8 +831,8 @@ def check_unit(tensors: Dict[str, torch.Tensor], weights: List[torch.Tensor], de
                                  tensors["output_positions"], tensors["gaps"])
     out = ops.decode(d["luts"], d["encoded_exponent"], d["sign_mantissa"], d["output_positions"], d["gaps"],
                      max_block_elems=widest)
-    want = torch.cat([w.reshape(-1) for w in weights]).view(torch.int16)
-    return bool(torch.equal(out.cpu().view(torch.int16), want))
+    want = torch.cat([w.reshape(-1) for w in weights]).view(torch.int16).to(out.device)
+    return bool(torch.equal(out.view(torch.int16), want))
 
 
 def compress_model(
