@@ -750,8 +750,8 @@ def run_e2e(units, scratch, status, device, world, args):
     from dfloat11_b200.dfloat11 import TensorManager, _OffloadStager
     TensorManager._tensors[(device, 0)] = scratch     # same scratch as the resident runs
     hook = df11.get_hook((512,), 8)
-    # pinned host memory is bounded (24 GB per rank): the workload's first units up to that size
-    budget, kept = 24e9, []
+    # pinned host memory is bounded (24 GB per rank, 64 GB per job): the workload's first units up to that size
+    budget, kept = min(24e9, 64e9 / world), []
     for u in units:
         budget -= u["n_bytes"] + u["n_elements"]
         if budget < 0 and len(kept) >= 2:
