@@ -2,7 +2,7 @@
 
 Run in the build container only (needs the read-only reference checkout):
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [path of the reference checkout]
 
 The reference's ``dfloat11/dfloat11_utils.py`` is imported unmodified, by file
 path.  Its one missing dependency, the third-party ``dahuffman`` package
