@@ -353,54 +353,133 @@ DF11_HD void df11_mark_window(const M &m, int n_luts, uint32_t w0, uint32_t w1, 
     }
 }
 
-// Decodes the EPT codes of one group and hands them over four at a time, packed lowest
-// byte first.  The group's first code starts `bit` (0..31) bits into stream word
-// `word_index` (32-bit big-endian words; streams up to 16 GiB).  A lane with no group to
-// decode passes active = false.  (The fast kernel runs this loop as hand-scheduled device
-// code, df11_decode.cu; this is the statement of the algorithm and the form the CPU tests run.)
+// Low 32 bits of (hi:lo) >> min(s, 32).
+DF11_HD uint32_t df11_funnel_rc(uint32_t lo, uint32_t hi, uint32_t s)
+{
+#ifdef __CUDA_ARCH__
+    return __funnelshift_rc(lo, hi, s);
+#else
+    if (s >= 32u) return hi;
+    return s ? (lo >> s) | (hi << (32u - s)) : lo;
+#endif
+}
+
+// The exponents a thread has decoded, as a 20-byte shift register x0 (lowest) .. x4: every
+// table probe shifts it right by as many bytes as the entry has symbols and enters them at the
+// top, first symbol lowest.  After c codes (16 <= c <= 19: the last probe may run up to three
+// codes past the sixteenth) code k sits at byte 20 - c + k, so the sixteen wanted bytes are the
+// register shifted right by 20 - c bytes, and the c - 16 extra codes stay at the top of x4.
+struct Df11ExpShift {
+    uint32_t x0, x1, x2, x3, x4;
+    DF11_HD void push(uint32_t syms, uint32_t bits)  // bits = 8 * symbols, 0..32
+    {
+        x0 = df11_funnel_rc(x0, x1, bits);
+        x1 = df11_funnel_rc(x1, x2, bits);
+        x2 = df11_funnel_rc(x2, x3, bits);
+        x3 = df11_funnel_rc(x3, x4, bits);
+        x4 = df11_funnel_rc(x4, syms, bits);
+    }
+    // the sixteen exponents, four per word, lowest byte first; acc as described at DF11_FAST_ESCAPE
+    DF11_HD void take(uint32_t acc, uint32_t *e0, uint32_t *e1, uint32_t *e2, uint32_t *e3) const
+    {
+        const uint32_t bits = 160u - ((acc >> 16) & 0xFFu);  // 8 * (20 - codes done): 8..32
+        *e0 = df11_funnel_rc(x0, x1, bits);
+        *e1 = df11_funnel_rc(x1, x2, bits);
+        *e2 = df11_funnel_rc(x2, x3, bits);
+        *e3 = df11_funnel_rc(x3, x4, bits);
+    }
+};
+
+// Fast-decoder form of a decode-table entry's first word: bits consumed in bits 0..7 (at most
+// 31), eight times the number of symbols in bits 16..23; an entry that needs the full walk is
+// DF11_FAST_ESCAPE alone.  The running state `acc` of a thread is the sum of the entries it used:
+//   bits 0..7   position in the window (64 and more: window used up)
+//   bit 15      an escape entry was met
+//   bits 16..23 8 * codes done (128 and more: the sixteen codes of this pass are done)
+#define DF11_FAST_ESCAPE (1u << 15)
+#define DF11_FAST_DONE (128u << 16)
+#define DF11_FAST_LEAVE (DF11_FAST_ESCAPE | DF11_FAST_DONE | 64u)
+
+DF11_HD constexpr uint32_t df11_fast_meta(uint32_t meta)
+{
+    return (meta == DF11_DEC_ESCAPE || (meta & 0xFFu) > 31u) ? DF11_FAST_ESCAPE
+                                                             : (meta & 0xFFu) | (((meta >> 8) & 7u) << 19);
+}
+
+// Decodes the EPT codes of one group sixteen at a time and hands them over four per word,
+// lowest byte first.  The group's first code starts `bit` (0..31) bits into stream word
+// `word_index` (32-bit big-endian words; streams up to 16 GiB).  This is the statement of the
+// fast kernel's algorithm, instruction for instruction in its arithmetic (the kernel runs the
+// inner loop as hand-scheduled device code, df11_decode.cu), and the form the CPU tests run.
 // Extra policy members:
 //   uint32_t M::word(i)            stream bytes [4i, 4i+4) as a big-endian word, 0 past the end
 //   void     M::flush(k, word)     exponents 4k .. 4k+3 of the group
 //
-// The 96-bit window is shifted so that the next code to decode is at position 0 whenever
-// it is (re)loaded; a group of 16 codes rarely needs more than the 64 positions that
-// gives, so the reload inside the loop is the exception, not the rule.
+// The 96-bit window w0:w1:w2 is kept shifted so that the next code starts at its top bit; a
+// group of 16 codes rarely needs more than the 64 positions that gives, so the reload inside
+// the loop is the exception, not the rule.
 template <int K, int EPT, class M>
 DF11_HD void df11_decode_group(const M &m, int n_luts, uint32_t word_index, uint32_t bit, bool active, int *bad)
 {
-    constexpr uint32_t kDone = (uint32_t)EPT << 8;
-    uint32_t w0 = 0, w1 = 0, w2 = 0;
-    uint32_t acc = active ? 64u : kDone;  // pos | codes done << 8; pos >= 64 asks for a (re)load
-    uint32_t q = 0;                       // fewer than four pending exponents, lowest byte first
-    word_index -= 2u;                     // the first load advances by the 64 positions pretended above
-    while (acc < kDone) {
-        {
-            if (acc & 64u) {
-                // (re)load: the window starts at the code the position has reached
-                const uint32_t at = bit + (acc & 0x7Fu);  // position 64..127 relative to the old window
+    if (!active) return;
+    uint32_t w0, w1, w2;
+    auto load = [&]() {
+        const uint32_t a = m.word(word_index), b = m.word(word_index + 1u);
+        const uint32_t c = m.word(word_index + 2u), d = m.word(word_index + 3u);
+        w0 = df11_funnel_l(b, a, bit);
+        w1 = df11_funnel_l(c, b, bit);
+        w2 = df11_funnel_l(d, c, bit);
+    };
+    auto shift = [&](uint32_t len) {  // window <<= len, 0 <= len <= 31
+        w0 = df11_funnel_l(w1, w0, len);
+        w1 = df11_funnel_l(w2, w1, len);
+        w2 = len ? w2 << len : w2;
+    };
+    Df11ExpShift X = {0, 0, 0, 0, 0};
+    uint32_t acc = 0;
+    for (int part = 0; part < EPT / 16; ++part) {
+        if (part > 0) {  // go on where the previous sixteen stopped; codes decoded beyond them are at the top of X
+            const uint32_t at = bit + (acc & 0x7Fu);
+            word_index += at >> 5;
+            bit = at & 31u;
+            acc = (acc & ~0xFFu) - DF11_FAST_DONE;
+        }
+        load();
+        for (;;) {
+            while ((acc & DF11_FAST_LEAVE) == 0u) {  // the probe loop
+                const Df11Entry e = m.dec(w0 >> (32 - K));
+                const uint32_t meta = df11_fast_meta(e.meta);
+                X.push(e.syms, meta >> 16);
+                shift(meta & 31u);
+                acc += meta;
+            }
+            if ((acc & (DF11_FAST_ESCAPE | 64u)) == 0u) break;  // 16 codes done, nothing special
+            if (acc & DF11_FAST_ESCAPE) {  // the table could not resolve this code from K bits: full walk
+                acc -= DF11_FAST_ESCAPE;
+                uint32_t len;
+                const uint32_t sym = df11_walk_m(m, n_luts, w0, &len, bad);
+                X.push(sym, 8u);
+                acc += len | (8u << 16);
+                if (len < 32u) {
+                    shift(len);
+                } else {  // a 32-bit code, or an unusable table (len 64): the reload below follows
+                    w0 = w1, w1 = w2, w2 = 0;
+                }
+            }
+            if (acc & DF11_FAST_DONE) break;  // 16 codes done (the position may be past 63)
+            if (acc & 64u) {                  // position 64..127: reload the window where the position has got to
+                const uint32_t at = bit + (acc & 0x7Fu);
                 word_index += at >> 5;
                 bit = at & 31u;
-                const uint32_t a = m.word(word_index), b = m.word(word_index + 1u);
-                const uint32_t c = m.word(word_index + 2u), d = m.word(word_index + 3u);
-                w0 = df11_funnel_l(b, a, bit);
-                w1 = df11_funnel_l(c, b, bit);
-                w2 = df11_funnel_l(d, c, bit);
+                load();
                 acc &= ~0xFFu;
             }
-            const uint32_t x = df11_peek(w0, w1, w2, acc);
-            Df11Entry e = m.dec(x >> (32 - K));
-            if (e.meta == DF11_DEC_ESCAPE) {
-                uint32_t len;
-                e.syms = df11_walk_m(m, n_luts, x, &len, bad);
-                e.meta = len | 256u;
-            }
-            const uint32_t sh = (acc >> 5) & 0x18u;  // 8 * (codes done mod 4)
-            const uint32_t lo = q | (e.syms << sh);
-            const uint32_t old = acc;
-            acc += e.meta;
-            const bool complete = ((acc ^ old) & 0xFC00u) != 0u;  // the count crossed a multiple of four
-            if (complete) m.flush((old >> 10) & 0x3Fu, lo);
-            q = complete ? df11_funnel_l(e.syms, 0u, sh) : lo;  // exponents that did not fit / all pending
         }
+        uint32_t e0, e1, e2, e3;
+        X.take(acc, &e0, &e1, &e2, &e3);
+        m.flush(4u * part + 0u, e0);
+        m.flush(4u * part + 1u, e1);
+        m.flush(4u * part + 2u, e2);
+        m.flush(4u * part + 3u, e3);
     }
 }

@@ -313,47 +313,14 @@ struct FastTables {
     __device__ __forceinline__ uint32_t lut(uint32_t i) const { return lds8(luts_addr + i); }
 };
 
-// The exponents a thread has decoded, as a 20-byte shift register x0 (lowest) .. x4: every
-// table probe shifts it right by as many bytes as the entry has symbols and enters them at the
-// top, first symbol lowest.  After c codes (16 <= c <= 19: the last probe may run up to three
-// codes past the sixteenth) code k sits at byte 20 - c + k, so the sixteen wanted bytes are the
-// register shifted right by 20 - c bytes, and the c - 16 extra codes stay at the top of x4.
-struct ExpShift {
-    uint32_t x0, x1, x2, x3, x4;
-    __device__ __forceinline__ void push(uint32_t syms, uint32_t bits)  // bits = 8 * symbols, 0..32
-    {
-        x0 = __funnelshift_rc(x0, x1, bits);
-        x1 = __funnelshift_rc(x1, x2, bits);
-        x2 = __funnelshift_rc(x2, x3, bits);
-        x3 = __funnelshift_rc(x3, x4, bits);
-        x4 = __funnelshift_rc(x4, syms, bits);
-    }
-    // the sixteen exponents, four per word, lowest byte first; acc as described below
-    __device__ __forceinline__ void take(uint32_t acc, uint32_t &e0, uint32_t &e1, uint32_t &e2, uint32_t &e3) const
-    {
-        const uint32_t bits = 160u - ((acc >> 16) & 0xFFu);  // 8 * (20 - codes done): 8..32
-        e0 = __funnelshift_rc(x0, x1, bits);
-        e1 = __funnelshift_rc(x1, x2, bits);
-        e2 = __funnelshift_rc(x2, x3, bits);
-        e3 = __funnelshift_rc(x3, x4, bits);
-    }
-};
-
-// Fast-decoder form of a decode-table entry's first word: bits consumed in bits 0..7 (at most
-// 31), eight times the number of symbols in bits 16..23; an entry that needs the full walk is
-// kFastEscape alone.  The running state `acc` of a thread is the sum of the entries it used:
-//   bits 0..7   position in the window (64 and more: window used up)
-//   bit 15      an escape entry was met
-//   bits 16..23 8 * codes done (128 and more: the sixteen codes of this pass are done)
-constexpr uint32_t kFastEscape = 1u << 15;
-constexpr uint32_t kFastDone = 128u << 16;
-constexpr uint32_t kFastLeave = kFastEscape | kFastDone | 64u;
-
-__host__ __device__ constexpr uint32_t fast_meta(uint32_t meta)
-{
-    return (meta == DF11_DEC_ESCAPE || (meta & 0xFFu) > 31u) ? kFastEscape
-                                                             : (meta & 0xFFu) | (((meta >> 8) & 7u) << 19);
-}
+// The exponent shift register (Df11ExpShift), the fast entry format (df11_fast_meta) and the
+// meaning of the running state `acc` are defined in df11_common.h, where the CPU tests run the
+// same arithmetic.
+using ExpShift = Df11ExpShift;
+constexpr uint32_t kFastEscape = DF11_FAST_ESCAPE;
+constexpr uint32_t kFastDone = DF11_FAST_DONE;
+constexpr uint32_t kFastLeave = DF11_FAST_LEAVE;
+__host__ __device__ constexpr uint32_t fast_meta(uint32_t meta) { return df11_fast_meta(meta); }
 
 // The probe loop of the fast decoder (the device form of df11_decode_group's inner loop,
 // df11_common.h, for 16 codes).  The 96-bit window w0:w1:w2 is kept shifted so that the next
@@ -500,7 +467,7 @@ __device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &ta
             }
         }
         uint32_t e0, e1, e2, e3;
-        X.take(acc, e0, e1, e2, e3);
+        X.take(acc, &e0, &e1, &e2, &e3);
         sink(t, e0, e1, e2, e3, cur.sm);
     };
     Inputs a, b;
@@ -720,7 +687,7 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
             }
 
             uint32_t e0, e1, e2, e3;
-            X.take(acc, e0, e1, e2, e3);
+            X.take(acc, &e0, &e1, &e2, &e3);
             if (whole && vec) {
                 uint4 r0, r1;
                 df11_merge4(e0, m.x, &r0.x, &r0.y);
