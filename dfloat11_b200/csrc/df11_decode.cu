@@ -52,7 +52,7 @@ constexpr int kWarps = kThreads / 32;
 #define DF11_FAST_MIN_CTAS 4
 #endif
 #ifndef DF11_GEMV_MIN_CTAS
-#define DF11_GEMV_MIN_CTAS 3
+#define DF11_GEMV_MIN_CTAS 4
 #endif
 constexpr int kTableBits = DF11_TABLE_BITS;           // K of the self-contained decoder and the seek-point pass
 constexpr int kFastTableBits = DF11_FAST_TABLE_BITS;  // K of the fast decoder (its table is larger, its CTAs smaller)
@@ -1180,15 +1180,22 @@ int launch_gemv(Kernel kernel, int slot, int m_count, size_t smem, int64_t work_
     int64_t grid = (int64_t)info.sm_count * per_sm;
     if (grid > work_items) grid = work_items;
     if (grid < 1) grid = 1;
-    // longest run (8, 4, 2, 1 chunks, dividing the row) whose items still fill the warps' rounds to 85 %
+    // Longest run (8, 4, 2, 1 chunks, dividing the row) that keeps the warps busy: either there
+    // are no more items than resident warps (then the grid shrinks to one item per warp: no
+    // partly filled last round), or the items fill the warps' rounds to 85 %.
     GemvArgs args = g;
     const int64_t warps = grid * (kFastThreads / 32);
     args.run_log = 0;
-    for (int log = 3; log > 0; --log) {
+    for (int log = 3; log >= 0; --log) {
         if (g.chunks_per_row % (1u << log)) continue;
         const int64_t items = (int64_t)g.n_rows * (g.chunks_per_row >> log);
+        if (items <= warps) {
+            args.run_log = (uint32_t)log;
+            grid = (items + kFastThreads / 32 - 1) / (kFastThreads / 32);
+            break;
+        }
         const int64_t rounds = (items + warps - 1) / warps;
-        if (items * 100 >= rounds * warps * 85) {
+        if (log == 0 || items * 100 >= rounds * warps * 85) {
             args.run_log = (uint32_t)log;
             break;
         }

@@ -375,11 +375,13 @@ def test_fused_matrix_vector_product(m):
         ops.gemv_prepared(d["luts"], d["enc"], d["sm"], aux, x[:, :1000].contiguous(), 0, 16, 1000)   # not a multiple of 512
 
 
-@pytest.mark.parametrize("rows,in_features", [(10656, 1024), (5328, 2048), (7104, 2048), (4096, 4096)])
+@pytest.mark.parametrize("rows,in_features", [(10656, 1024), (7104, 2048), (4096, 4096), (9472, 2048), (4736, 8192)])
 def test_fused_product_with_longer_runs(rows, in_features):
-    """Shapes for which the fused kernel keeps sums over runs of 2, 4 or 8 chunks of a row (on a
-    148-SM part with 3 CTAs per SM: whole-row runs for the first and third shape, half-row runs
-    for the second); same tolerance as above, two activation vectors, with bias."""
+    """Shapes that make the fused kernel choose its different work splits (on a 148-SM part with
+    4 CTAs of 8 warps per SM: single chunks; runs of 2 of a row's 4 chunks plus the adding-up
+    kernel; one whole row per warp on a shrunk grid; whole rows in two full rounds; runs of 8 of
+    a row's 16 chunks plus the adding-up kernel); same tolerance as above, two activation
+    vectors, with bias."""
     g = torch.Generator().manual_seed(rows)
     w = (torch.randn(rows, in_features, generator=g) * 0.02).to(torch.bfloat16)
     pad = (torch.randn(3000, generator=g) * 0.02).to(torch.bfloat16)        # the matrix does not end the unit
