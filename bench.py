@@ -316,6 +316,9 @@ def main():
     ap.add_argument("--fused-gemv", action="store_true",
                     help="only: the matrix-vector products of one block at batch 1, fused with the decode "
                          "(df11_gemv_prepared) against decode-then-torch GEMV")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="with --generation: also sum the GPU kernel time per token with the torch profiler; run it "
+                         "separately, the profiler leaves a per-launch cost behind that slows the eager legs after it")
     ap.add_argument("--cpu-offload", action="store_true",
                     help="with --generation: DF11 with cpu_offload=True at --batch sequences against resident BF16")
     ap.add_argument("--new-tokens", type=int, default=512)
@@ -616,7 +619,11 @@ def run_generation(args, cfg):
 
     def gpu_ms_per_token():
         """Sum of kernel time of one single-token forward with a KV cache (torch profiler): what
-        the GPU is busy for, whatever the Python harness adds on the host."""
+        the GPU is busy for, whatever the Python harness adds on the host.  Only with
+        --kernel-times: once the profiler has run, every later launch of the process costs more
+        host time, which would be charged to whichever model is timed after it."""
+        if not args.kernel_times:
+            return None
         from torch.profiler import ProfilerActivity, profile
         with torch.no_grad():
             pkv = model(input_ids=ids, use_cache=True).past_key_values
@@ -698,7 +705,7 @@ def run_generation(args, cfg):
         same = (graph_fused["ids"] == graph_bf16["ids"])
         fused = {"df11_tok_s": round(graph_fused["tok_s"], 2),
                  "slowdown_vs_bf16": round(graph_bf16["tok_s"] / graph_fused["tok_s"], 3),
-                 "gpu_kernel_ms_per_token": round(gpu_fused, 2),
+                 "gpu_kernel_ms_per_token": round(gpu_fused, 2) if gpu_fused else None,
                  "tokens_equal_to_bf16": int(same.sum()), "tokens": int(same.numel()),
                  "note": "products exact, fp32 sums in another order than the library GEMV: not bit-identical by design"}
     else:
@@ -716,8 +723,8 @@ def run_generation(args, cfg):
         "prompt_tokens": args.prompt_tokens, "new_tokens": n, "harness": "transformers generate, greedy, eager",
         "bf16_tok_s": round(n / t_bf16, 2), "df11_tok_s": round(n / t_df11, 2),
         "slowdown_vs_bf16": round(t_df11 / t_bf16, 3),
-        "gpu_kernel_ms_per_token": {"bf16": round(gpu_bf16, 2), "df11": round(gpu_df11, 2),
-                                    "ratio": round(gpu_df11 / gpu_bf16, 3)},
+        "gpu_kernel_ms_per_token": ({"bf16": round(gpu_bf16, 2), "df11": round(gpu_df11, 2),
+                                     "ratio": round(gpu_df11 / gpu_bf16, 3)} if gpu_bf16 else None),
         "identical_tokens": bool(torch.equal(out_bf16, out_df11)),
         "cuda_graph_static_cache": graphed,
         "cuda_graph_fused_gemv": fused,

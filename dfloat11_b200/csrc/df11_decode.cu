@@ -1090,13 +1090,46 @@ struct DeviceGuard {
     explicit DeviceGuard(int device)
     {
         if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        if (prev != device && cudaSetDevice(device) != cudaSuccess) ok = false;
+        if (prev != device) {
+            changed = true;
+            if (cudaSetDevice(device) != cudaSuccess) ok = false;
+        }
     }
     ~DeviceGuard()
     {
-        if (prev >= 0) cudaSetDevice(prev);
+        if (prev >= 0 && changed) cudaSetDevice(prev);
     }
+    bool changed = false;
 };
+
+// CTAs per SM of a kernel for a given shared-memory size, asked once per device and kernel slot
+// (and again when the size changes): the query costs more host time than the launch itself.
+struct OccupancyCache {
+    size_t smem = ~(size_t)0;
+    int per_sm = 0;
+};
+OccupancyCache g_occupancy[64][10];
+
+template <class Kernel>
+int ctas_per_sm(Kernel kernel, int device, int slot, int threads, size_t smem, int *per_sm)
+{
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (g_occupancy[device][slot].smem == smem) {
+            *per_sm = g_occupancy[device][slot].per_sm;
+            return DF11_OK;
+        }
+    }
+    int n = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem);
+    if (e != cudaSuccess || n < 1)
+        return df11_fail(DF11_ERR_CUDA, "occupancy query failed (%s, %d CTAs/SM)", cudaGetErrorString(e), n);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    g_occupancy[device][slot].smem = smem;
+    g_occupancy[device][slot].per_sm = n;
+    *per_sm = n;
+    return DF11_OK;
+}
 
 int device_info(int device, DeviceInfo *out)
 {
@@ -1137,9 +1170,9 @@ int launch(Kernel kernel, int threads, int slot, size_t smem, int64_t work_items
         }
     }
     int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
-    if (e != cudaSuccess || per_sm < 1)
-        return df11_fail(DF11_ERR_CUDA, "occupancy query failed (%s, %d CTAs/SM)", cudaGetErrorString(e), per_sm);
+    rc = ctas_per_sm(kernel, device, slot, threads, smem, &per_sm);
+    if (rc != DF11_OK) return rc;
+    cudaError_t e;
     if (max_ctas_per_sm > 0 && per_sm > max_ctas_per_sm) per_sm = max_ctas_per_sm;  // leave room for other kernels
     int64_t grid = (int64_t)info.sm_count * per_sm;
     if (grid > work_items) grid = work_items;
@@ -1174,9 +1207,9 @@ int launch_gemv(Kernel kernel, int slot, int m_count, size_t smem, int64_t work_
         }
     }
     int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFastThreads, smem);
-    if (e != cudaSuccess || per_sm < 1)
-        return df11_fail(DF11_ERR_CUDA, "occupancy query failed (%s, %d CTAs/SM)", cudaGetErrorString(e), per_sm);
+    rc = ctas_per_sm(kernel, device, slot, kFastThreads, smem, &per_sm);
+    if (rc != DF11_OK) return rc;
+    cudaError_t e;
     int64_t grid = (int64_t)info.sm_count * per_sm;
     if (grid > work_items) grid = work_items;
     if (grid < 1) grid = 1;

@@ -161,6 +161,31 @@ def test_tensor_manager_reuses_and_grows():
     assert not host.TensorManager._tensors
 
 
+def test_environment_switches_are_read_once_per_forward_of_a_marked_model(monkeypatch):
+    net = nn.Sequential(nn.Linear(2, 2), nn.Linear(2, 2))
+    host._mark_root(net)
+    host._mark_root(net)                                         # idempotent
+    seen = []
+    net[0].register_forward_pre_hook(lambda mod, inp: seen.append((host._use_fused_gemv(), host._Flags.in_forward)))
+
+    def flip(mod, inp):                                          # a change in mid-forward is not seen before the next one
+        monkeypatch.setenv("DF11_FUSED_GEMV", "0")
+        seen.append((host._use_fused_gemv(), host._Flags.in_forward))
+    net[1].register_forward_pre_hook(flip)
+    monkeypatch.setenv("DF11_FUSED_GEMV", "1")
+    net(torch.zeros(1, 2))
+    net(torch.zeros(1, 2))
+    assert seen == [(True, True), (True, True), (False, True), (False, True)]
+    assert host._Flags.in_forward is False
+    monkeypatch.setenv("DF11_FUSED_GEMV", "1")                   # outside a forward: read on every call
+    assert host._use_fused_gemv()
+    monkeypatch.setenv("DF11_FUSED_GEMV", "0")
+    assert not host._use_fused_gemv()
+    with pytest.raises(RuntimeError):                            # an exception in the forward still ends it
+        net(torch.zeros(1, 3))
+    assert host._Flags.in_forward is False
+
+
 # ------------------------------------------------------------------ GPU
 @pytest.mark.gpu
 @pytest.mark.parametrize("mode", ["resident", "ahead", "ahead_3_ctas", "offload", "offload_some_ahead", "two_pass",
