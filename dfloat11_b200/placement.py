@@ -81,11 +81,34 @@ def _parse_bytes(v) -> float:
 def _move(obj, device):
     if isinstance(obj, torch.Tensor):
         return obj.to(device, non_blocking=True) if obj.device != device else obj
+    if isinstance(obj, tuple) and hasattr(obj, "_fields"):          # a named tuple
+        return type(obj)(*(_move(o, device) for o in obj))
     if isinstance(obj, (list, tuple)):
         return type(obj)(_move(o, device) for o in obj)
     if isinstance(obj, dict):
-        return {k: _move(v, device) for k, v in obj.items()}
+        moved = {k: _move(v, device) for k, v in obj.items()}
+        if type(obj) is dict:
+            return moved
+        try:                                                        # transformers' ModelOutput and the like
+            return type(obj)(**moved)
+        except TypeError:
+            return moved
     return obj
+
+
+def _first_tensor_device(*objs):
+    for obj in objs:
+        if isinstance(obj, torch.Tensor):
+            return obj.device
+        if isinstance(obj, (list, tuple)):
+            found = _first_tensor_device(*obj)
+            if found is not None:
+                return found
+        if isinstance(obj, dict):
+            found = _first_tensor_device(*obj.values())
+            if found is not None:
+                return found
+    return None
 
 
 def dispatch_model(model: nn.Module, device_map: Dict[str, torch.device]) -> nn.Module:
@@ -98,5 +121,15 @@ def dispatch_model(model: nn.Module, device_map: Dict[str, torch.device]) -> nn.
             return _move(args, _device), _move(kwargs, _device)
 
         module.register_forward_pre_hook(pre_hook, with_kwargs=True)
+
+    if len(set(device_map.values())) > 1 and "" not in device_map:
+        # what the whole model returns goes back to the device its inputs came from (accelerate's
+        # io_same_device of the reference's dispatch_model, dfloat11.py:460), so that callers such
+        # as `generate` can go on combining it with their own tensors
+        def root_post_hook(mod, args, kwargs, output):
+            device = _first_tensor_device(args, kwargs)
+            return output if device is None else _move(output, device)
+
+        model.register_forward_hook(root_post_hook, with_kwargs=True)
     model.df11_device_map = dict(device_map)
     return model
