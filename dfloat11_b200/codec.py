@@ -19,7 +19,7 @@ from __future__ import annotations
 
 import heapq
 import os
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, Sequence, Tuple
 
 import numpy as np
 import torch
