@@ -186,6 +186,11 @@ def test_environment_switches_are_read_once_per_forward_of_a_marked_model(monkey
     assert host._Flags.in_forward is False
 
 
+def test_graphed_decoder_refuses_a_model_that_is_not_on_a_gpu():
+    with pytest.raises(RuntimeError):
+        df11.GraphedGreedyDecoder(nn.Linear(2, 2))
+
+
 # ------------------------------------------------------------------ GPU
 @pytest.mark.gpu
 @pytest.mark.parametrize("mode", ["resident", "ahead", "ahead_3_ctas", "offload", "offload_some_ahead", "two_pass",
