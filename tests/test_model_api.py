@@ -186,6 +186,24 @@ def test_environment_switches_are_read_once_per_forward_of_a_marked_model(monkey
     assert host._Flags.in_forward is False
 
 
+def test_placement_moves_structured_outputs_and_keeps_their_type():
+    from collections import namedtuple
+    from transformers import DynamicCache
+    from transformers.modeling_outputs import CausalLMOutputWithPast
+    from dfloat11_b200.placement import _first_tensor_device, _move
+    cpu = torch.device("cpu")
+    out = CausalLMOutputWithPast(logits=torch.zeros(1, 2, 3), past_key_values=DynamicCache())
+    moved = _move(out, cpu)
+    assert type(moved) is CausalLMOutputWithPast and moved.logits is out.logits
+    assert moved.past_key_values is out.past_key_values           # objects that are not tensors pass through
+    pair = namedtuple("pair", "a b")(torch.zeros(1), [torch.ones(2), {"k": torch.ones(1)}])
+    moved = _move(pair, cpu)
+    assert type(moved) is type(pair) and isinstance(moved.b, list) and isinstance(moved.b[1], dict)
+    assert _first_tensor_device((), {"input_ids": torch.zeros(1)}) == cpu
+    assert _first_tensor_device((None, [3, (torch.zeros(1),)]), {}) == cpu
+    assert _first_tensor_device((1, "x"), {}) is None
+
+
 def test_graphed_decoder_refuses_a_model_that_is_not_on_a_gpu():
     with pytest.raises(RuntimeError):
         df11.GraphedGreedyDecoder(nn.Linear(2, 2))
