@@ -353,6 +353,48 @@ DF11_HD void df11_mark_window(const M &m, int n_luts, uint32_t w0, uint32_t w1, 
     }
 }
 
+// ---------------------------------------------------------------------------
+// Bit packer arithmetic shared by the GPU packer (df11_encode.cu) and its CPU emulation.
+// The stream is a sequence of big-endian 32-bit words; a code of `len` bits (1..32) whose
+// first bit is stream bit `bit` lies in word bit >> 5 and possibly the next one.
+// ---------------------------------------------------------------------------
+
+// The two big-endian words a code contributes: *hi to word (bit >> 5), *lo to the next (0 when
+// the code does not reach it).
+DF11_HD void df11_place_code(uint64_t bit, uint32_t len, uint32_t val, uint32_t *hi, uint32_t *lo)
+{
+    const uint64_t v = (uint64_t)val << (64u - len - (uint32_t)(bit & 31u));
+    *hi = (uint32_t)(v >> 32);
+    *lo = (uint32_t)v;
+}
+
+// A big-endian word as the little-endian machine stores it (what is ORed into memory).
+DF11_HD uint32_t df11_bswap32(uint32_t v)
+{
+    return (v >> 24) | ((v >> 8) & 0xFF00u) | ((v << 8) & 0xFF0000u) | (v << 24);
+}
+
+// gaps[window] = g as the bytes to OR into the packed 5-bit array: *byte is the index of the
+// first byte, *first / *second what goes into it and into the byte after it (0: nothing).
+DF11_HD void df11_gap_field(uint64_t window, uint32_t g, uint64_t *byte, uint32_t *first, uint32_t *second)
+{
+    const uint64_t bit = 5u * window;
+    const uint32_t v = g << (11u - (uint32_t)(bit & 7u));  // the field inside the 16 bits byte:byte+1
+    *byte = bit >> 3;
+    *first = v >> 8;
+    *second = v & 0xFFu;
+}
+
+// The bits of the padding code that complete a last byte of which `rem` (1..7) bits are used.
+DF11_HD uint32_t df11_pad_bits(uint32_t rem, uint32_t pad_len, uint32_t pad_val)
+{
+    const uint32_t room = 8u - rem;
+    uint32_t pad = 0;
+    if (pad_len >= room) pad = pad_val >> (pad_len - room);
+    else if (pad_len > 0u) pad = pad_val << (room - pad_len);
+    return pad & ((1u << room) - 1u);
+}
+
 // Low 32 bits of (hi:lo) >> min(s, 32).
 DF11_HD uint32_t df11_funnel_rc(uint32_t lo, uint32_t hi, uint32_t s)
 {

@@ -110,10 +110,11 @@ __device__ __forceinline__ void or_byte(uint8_t *buf, int64_t index, uint32_t va
 // gaps[w] = g: a 5-bit field at bit 5w of the packed array, most significant bit first
 __device__ __forceinline__ void set_gap(uint8_t *gaps, int64_t window, uint32_t g)
 {
-    const int64_t bit = 5 * window, byte = bit >> 3;
-    const uint32_t v = g << (11u - (uint32_t)(bit & 7));  // the field inside the 16 bits byte:byte+1
-    or_byte(gaps, byte, v >> 8);
-    if (v & 0xFFu) or_byte(gaps, byte + 1, v & 0xFFu);
+    uint64_t byte;
+    uint32_t first, second;
+    df11_gap_field((uint64_t)window, g, &byte, &first, &second);
+    or_byte(gaps, (int64_t)byte, first);
+    if (second) or_byte(gaps, (int64_t)byte + 1, second);
 }
 
 __global__ void __launch_bounds__(kEncThreads) df11_enc_pack_kernel(const uint8_t *ex, int64_t n, EncTables t,
@@ -149,11 +150,11 @@ __global__ void __launch_bounds__(kEncThreads) df11_enc_pack_kernel(const uint8_
         }
         if (len > 0u) {
             // the code, MSB first, inside the 64 bits of big-endian words (bit >> 5) and the next one
-            const unsigned long long v = (unsigned long long)t.val[sym[k]] << (64u - len - (uint32_t)(bit & 31));
-            const uint32_t hi = (uint32_t)(v >> 32), lo = (uint32_t)v;
+            uint32_t hi, lo;
+            df11_place_code((uint64_t)bit, len, t.val[sym[k]], &hi, &lo);
             const int64_t w = bit >> 5;
-            atomicOr(words + w, __byte_perm(hi, 0, 0x0123));
-            if (lo) atomicOr(words + w + 1, __byte_perm(lo, 0, 0x0123));
+            atomicOr(words + w, df11_bswap32(hi));
+            if (lo) atomicOr(words + w + 1, df11_bswap32(lo));
         }
         prev_start = bit;
         bit += len;
@@ -164,11 +165,7 @@ __global__ void __launch_bounds__(kEncThreads) df11_enc_pack_kernel(const uint8_
             if (rem) {
                 if ((prev_start >> 6) != (bit >> 6)) set_gap(gaps, bit >> 6, (uint32_t)(bit & 63));
                 if ((prev_start >> 15) != (bit >> 15)) pos[bit >> 15] = (uint32_t)n;
-                const uint32_t room = 8u - rem;
-                uint32_t pad = 0;
-                if (pad_len >= room) pad = pad_val >> (pad_len - room);
-                else if (pad_len > 0u) pad = pad_val << (room - pad_len);
-                or_byte(codes, n_bytes - 1, pad & ((1u << room) - 1u));
+                or_byte(codes, n_bytes - 1, df11_pad_bits(rem, pad_len, pad_val));
             }
             pos[n_blocks] = (uint32_t)n;
         }

@@ -255,3 +255,52 @@ extern "C" int df11_emul_table(const uint8_t *luts, int n_luts, int K, uint32_t 
     }
     return 0;
 }
+
+// The GPU bit packer's per-element rules (df11_encode.cu), run one element after the other with
+// the same shared arithmetic (df11_place_code, df11_bswap32, df11_gap_field, df11_pad_bits) and
+// the same way of writing: ORs into zeroed little-endian 32-bit words.  `codes` must have room
+// for n_bytes rounded up to a multiple of 4; `gaps` and `pos` as for df11_encode_host.
+extern "C" int df11_emul_pack(const uint8_t *ex, int64_t n, const uint8_t *code_len, const uint32_t *code_val,
+                              uint32_t pad_len, uint32_t pad_val, uint8_t *codes, int64_t n_bytes, uint8_t *gaps,
+                              int64_t n_gap_bytes, uint32_t *pos, int64_t n_positions)
+{
+    const int64_t n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
+    if (n_gap_bytes != n_blocks * DF11_GAP_BYTES_PER_BLOCK || n_positions != n_blocks + 1) return -1;
+    memset(codes, 0, (size_t)((n_bytes + 3) / 4 * 4));
+    memset(gaps, 0, (size_t)n_gap_bytes);
+    memset(pos, 0, (size_t)n_positions * 4);
+    uint32_t *words = reinterpret_cast<uint32_t *>(codes);
+    auto or_byte = [](uint8_t *buf, int64_t index, uint32_t value) {
+        reinterpret_cast<uint32_t *>(buf)[index >> 2] |= value << (8 * (index & 3));
+    };
+    auto set_gap = [&](int64_t window, uint32_t g) {
+        uint64_t byte;
+        uint32_t first, second;
+        df11_gap_field((uint64_t)window, g, &byte, &first, &second);
+        or_byte(gaps, (int64_t)byte, first);
+        if (second) or_byte(gaps, (int64_t)byte + 1, second);
+    };
+    int64_t bit = 0, prev_start = -1;
+    for (int64_t i = 0; i < n; ++i) {
+        const uint32_t len = code_len[ex[i]];
+        if (len == 0) return -2;
+        if (prev_start < 0 || (prev_start >> 6) != (bit >> 6)) {
+            set_gap(bit >> 6, (uint32_t)(bit & 63));
+            if (prev_start < 0 || (prev_start >> 15) != (bit >> 15)) pos[bit >> 15] = (uint32_t)i;
+        }
+        uint32_t hi, lo;
+        df11_place_code((uint64_t)bit, len, code_val[ex[i]], &hi, &lo);
+        words[bit >> 5] |= df11_bswap32(hi);
+        if (lo) words[(bit >> 5) + 1] |= df11_bswap32(lo);
+        prev_start = bit;
+        bit += len;
+    }
+    const uint32_t rem = (uint32_t)(bit & 7);
+    if (rem) {
+        if ((prev_start >> 6) != (bit >> 6)) set_gap(bit >> 6, (uint32_t)(bit & 63));
+        if ((prev_start >> 15) != (bit >> 15)) pos[bit >> 15] = (uint32_t)n;
+        or_byte(codes, n_bytes - 1, df11_pad_bits(rem, pad_len, pad_val));
+    }
+    pos[n_blocks] = (uint32_t)n;
+    return (bit + 7) / 8 == n_bytes ? 0 : -3;
+}

@@ -81,3 +81,40 @@ def test_table_entries_are_consistent(emul, golden):
         assert total == bits
         for j in range(n, 4):
             assert ((c >> (16 + 4 * j)) & 15) == 15
+
+
+@pytest.mark.parametrize("n", [1, 15, 4097, 100_003])
+@pytest.mark.parametrize("case", ["gaussian", "one_bit_codes", "eight_bit_codes", "deep_codes"])
+def test_gpu_packer_rules_match_the_host_packer(emul, n, case):
+    """The per-element rules of the GPU bit packer (shared arithmetic in df11_common.h, run here
+    one element after the other) give the bytes of df11_encode_host, which the golden vectors
+    pin to the reference's `encode`."""
+    from dfloat11_b200 import codec
+    rng = np.random.default_rng(n + len(case))
+    if case == "gaussian":
+        e = np.clip(np.rint(rng.normal(120, 2.5, size=n)), 1, 239).astype(np.uint8)
+    elif case == "one_bit_codes":
+        e = ((rng.random(n) < 0.9).astype(np.uint8) * 3 + 100).astype(np.uint8)
+    elif case == "eight_bit_codes":
+        e = rng.integers(0, 240, size=n).astype(np.uint8)
+    else:
+        p = 0.5 ** np.arange(1, 41)
+        e = rng.choice(np.arange(60, 100), size=n, p=p / p.sum()).astype(np.uint8)
+    hist = np.bincount(e, minlength=256)
+    if (hist > 0).sum() < 2:
+        hist[(int(e[0]) + 1) % 240] += 1
+    lens = np.ascontiguousarray(codec.code_lengths(hist), dtype=np.uint8)
+    vals = np.ascontiguousarray(codec.canonical_codes(lens), dtype=np.uint32)
+    vp = lambda a: a.ctypes.data_as(ctypes.c_void_p)  # noqa: E731
+    for pad in ((0, 0), (5, 0b10110), (32, 0xDEADBEEF)):
+        enc_h, gaps_h, pos_h = codec.pack_exponents(e, lens, vals, n_threads=2, pad=pad)
+        enc = np.full((enc_h.size + 3) // 4 * 4, 0xEE, np.uint8)
+        gaps = np.full(gaps_h.size, 0xEE, np.uint8)
+        pos = np.full(pos_h.size, 0xEEEEEEEE, np.uint32)
+        rc = emul.df11_emul_pack(vp(e), ctypes.c_int64(n), vp(lens), vp(vals), ctypes.c_uint32(pad[0]),
+                                 ctypes.c_uint32(pad[1]), vp(enc), ctypes.c_int64(enc_h.size), vp(gaps),
+                                 ctypes.c_int64(gaps.size), vp(pos), ctypes.c_int64(pos.size))
+        assert rc == 0
+        assert np.array_equal(enc[:enc_h.size], enc_h)
+        assert np.array_equal(gaps, gaps_h)
+        assert np.array_equal(pos, pos_h)
