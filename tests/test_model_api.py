@@ -204,6 +204,31 @@ def test_placement_moves_structured_outputs_and_keeps_their_type():
     assert _first_tensor_device((1, "x"), {}) is None
 
 
+def test_fused_product_groups_follow_the_layer_families():
+    """q/k/v and gate/up of a block are served by one stacked product each; o and down stand alone;
+    a unit whose rows are not multiples of 512 elements, a lookup table or an offloaded unit take no
+    fused product at all."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=1, num_attention_heads=8,
+                      num_key_value_heads=2, vocab_size=1024, max_position_embeddings=64, tie_word_embeddings=False)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    df11.compress_in_place(model, LLAMA_PATTERNS)
+    block = model.model.layers[0]
+    layers = host._fused_layers(block)
+    assert [first for _, first in layers] == [0] + list(block.split_positions)
+    groups = host._fused_groups(block, layers)
+    names = {id(m): n.rsplit(".", 1)[-1] for n, m in block.named_modules()}
+    assert [[names[id(l)] for l, _ in g] for g in groups] == [["q_proj", "k_proj", "v_proj"], ["o_proj"],
+                                                              ["gate_proj", "up_proj"], ["down_proj"]]
+    assert host._fused_layers(model.model.embed_tokens) is None
+    assert [first for _, first in host._fused_layers(model.lm_head)] == [0]
+    small = tiny_llama()                                         # hidden 256: rows of 256 elements
+    df11.compress_in_place(small, LLAMA_PATTERNS)
+    assert host._fused_layers(small.model.layers[0]) is None
+    block.offloaded_tensors = {}
+    assert host._fused_layers(block) is None
+
+
 def test_graphed_decoder_refuses_a_model_that_is_not_on_a_gpu():
     with pytest.raises(RuntimeError):
         df11.GraphedGreedyDecoder(nn.Linear(2, 2))
