@@ -81,7 +81,7 @@ def algorithmic_bytes(unit) -> int:
             + unit["luts"].numel() + 2 * unit["n_elements"])
 
 
-def make_unit(n_elements, std, seed, device, keep_host=False, n_threads=None):
+def make_unit(n_elements, std, seed, device, keep_host=False, n_threads=None, keep_weights=False):
     """Synthesise one unit on the GPU, compress it (native host packer), put it in HBM."""
     from dfloat11_b200 import codec
     g = torch.Generator(device=device).manual_seed(seed)
@@ -107,6 +107,8 @@ def make_unit(n_elements, std, seed, device, keep_host=False, n_threads=None):
     if keep_host:
         unit["host"] = dict(luts=luts, enc=enc_d.cpu().numpy(), sm=sign_mantissa.cpu().numpy(), pos=positions,
                             gaps=gaps_d.cpu().numpy())
+    if keep_weights:
+        unit["weights"] = w
     return unit
 
 

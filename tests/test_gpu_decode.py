@@ -438,3 +438,28 @@ def test_encode_weights_on_the_gpu_round_trips():
     d = {k: v.to(DEV) for k, v in on_gpu.items() if k != "split_positions"}
     out = ops.decode(d["luts"], d["encoded_exponent"], d["sign_mantissa"], d["output_positions"], d["gaps"])
     assert torch.equal(out.cpu().view(torch.int16), w.view(torch.int16))
+
+
+def test_unit_of_more_than_2_to_the_31_elements():
+    """An unsharded Llama-405B block has 3.19 G weights: element and byte offsets pass 2^31 (the
+    reference kernel indexes with `int`, decode.cu:26-34).  Packed on the GPU, decoded by both
+    kernels, compared with the original weights bit for bit.  Needs about 30 GB of device memory."""
+    import bench
+    if torch.cuda.get_device_properties(0).total_memory < 60e9:
+        pytest.skip("needs a GPU with 60 GB")
+    n = 2 * 16384 * 16384 + 2 * 1024 * 16384 + 3 * 16384 * 53248          # 3 187 671 040
+    assert n > 2 ** 31
+    u = bench.make_unit(n, 0.02, seed=405, device=torch.device(DEV), keep_weights=True)
+    want = u.pop("weights").view(torch.int16)
+    st = _status()
+    out = torch.empty(n, dtype=torch.bfloat16, device=DEV)
+    aux = ops.prepare(u["luts"], u["enc"], u["pos"], u["gaps"], n, status=st)
+    ops.decode_prepared(u["luts"], u["enc"], u["sm"], u["pos"], u["gaps"], aux, out=out, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0 and torch.equal(out.view(torch.int16), want)
+    out.zero_()
+    ops.decode(u["luts"], u["enc"], u["sm"], u["pos"], u["gaps"], out=out, max_block_elems=u["widest"], status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0 and torch.equal(out.view(torch.int16), want)
+    del out, want, aux, u
+    torch.cuda.empty_cache()
