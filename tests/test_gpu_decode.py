@@ -463,3 +463,35 @@ def test_unit_of_more_than_2_to_the_31_elements():
     assert st.item() == 0 and torch.equal(out.view(torch.int16), want)
     del out, want, aux, u
     torch.cuda.empty_cache()
+
+
+def test_empty_and_one_element_units():
+    """Nothing to decode is not an error (no launch, output untouched); a unit of one element and
+    one of 17 (a group and a bit) decode through every entry point."""
+    from tests.conftest import load_golden
+    d = _to_dev(load_golden("gauss_n3"))
+    guard = torch.full((8,), 7.0, dtype=torch.bfloat16, device=DEV)
+    empty_u8 = torch.empty(0, dtype=torch.uint8, device=DEV)
+    for fn in (lambda: _lib.lib.df11_decode(d["luts"].data_ptr(), d["enc"].data_ptr(), d["sm"].data_ptr(),
+                                            d["pos"].data_ptr(), d["gaps"].data_ptr(), guard.data_ptr(),
+                                            d["luts"].shape[0], 0, 0, 0, None, 0, None),
+               lambda: _lib.lib.df11_decode_prepared(d["luts"].data_ptr(), d["enc"].data_ptr(), d["sm"].data_ptr(),
+                                                     d["pos"].data_ptr(), d["gaps"].data_ptr(), guard.data_ptr(),
+                                                     guard.data_ptr(), d["luts"].shape[0], 0, 0, 0, None, 0, None)):
+        assert fn() == 0
+    torch.cuda.synchronize()
+    assert torch.all(guard == 7.0) and empty_u8.numel() == 0
+    with pytest.raises(ValueError):
+        codec.encode_weights([torch.empty(0, dtype=torch.bfloat16)])
+    for n in (1, 17):
+        w = (torch.randn(n, generator=torch.Generator().manual_seed(n)) * 0.02).to(torch.bfloat16)
+        for where in ("cpu", DEV):
+            t, dd, widest = _unit_from_weights([w.to(where)])
+            st = _status()
+            out = ops.decode(dd["luts"], dd["enc"], dd["sm"], dd["pos"], dd["gaps"], max_block_elems=widest, status=st)
+            aux = ops.prepare(dd["luts"], dd["enc"], dd["pos"], dd["gaps"], n, status=st)
+            out2 = ops.decode_prepared(dd["luts"], dd["enc"], dd["sm"], dd["pos"], dd["gaps"], aux, status=st)
+            torch.cuda.synchronize()
+            assert st.item() == 0
+            assert torch.equal(out.cpu().view(torch.int16), w.view(torch.int16))
+            assert torch.equal(out2.cpu().view(torch.int16), w.view(torch.int16))
