@@ -758,7 +758,7 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float f)  // round to nea
     return (uint16_t)(u >> 16);
 }
 
-template <int K, int M>
+template <int K, int M, bool CHECKED>
 __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_kernel(const Params p, const GemvArgs g)
 {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -799,7 +799,7 @@ __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
 #pragma unroll
     for (int m = 0; m < M; ++m) sum[m] = 0.f;
 
-    lean_tasks<K, true>(
+    lean_tasks<K, CHECKED>(
         p, tab, lane, my_items << run_log,
         [&](uint32_t j) { return g.first_chunk + ((gw + (j >> run_log) * warps) << run_log) + (j & (run - 1u)); },
         n_words, bad, [&](uint32_t j, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &sm) {
@@ -1082,7 +1082,7 @@ struct DeviceInfo {
 };
 std::mutex g_mutex;
 DeviceInfo g_devices[64];
-bool g_attr_set[64][10] = {};
+bool g_attr_set[64][14] = {};
 
 struct DeviceGuard {
     int prev = -1;
@@ -1108,7 +1108,7 @@ struct OccupancyCache {
     size_t smem = ~(size_t)0;
     int per_sm = 0;
 };
-OccupancyCache g_occupancy[64][10];
+OccupancyCache g_occupancy[64][14];
 
 template <class Kernel>
 int ctas_per_sm(Kernel kernel, int device, int slot, int threads, size_t smem, int *per_sm)
@@ -1576,11 +1576,23 @@ extern "C" int df11_gemv_prepared(const void *luts, const void *codes, const voi
     g.n_rows = (uint32_t)n_rows;
     const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
     const int64_t cta_items = (n_rows * g.chunks_per_row + kFastThreads / 32 - 1) / (kFastThreads / 32);
+    // A matrix that stays clear of the unit's last two chunks needs no bounds checks on its
+    // stream loads (see lean_tasks); the last matrix of a unit keeps them.
+    const bool interior = (int64_t)g.first_chunk + n_rows * g.chunks_per_row + 2 <= a.n_chunks && (n_bytes >> 2) >= 4;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (interior) {
+        switch (m) {
+        case 1: return launch_gemv(df11_gemv_kernel<kFastTableBits, 1, false>, 10, 1, smem, cta_items, p, g, device, s);
+        case 2: return launch_gemv(df11_gemv_kernel<kFastTableBits, 2, false>, 11, 2, smem, cta_items, p, g, device, s);
+        case 3: return launch_gemv(df11_gemv_kernel<kFastTableBits, 3, false>, 12, 3, smem, cta_items, p, g, device, s);
+        default: return launch_gemv(df11_gemv_kernel<kFastTableBits, 4, false>, 13, 4, smem, cta_items, p, g, device, s);
+        }
+    }
     switch (m) {
-    case 1: return launch_gemv(df11_gemv_kernel<kFastTableBits, 1>, 6, 1, smem, cta_items, p, g, device, (cudaStream_t)stream);
-    case 2: return launch_gemv(df11_gemv_kernel<kFastTableBits, 2>, 7, 2, smem, cta_items, p, g, device, (cudaStream_t)stream);
-    case 3: return launch_gemv(df11_gemv_kernel<kFastTableBits, 3>, 8, 3, smem, cta_items, p, g, device, (cudaStream_t)stream);
-    default: return launch_gemv(df11_gemv_kernel<kFastTableBits, 4>, 9, 4, smem, cta_items, p, g, device, (cudaStream_t)stream);
+    case 1: return launch_gemv(df11_gemv_kernel<kFastTableBits, 1, true>, 6, 1, smem, cta_items, p, g, device, s);
+    case 2: return launch_gemv(df11_gemv_kernel<kFastTableBits, 2, true>, 7, 2, smem, cta_items, p, g, device, s);
+    case 3: return launch_gemv(df11_gemv_kernel<kFastTableBits, 3, true>, 8, 3, smem, cta_items, p, g, device, s);
+    default: return launch_gemv(df11_gemv_kernel<kFastTableBits, 4, true>, 9, 4, smem, cta_items, p, g, device, s);
     }
 }
 
