@@ -60,7 +60,10 @@ constexpr int kFastTableBits = DF11_FAST_TABLE_BITS;  // K of the fast decoder (
 constexpr int kCodesBufBytes = DF11_BLOCK_BYTES + 16;      // block + look-ahead, multiple of 16
 constexpr int kInBufBytes = kCodesBufBytes + DF11_GAP_BYTES_PER_BLOCK;  // stream bytes, then gap bytes
 constexpr uint32_t kWaitLimit = 1u << 16;                  // bounded mbarrier polling
-constexpr int kFastThreads = 256;
+#ifndef DF11_FAST_THREADS
+#define DF11_FAST_THREADS 256
+#endif
+constexpr int kFastThreads = DF11_FAST_THREADS;
 
 struct Params {
     const uint8_t *luts;
