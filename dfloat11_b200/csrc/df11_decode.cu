@@ -51,8 +51,11 @@ constexpr int kWarps = kThreads / 32;
 #ifndef DF11_FAST_MIN_CTAS
 #define DF11_FAST_MIN_CTAS 4
 #endif
+#ifndef DF11_GEMV_THREADS
+#define DF11_GEMV_THREADS 1024
+#endif
 #ifndef DF11_GEMV_MIN_CTAS
-#define DF11_GEMV_MIN_CTAS 4
+#define DF11_GEMV_MIN_CTAS 1
 #endif
 constexpr int kTableBits = DF11_TABLE_BITS;           // K of the self-contained decoder and the seek-point pass
 constexpr int kFastTableBits = DF11_FAST_TABLE_BITS;  // K of the fast decoder (its table is larger, its CTAs smaller)
@@ -64,6 +67,9 @@ constexpr uint32_t kWaitLimit = 1u << 16;                  // bounded mbarrier p
 #define DF11_FAST_THREADS 256
 #endif
 constexpr int kFastThreads = DF11_FAST_THREADS;
+// The fused product runs one CTA of 1024 threads per SM: its launches are short, and one copy of
+// the decode table per SM instead of four shortens every one of them.
+constexpr int kGemvThreads = DF11_GEMV_THREADS;
 
 struct Params {
     const uint8_t *luts;
@@ -762,7 +768,7 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float f)  // round to nea
 }
 
 template <int K, int M, bool CHECKED>
-__global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_kernel(const Params p, const GemvArgs g)
+__global__ void __launch_bounds__(kGemvThreads, DF11_GEMV_MIN_CTAS) df11_gemv_kernel(const Params p, const GemvArgs g)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
@@ -771,8 +777,8 @@ __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
     {
         const uint4 *src = reinterpret_cast<const uint4 *>(p.table_g);
         uint4 *dst = reinterpret_cast<uint4 *>(smem);
-        for (int i = tid; i < (1 << K) / 2; i += kFastThreads) dst[i] = __ldg(src + i);
-        for (int i = tid; i < p.n_luts * 256; i += kFastThreads) smem[luts_off + i] = __ldg(p.luts + i);
+        for (int i = tid; i < (1 << K) / 2; i += kGemvThreads) dst[i] = __ldg(src + i);
+        for (int i = tid; i < p.n_luts * 256; i += kGemvThreads) smem[luts_off + i] = __ldg(p.luts + i);
     }
     __syncthreads();
     // Tables, seek points, stream and sign/mantissa bytes belong to the unit and may be read while
@@ -788,8 +794,8 @@ __global__ void __launch_bounds__(kFastThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
     // chunks_per_row); items go round the warps.  A lane keeps its products of a run in a
     // register, so the warp adds its 32 lanes up once per run, not once per chunk.
     const uint32_t n_words = (uint32_t)(p.n_bytes >> 2);
-    const uint32_t warps = gridDim.x * (kFastThreads / 32);
-    const uint32_t gw = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
+    const uint32_t warps = gridDim.x * (kGemvThreads / 32);
+    const uint32_t gw = blockIdx.x * (kGemvThreads / 32) + (tid >> 5);
     const uint32_t cpr = g.chunks_per_row, run_log = g.run_log, run = 1u << run_log;
     const uint32_t parts = cpr >> run_log;  // runs per row
     const uint32_t n_items = g.n_rows * parts;
@@ -1210,7 +1216,7 @@ int launch_gemv(Kernel kernel, int slot, int m_count, size_t smem, int64_t work_
         }
     }
     int per_sm = 0;
-    rc = ctas_per_sm(kernel, device, slot, kFastThreads, smem, &per_sm);
+    rc = ctas_per_sm(kernel, device, slot, kGemvThreads, smem, &per_sm);
     if (rc != DF11_OK) return rc;
     cudaError_t e;
     int64_t grid = (int64_t)info.sm_count * per_sm;
@@ -1220,14 +1226,14 @@ int launch_gemv(Kernel kernel, int slot, int m_count, size_t smem, int64_t work_
     // are no more items than resident warps (then the grid shrinks to one item per warp: no
     // partly filled last round), or the items fill the warps' rounds to 85 %.
     GemvArgs args = g;
-    const int64_t warps = grid * (kFastThreads / 32);
+    const int64_t warps = grid * (kGemvThreads / 32);
     args.run_log = 0;
     for (int log = 3; log >= 0; --log) {
         if (g.chunks_per_row % (1u << log)) continue;
         const int64_t items = (int64_t)g.n_rows * (g.chunks_per_row >> log);
         if (items <= warps) {
             args.run_log = (uint32_t)log;
-            grid = (items + kFastThreads / 32 - 1) / (kFastThreads / 32);
+            grid = (items + kGemvThreads / 32 - 1) / (kGemvThreads / 32);
             break;
         }
         const int64_t rounds = (items + warps - 1) / warps;
@@ -1243,7 +1249,7 @@ int launch_gemv(Kernel kernel, int slot, int m_count, size_t smem, int64_t work_
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kFastThreads);
+    cfg.blockDim = dim3(kGemvThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cfg.attrs = attr;
@@ -1578,7 +1584,7 @@ extern "C" int df11_gemv_prepared(const void *luts, const void *codes, const voi
     g.chunks_per_row = (uint32_t)(in_features / 512);
     g.n_rows = (uint32_t)n_rows;
     const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
-    const int64_t cta_items = (n_rows * g.chunks_per_row + kFastThreads / 32 - 1) / (kFastThreads / 32);
+    const int64_t cta_items = (n_rows * g.chunks_per_row + kGemvThreads / 32 - 1) / (kGemvThreads / 32);
     // A matrix that stays clear of the unit's last two chunks needs no bounds checks on its
     // stream loads (see lean_tasks); the last matrix of a unit keeps them.
     const bool interior = (int64_t)g.first_chunk + n_rows * g.chunks_per_row + 2 <= a.n_chunks && (n_bytes >> 2) >= 4;

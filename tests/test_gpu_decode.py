@@ -378,7 +378,7 @@ def test_fused_matrix_vector_product(m):
 @pytest.mark.parametrize("rows,in_features", [(10656, 1024), (7104, 2048), (4096, 4096), (9472, 2048), (4736, 8192)])
 def test_fused_product_with_longer_runs(rows, in_features):
     """Shapes that make the fused kernel choose its different work splits (on a 148-SM part with
-    4 CTAs of 8 warps per SM: single chunks; runs of 2 of a row's 4 chunks plus the adding-up
+    32 resident warps per SM: single chunks; runs of 2 of a row's 4 chunks plus the adding-up
     kernel; one whole row per warp on a shrunk grid; whole rows in two full rounds; runs of 8 of
     a row's 16 chunks plus the adding-up kernel); same tolerance as above, two activation
     vectors, with bias."""
