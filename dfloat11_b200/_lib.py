@@ -20,13 +20,19 @@ DF11_ERR_NOSPACE = -4
 STATUS_BAD_TABLE = 1
 STATUS_BAD_POSITIONS = 2
 STATUS_TRUNCATED = 4
+STATUS_TIMEOUT = 8
 
 # every symbol declared in include/df11.h: name -> (restype, argtypes)
 SIGNATURES = {
     "df11_version": (c_int32, []),
     "df11_last_error": (c_char_p, []),
     "df11_decode": (c_int32, [c_void_p] * 6 + [c_int32, c_int64, c_int64, c_int32, c_void_p, c_int32, c_void_p]),
+    "df11_selftest_wait_timeout": (c_int32, [c_void_p] * 6 + [c_int32, c_int64, c_int64, c_int32, c_int64, c_void_p,
+                                             c_int32, c_void_p]),
     "df11_aux_bytes": (c_int64, [c_int64, c_int64]),
+    "df11_seek_interval": (c_int32, [c_int32]),
+    "df11_decode_range_prepared": (c_int32, [c_void_p] * 4 + [c_int64, c_int64, c_void_p, c_int32, c_int64, c_int64,
+                                             c_void_p, c_int32, c_void_p]),
     "df11_prepare": (c_int32, [c_void_p] * 5 + [c_int64, c_int32, c_int64, c_int64, c_void_p, c_int32, c_void_p]),
     "df11_decode_prepared": (c_int32, [c_void_p] * 7 + [c_int32, c_int64, c_int64, c_int32, c_void_p, c_int32, c_void_p]),
     "df11_decode_prepared_shared": (c_int32, [c_void_p] * 7 + [c_int32, c_int64, c_int64, c_int32, c_void_p, c_int32,

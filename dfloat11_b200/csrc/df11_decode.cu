@@ -32,6 +32,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "../../include/df11.h"
@@ -62,7 +63,13 @@ constexpr int kFastTableBits = DF11_FAST_TABLE_BITS;  // K of the fast decoder (
 
 constexpr int kCodesBufBytes = DF11_BLOCK_BYTES + 16;      // block + look-ahead, multiple of 16
 constexpr int kInBufBytes = kCodesBufBytes + DF11_GAP_BYTES_PER_BLOCK;  // stream bytes, then gap bytes
-constexpr uint32_t kWaitLimit = 1u << 16;                  // bounded mbarrier polling
+// Bounded waits for bulk copies.  A copy of a few KB lands within microseconds; a wait gives up
+// after kWaitNs of wall time (and after kWaitPolls polls whatever the clock says).  A CTA that gave
+// up leaves its loop, waits once more, kDrainNs at most, for the copies it still has in flight into
+// its own shared memory, and returns.
+constexpr uint32_t kWaitPolls = 1u << 20;
+constexpr uint64_t kWaitNs = 50ull * 1000 * 1000;
+constexpr uint64_t kDrainNs = 200ull * 1000 * 1000;
 #ifndef DF11_FAST_THREADS
 #define DF11_FAST_THREADS 256
 #endif
@@ -90,6 +97,8 @@ struct Params {
     uint32_t chunks_per_row;   // row-wise decode: 512-element chunks per row
     uint32_t n_tasks;          // row-wise decode: rows wanted * chunks_per_row
     uint32_t n_rows_total;     // row-wise decode: rows the unit holds
+    uint32_t chunk_first;      // range decode: first chunk to produce (its output starts at `out`), else 0
+    uint32_t chunk_count;      // range decode: chunks to produce; 0 = the whole unit
     int n_luts;
     int ept;          // elements per seek point (16 or 32)
     int stage_bytes;  // shared staging area (and sign/mantissa tile), multiple of 16
@@ -97,6 +106,11 @@ struct Params {
                         // bit 2: codes 4-byte aligned (word loads allowed)
     int sm_aligned;     // sign_mantissa 16-byte aligned: bulk copies / 16-byte loads allowed
     int out_aligned;    // out 16-byte aligned: vector stores allowed
+    // self-test of the bounded waits (df11_selftest_wait_timeout): the producer announces the
+    // bytes of format block `drop_block`'s input copy but never issues it, and waits are cut to
+    // `wait_ns`.  0 / -1 in every ordinary launch.
+    int64_t drop_block;
+    uint64_t wait_ns;
 };
 
 // ---- shared-memory accessors: explicit 32-bit shared addresses ---------------------------
@@ -150,19 +164,37 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-// Waits for the given phase of an mbarrier, giving up after `limit` polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit)
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 {
-    for (uint32_t it = 0; it < limit; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0u;
+}
+__device__ __forceinline__ uint64_t global_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for the given phase of an mbarrier; gives up after `limit_ns` nanoseconds or kWaitPolls
+// polls, whichever comes first.  The clock is only read when the first poll fails.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint64_t limit_ns)
+{
+    const uint64_t t0 = global_ns();
+    for (uint32_t it = 0; it < kWaitPolls; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if (global_ns() - t0 > limit_ns) break;
     }
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns)
+{
+    if (mbar_try(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, limit_ns);
 }
 
 // Memory policy of the window routines (df11_common.h) for the kernels: every table probe is
@@ -390,11 +422,14 @@ __device__ __forceinline__ void stream_window(const uint4 &r, uint32_t bit, uint
     w2 = __funnelshift_l(d, c, bit);
 }
 
-// The inner loop of the fast decoder for tasks that are known to be whole chunks of 512
-// elements of aligned tensors (seek point every 16 elements).  This warp runs `n_seq` tasks,
-// numbered 0 .. n_seq-1 in the order it runs them; task j is chunk `chunk_of(j)`.  For every
-// task the sink gets the task's number, the sixteen exponents of this lane's group (four per
-// word, lowest byte first) and the group's sixteen sign/mantissa bytes.
+// The inner loop of the fast decoder for tasks that are known to be whole chunks of 32 * EPT
+// elements of aligned tensors (a seek point every EPT = 16 or 32 elements).  This warp runs
+// `n_seq` tasks, numbered 0 .. n_seq-1 in the order it runs them; task j is chunk `chunk_of(j)`.
+// For every sixteen elements of this lane's group the sink gets the task's number, which
+// sixteen of the group they are (`part`, 0 or 1), their exponents (four per word, lowest byte
+// first) and their sign/mantissa bytes.  With EPT = 32 the second half of a group goes on where
+// the first stopped: its stream words were loaded by neighbouring lanes a moment ago, so the
+// reload in the middle of a task is served by L1.
 //
 // Three stages run ahead of each other: the seek point of the task after the next is being
 // loaded while the stream words and sign/mantissa bytes of the next task are being loaded
@@ -406,7 +441,7 @@ __device__ __forceinline__ void stream_window(const uint4 &r, uint32_t bit, uint
 // start of every task's last group (true for every chunk but the last two of a unit), so a
 // word index is only clamped: a foreign auxiliary buffer gives wrong output, never a fault.
 // CHECKED = true: any chunk of the unit; word loads near the end of the stream go byte by byte.
-template <int K, bool CHECKED, class ChunkOf, class Sink>
+template <int K, int EPT, bool CHECKED, class ChunkOf, class Sink>
 __device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &tab, uint32_t lane, uint32_t n_seq,
                                            ChunkOf &&chunk_of, uint32_t n_words, int &bad, Sink &&sink)
 {
@@ -416,7 +451,7 @@ __device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &ta
     const uint32_t last_wi = n_words - 4u;  // callers make sure of n_words >= 4
     struct Inputs {
         uint32_t wi, bit;
-        uint4 words, sm;
+        uint4 words, sm[EPT / 16];
     };
     auto words_at = [&](uint32_t wi) -> uint4 {
         if (CHECKED && wi > last_wi) return stream_words_slow(p.codes, p.n_bytes, wi);
@@ -438,7 +473,9 @@ __device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &ta
         if (!CHECKED) in.wi = min(in.wi, last_wi);
         in.bit = lo & 31u;
         in.words = words_at(in.wi);
-        in.sm = __ldg(reinterpret_cast<const uint4 *>(p.sm) + (chunk * 32u + lane));
+        const uint4 *sm16 = reinterpret_cast<const uint4 *>(p.sm) + (chunk * 32u + lane) * (EPT / 16);
+#pragma unroll
+        for (int part = 0; part < EPT / 16; ++part) in.sm[part] = __ldg(sm16 + part);
     };
     ExpShift X = {0, 0, 0, 0, 0};
     auto run_task = [&](uint32_t t, const Inputs &cur, Inputs &nxt) {
@@ -446,38 +483,49 @@ __device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &ta
         fetch_seek(t + 2u);
         uint32_t wi = cur.wi, bit = cur.bit, acc = 0, w0, w1, w2;
         stream_window(cur.words, bit, w0, w1, w2);
-        for (;;) {
-            probe_loop<K>(acc, X, w0, w1, w2, tab.dec_addr);
-            if (acc & kFastDone) break;  // the usual exit
-            if (acc & kFastEscape) {     // full walk for one symbol
-                acc -= kFastEscape;
-                uint32_t len;
-                int tbad = 0;
-                const uint32_t sym = df11_walk_m(tab, p.n_luts, w0, &len, &tbad);
-                if (tbad) bad |= DF11_STATUS_BAD_TABLE;
-                X.push(sym, 8u);
-                acc += len | (8u << 16);
-                if (len < 32u) {
-                    w0 = __funnelshift_l(w1, w0, len);
-                    w1 = __funnelshift_l(w2, w1, len);
-                    w2 <<= len;
-                } else {
-                    w0 = w1, w1 = w2, w2 = 0;
-                }
-                if (acc & kFastDone) break;
-            }
-            if (acc & 64u) {  // position 64..127: reload the window where the position has got to
+#pragma unroll
+        for (int part = 0; part < EPT / 16; ++part) {
+            if (part > 0) {  // go on where the first sixteen stopped; codes decoded beyond them are at the top of X
                 const uint32_t at = bit + (acc & 0x7Fu);
                 wi += at >> 5;
                 if (!CHECKED) wi = min(wi, last_wi);
                 bit = at & 31u;
+                acc = (acc & ~0xFFu) - kFastDone;
                 stream_window(words_at(wi), bit, w0, w1, w2);
-                acc &= ~0xFFu;
             }
+            for (;;) {
+                probe_loop<K>(acc, X, w0, w1, w2, tab.dec_addr);
+                if (acc & kFastDone) break;  // the usual exit
+                if (acc & kFastEscape) {     // full walk for one symbol
+                    acc -= kFastEscape;
+                    uint32_t len;
+                    int tbad = 0;
+                    const uint32_t sym = df11_walk_m(tab, p.n_luts, w0, &len, &tbad);
+                    if (tbad) bad |= DF11_STATUS_BAD_TABLE;
+                    X.push(sym, 8u);
+                    acc += len | (8u << 16);
+                    if (len < 32u) {
+                        w0 = __funnelshift_l(w1, w0, len);
+                        w1 = __funnelshift_l(w2, w1, len);
+                        w2 <<= len;
+                    } else {
+                        w0 = w1, w1 = w2, w2 = 0;
+                    }
+                    if (acc & kFastDone) break;
+                }
+                if (acc & 64u) {  // position 64..127: reload the window where the position has got to
+                    const uint32_t at = bit + (acc & 0x7Fu);
+                    wi += at >> 5;
+                    if (!CHECKED) wi = min(wi, last_wi);
+                    bit = at & 31u;
+                    stream_window(words_at(wi), bit, w0, w1, w2);
+                    acc &= ~0xFFu;
+                }
+            }
+            uint32_t e0, e1, e2, e3;
+            X.take(acc, &e0, &e1, &e2, &e3);
+            sink(t, (uint32_t)part, e0, e1, e2, e3, cur.sm[part]);
         }
-        uint32_t e0, e1, e2, e3;
-        X.take(acc, &e0, &e1, &e2, &e3);
-        sink(t, e0, e1, e2, e3, cur.sm);
     };
     Inputs a, b;
     fetch_seek(0u);
@@ -548,13 +596,14 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
     };
 
     // A task is one chunk of 32 groups.  Whole-unit decode: task t is chunk t and writes where it
-    // reads.  Row-wise decode (ROWS): task t is chunk t % chunks_per_row of row rows[t / chunks_per_row]
-    // and writes to the t-th chunk of the output.
-    const uint32_t n_tasks = ROWS ? p.n_tasks : (uint32_t)p.n_chunks;
+    // reads.  Range decode (chunk_count > 0): task t is chunk chunk_first + t and writes to the t-th
+    // chunk of the output.  Row-wise decode (ROWS): task t is chunk t % chunks_per_row of row
+    // rows[t / chunks_per_row] and writes to the t-th chunk of the output.
+    const uint32_t n_tasks = ROWS ? p.n_tasks : (p.chunk_count ? p.chunk_count : (uint32_t)p.n_chunks);
     const uint32_t n_elements = (uint32_t)p.n_elements;  // the host side rejects units too close to 2^32
     const uint32_t warps = gridDim.x * (kFastThreads / 32);
     auto chunk_of = [&](uint32_t task) -> uint32_t {
-        if (!ROWS) return task;
+        if (!ROWS) return task + p.chunk_first;
         const uint32_t r = task / p.chunks_per_row;
         int64_t row = __ldg(p.rows + r);
         if (row < 0 || row >= (int64_t)p.n_rows_total) {
@@ -591,21 +640,23 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
 
     uint32_t task = blockIdx.x * (kFastThreads / 32) + (tid >> 5);
 
-    // Whole-unit decode of aligned tensors: every chunk but the last two takes the lean loop
-    // (such a chunk is full, and at least 512 further codes, 16 stream words or more, follow it).
-    if (EPT == 16 && !ROWS && vec && n_words >= 4u && p.n_chunks > 2) {
-        const uint32_t n_lean = (uint32_t)p.n_chunks - 2u;
+    // Whole-unit and range decode of aligned tensors: every chunk but the last two of the unit takes
+    // the lean loop (such a chunk is full, and at least 512 further codes, 16 stream words or more,
+    // follow it).
+    if (!ROWS && vec && n_words >= 4u && p.n_chunks > 2 && p.chunk_first + 2u < (uint32_t)p.n_chunks) {
+        const uint32_t n_lean = min(n_tasks, (uint32_t)p.n_chunks - 2u - p.chunk_first);
         const uint32_t mine = task < n_lean ? (n_lean - 1u - task) / warps + 1u : 0u;  // this warp's lean tasks
-        const uint32_t task0 = task;
-        lean_tasks<K, false>(
-            p, tab, lane, mine, [&](uint32_t j) { return task0 + j * warps; }, n_words, bad,
-            [&](uint32_t j, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &m) {
+        const uint32_t task0 = task, chunk0 = task + p.chunk_first;
+        lean_tasks<K, EPT, false>(
+            p, tab, lane, mine, [&](uint32_t j) { return chunk0 + j * warps; }, n_words, bad,
+            [&](uint32_t j, uint32_t part, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &m) {
                 uint4 r0, r1;
                 df11_merge4(e0, m.x, &r0.x, &r0.y);
                 df11_merge4(e1, m.y, &r0.z, &r0.w);
                 df11_merge4(e2, m.z, &r1.x, &r1.y);
                 df11_merge4(e3, m.w, &r1.z, &r1.w);
-                uint4 *dst = reinterpret_cast<uint4 *>(p.out) + 2u * ((task0 + j * warps) * 32u + lane);
+                uint4 *dst = reinterpret_cast<uint4 *>(p.out) +
+                             ((task0 + j * warps) * 32u + lane) * (EPT / 8) + 2u * part;
                 dst[0] = r0;
                 dst[1] = r1;
             });
@@ -638,7 +689,7 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
 
         uint32_t first = (cur.chunk * 32u + lane) * EPT;  // the element my next code decodes to
         // where it goes: its own place, or (row-wise) the matching place of the gathered output
-        const uint32_t shift = ROWS ? (task * 32u + lane) * EPT - first : 0u;
+        const uint32_t shift = (task * 32u + lane) * EPT - first;  // 0 for whole-unit decode
         uint32_t wi = cur.wi, bit = cur.bit;
         uint32_t acc = 0;  // see kFastEscape
         ExpShift X = {0, 0, 0, 0, 0};
@@ -767,7 +818,7 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float f)  // round to nea
     return (uint16_t)(u >> 16);
 }
 
-template <int K, int M, bool CHECKED>
+template <int K, int EPT, int M, bool CHECKED>
 __global__ void __launch_bounds__(kGemvThreads, DF11_GEMV_MIN_CTAS) df11_gemv_kernel(const Params p, const GemvArgs g)
 {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -800,7 +851,8 @@ __global__ void __launch_bounds__(kGemvThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
     const uint32_t parts = cpr >> run_log;  // runs per row
     const uint32_t n_items = g.n_rows * parts;
     const uint32_t my_items = gw < n_items ? (n_items - 1u - gw) / warps + 1u : 0u;
-    const uint32_t in_features = cpr * 512u;
+    constexpr uint32_t chunk_elems = 32u * EPT;
+    const uint32_t in_features = cpr * chunk_elems;
     const uint32_t step_rows = warps / parts, step_parts = warps - step_rows * parts;
     uint32_t row = gw / parts, part = gw - row * parts;  // of the item the sink is in
     int bad = 0;
@@ -808,10 +860,11 @@ __global__ void __launch_bounds__(kGemvThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
 #pragma unroll
     for (int m = 0; m < M; ++m) sum[m] = 0.f;
 
-    lean_tasks<K, CHECKED>(
+    lean_tasks<K, EPT, CHECKED>(
         p, tab, lane, my_items << run_log,
         [&](uint32_t j) { return g.first_chunk + ((gw + (j >> run_log) * warps) << run_log) + (j & (run - 1u)); },
-        n_words, bad, [&](uint32_t j, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &sm) {
+        n_words, bad,
+        [&](uint32_t j, uint32_t half, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3, const uint4 &sm) {
             if (!waited) {
                 grid_dependency_wait();
                 waited = true;
@@ -822,7 +875,7 @@ __global__ void __launch_bounds__(kGemvThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
             df11_merge4(e2, sm.z, &w[4], &w[5]);
             df11_merge4(e3, sm.w, &w[6], &w[7]);
             const uint32_t sub = j & (run - 1u);
-            const uint32_t column = ((part << run_log) + sub) * 512u + 16u * lane;
+            const uint32_t column = ((part << run_log) + sub) * chunk_elems + EPT * lane + 16u * half;
 #pragma unroll
             for (int m = 0; m < M; ++m) {
                 const uint4 *xp = reinterpret_cast<const uint4 *>(g.x + (size_t)m * in_features + column);
@@ -838,7 +891,7 @@ __global__ void __launch_bounds__(kGemvThreads, DF11_GEMV_MIN_CTAS) df11_gemv_ke
                 s1 = bf16_dot2(w[7], xb.w, s1);
                 sum[m] = s0 + s1;
             }
-            if (sub != run - 1u) return;
+            if (half != EPT / 16 - 1 || sub != run - 1u) return;
             // end of the run: add the lanes up; a run that is a whole row gives the output itself
 #pragma unroll
             for (int m = 0; m < M; ++m) {
@@ -949,12 +1002,18 @@ __global__ void __launch_bounds__(kThreads, 3) df11_decode_kernel(const Params p
             return;
         }
         mbar_expect_tx(bar, total);
+        if (b == p.drop_block) return;  // self-test: bytes announced, nothing issued, nothing in flight
         if (with_codes) bulk_g2s(dst, p.codes + b * DF11_BLOCK_BYTES, kCodesBufBytes, bar);
         if (side_streamed)
             bulk_g2s(dst + kCodesBufBytes, p.gaps + b * DF11_GAP_BYTES_PER_BLOCK, DF11_GAP_BYTES_PER_BLOCK, bar);
     };
+    const uint64_t wait_ns = p.wait_ns ? p.wait_ns : kWaitNs;
+    uint32_t n_in[2] = {0, 0}, n_sm = 0;  // copies announced per barrier so far (uniform over the CTA)
 
-    if (tid == 0 && (int64_t)blockIdx.x < p.n_blocks) issue_inputs(blockIdx.x, 0);
+    if ((int64_t)blockIdx.x < p.n_blocks) {
+        if (tid == 0) issue_inputs(blockIdx.x, 0);
+        ++n_in[0];
+    }
 
     uint32_t it = 0;
     for (int64_t b = blockIdx.x; b < p.n_blocks; b += gridDim.x, ++it) {
@@ -963,11 +1022,14 @@ __global__ void __launch_bounds__(kThreads, 3) df11_decode_kernel(const Params p
 
         // next block's inputs start flowing into the other buffer (all its readers passed
         // the barrier that ended the previous iteration)
-        if (tid == 0 && b + gridDim.x < p.n_blocks) issue_inputs(b + gridDim.x, cur ^ 1u);
+        if (b + gridDim.x < p.n_blocks) {
+            if (tid == 0) issue_inputs(b + gridDim.x, cur ^ 1u);
+            ++n_in[cur ^ 1u];
+        }
 
-        // after one wait has run out, later ones give up quickly: the launch is lost anyway
-        if (!mbar_wait(bar_in + 8 * cur, (it >> 1) & 1u, (bad & DF11_STATUS_TIMEOUT) ? 8u : kWaitLimit))
-            bad |= DF11_STATUS_TIMEOUT;
+        // A wait that runs out: this thread goes through the block on whatever its buffer holds
+        // (every index below is clamped) and the CTA leaves the loop at the block's last barrier.
+        if (!mbar_wait(bar_in + 8 * cur, (it >> 1) & 1u, wait_ns)) bad |= DF11_STATUS_TIMEOUT;
 
         // ---- block bookkeeping (uniform) ---------------------------------------------------
         const int64_t base = (int64_t)__ldg(p.pos + b);
@@ -1005,6 +1067,7 @@ __global__ void __launch_bounds__(kThreads, 3) df11_decode_kernel(const Params p
                 mbar_arrive(bar_sm);
             }
         }
+        ++n_sm;
         for (uint32_t i = max(tma_bytes, phase) + tid; i < last; i += kThreads)
             smem[tile_off + i] = __ldg(sm_blk + i);
 
@@ -1047,7 +1110,7 @@ __global__ void __launch_bounds__(kThreads, 3) df11_decode_kernel(const Params p
             if (tbad) bad |= DF11_STATUS_BAD_TABLE;
         }
         __syncthreads();
-        if (!mbar_wait(bar_sm, it & 1u, (bad & DF11_STATUS_TIMEOUT) ? 8u : kWaitLimit)) bad |= DF11_STATUS_TIMEOUT;
+        if (!mbar_wait(bar_sm, it & 1u, (bad & DF11_STATUS_TIMEOUT) ? 0ull : wait_ns)) bad |= DF11_STATUS_TIMEOUT;
 
         // ---- merge with sign/mantissa ------------------------------------------------------------
         // Groups of eight elements aligned to eight in the output: group g covers staging and tile
@@ -1074,9 +1137,22 @@ __global__ void __launch_bounds__(kThreads, 3) df11_decode_kernel(const Params p
             for (uint32_t i = phase + tid; i < last; i += kThreads)
                 out_blk[i] = df11_merge1(lds8(mem.stage_addr + i), lds8(tile_addr + i));
         }
-        __syncthreads();  // staging, tile, wsum and this input buffer are reused
+        // staging, tile, wsum and this input buffer are reused; and if any thread's wait ran out the
+        // CTA stops here: its remaining blocks stay undecoded, the status word says so
+        if (__syncthreads_or(bad & DF11_STATUS_TIMEOUT)) break;
     }
 
+    // Never retire with a copy still on its way into this CTA's shared memory: the thread that
+    // issued the copies waits (bounded) for the last phase announced on each barrier.  After a
+    // normal run all of them completed long ago and this costs three polls.
+    if (tid == 0) {
+        const uint64_t drain_ns = p.wait_ns ? p.wait_ns : kDrainNs;
+        bool drained = true;
+        if (n_in[0]) drained &= mbar_wait(bar_in, (n_in[0] - 1u) & 1u, drain_ns);
+        if (n_in[1]) drained &= mbar_wait(bar_in + 8, (n_in[1] - 1u) & 1u, drain_ns);
+        if (n_sm) drained &= mbar_wait(bar_sm, (n_sm - 1u) & 1u, drain_ns);
+        if (!drained) bad |= DF11_STATUS_TIMEOUT;
+    }
     if (bad && p.status != nullptr) atomicOr(p.status, bad);
 }
 
@@ -1091,7 +1167,7 @@ struct DeviceInfo {
 };
 std::mutex g_mutex;
 DeviceInfo g_devices[64];
-bool g_attr_set[64][14] = {};
+bool g_attr_set[64][24] = {};
 
 struct DeviceGuard {
     int prev = -1;
@@ -1117,7 +1193,7 @@ struct OccupancyCache {
     size_t smem = ~(size_t)0;
     int per_sm = 0;
 };
-OccupancyCache g_occupancy[64][14];
+OccupancyCache g_occupancy[64][24];
 
 template <class Kernel>
 int ctas_per_sm(Kernel kernel, int device, int slot, int threads, size_t smem, int *per_sm)
@@ -1274,14 +1350,21 @@ int launch_decode(const Params &p, int device, cudaStream_t stream)
     return launch(df11_decode_kernel<kTableBits>, kThreads, 0, smem, p.n_blocks, p, device, stream);
 }
 
-// Elements per seek point of the prepared form: 16 unless DF11_EPT=32 is set in the environment
-// (half the auxiliary memory, longer dependent chains per thread).  Read once per process.
+// Elements per seek point of the prepared form, process-wide: DF11_EPT in the environment (16 or
+// 32) when the library is first used, else DF11_DEFAULT_EPT; df11_seek_interval() changes it.
+#ifndef DF11_DEFAULT_EPT
+#define DF11_DEFAULT_EPT 16
+#endif
+std::atomic<int> g_ept{0};
 int elements_per_seek_point()
 {
-    static const int ept = [] {
+    int ept = g_ept.load(std::memory_order_relaxed);
+    if (ept == 0) {
         const char *e = getenv("DF11_EPT");
-        return (e && atoi(e) == 32) ? 32 : 16;
-    }();
+        const int v = e ? atoi(e) : 0;
+        ept = (v == 16 || v == 32) ? v : DF11_DEFAULT_EPT;
+        g_ept.store(ept, std::memory_order_relaxed);
+    }
     return ept;
 }
 
@@ -1344,6 +1427,7 @@ Params base_params(const void *luts, const void *codes, const void *pos, const v
     p.n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
     p.n_luts = n_luts;
     p.stage_bytes = 16;
+    p.drop_block = -1;
     p.codes_aligned = (((uintptr_t)codes & 15) == 0 ? 1 : 0) | (((uintptr_t)gaps & 15) == 0 ? 2 : 0) |
                       (((uintptr_t)codes & 3) == 0 ? 4 : 0);
     return p;
@@ -1369,6 +1453,32 @@ extern "C" int df11_decode(const void *luts, const void *codes, const void *sign
     return launch_decode(p, device, (cudaStream_t)stream);
 }
 
+extern "C" int df11_selftest_wait_timeout(const void *luts, const void *codes, const void *sign_mantissa,
+                                          const void *output_positions, const void *gaps, void *out_bf16,
+                                          int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                                          int32_t max_block_elems, int64_t drop_block, void *status, int32_t device,
+                                          void *stream)
+{
+    int rc = check_common(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements);
+    if (rc != DF11_OK) return rc;
+    if (!sign_mantissa || !out_bf16 || n_bytes == 0 || n_elements == 0)
+        return df11_fail(DF11_ERR_BADARG, "the self-test needs a non-empty unit");
+    Params p = base_params(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements, status);
+    if (drop_block < 0 || drop_block >= p.n_blocks)
+        return df11_fail(DF11_ERR_BADARG, "drop_block = %lld, the unit has %lld format blocks", (long long)drop_block,
+                         (long long)p.n_blocks);
+    p.sm = (const uint8_t *)sign_mantissa;
+    p.out = (uint16_t *)out_bf16;
+    p.stage_bytes = stage_bytes_for(max_block_elems);
+    p.sm_aligned = ((uintptr_t)sign_mantissa & 15) == 0;
+    p.out_aligned = ((uintptr_t)out_bf16 & 15) == 0;
+    if (!(p.codes_aligned & 1) && !(p.codes_aligned & 2))
+        return df11_fail(DF11_ERR_BADARG, "the self-test needs 16-byte aligned tensors (no bulk copy otherwise)");
+    p.drop_block = drop_block;
+    p.wait_ns = 2ull * 1000 * 1000;  // 2 ms per wait: the CTA that owns the block gives up after ~4 ms
+    return launch_decode(p, device, (cudaStream_t)stream);
+}
+
 namespace {
 // Auxiliary buffer: decode table | seek points, high parts (uint32 per 32 groups, padded to 16
 // bytes) | seek points, low parts (uint16 per group, 32 per chunk).
@@ -1387,6 +1497,15 @@ AuxLayout aux_layout(int64_t n_elements, int ept)
     return a;
 }
 }  // namespace
+
+extern "C" int df11_seek_interval(int32_t elements)
+{
+    if (elements == 0) return elements_per_seek_point();
+    if (elements != 16 && elements != 32)
+        return df11_fail(DF11_ERR_BADARG, "a seek point every %d elements: 16 and 32 are supported", elements);
+    g_ept.store(elements, std::memory_order_relaxed);
+    return elements;
+}
 
 extern "C" int64_t df11_aux_bytes(int64_t n_bytes, int64_t n_elements)
 {
@@ -1427,13 +1546,16 @@ extern "C" int df11_prepare(const void *luts, const void *codes, const void *out
 }
 
 namespace {
+// first_element / range_elements: which part of the unit to produce (range_elements < 0: all of
+// it); `out_bf16` receives that part from its first element on.
 int decode_prepared(const void *luts, const void *codes, const void *sign_mantissa, const void *output_positions,
                     const void *gaps, const void *aux, void *out_bf16, int32_t n_luts, int64_t n_bytes,
-                    int64_t n_elements, void *status, int32_t device, void *stream, int max_ctas_per_sm)
+                    int64_t n_elements, void *status, int32_t device, void *stream, int max_ctas_per_sm,
+                    int64_t first_element = 0, int64_t range_elements = -1)
 {
     int rc = check_common(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements);
     if (rc != DF11_OK) return rc;
-    if (n_bytes == 0 || n_elements == 0) return DF11_OK;
+    if (n_bytes == 0 || n_elements == 0 || range_elements == 0) return DF11_OK;
     if (!sign_mantissa || !out_bf16 || !aux || ((uintptr_t)aux & 15))
         return df11_fail(DF11_ERR_BADARG, "null tensor pointer or misaligned aux buffer");
     if (n_elements > kMaxPreparedElements)
@@ -1451,14 +1573,26 @@ int decode_prepared(const void *luts, const void *codes, const void *sign_mantis
     p.ept = ept;
     p.sm_aligned = ((uintptr_t)sign_mantissa & 15) == 0;
     p.out_aligned = ((uintptr_t)out_bf16 & 15) == 0;
+    int64_t chunks = a.n_chunks;
+    if (range_elements >= 0) {
+        const int64_t chunk_elems = 32 * ept;
+        const int64_t end = first_element + range_elements;
+        if (first_element < 0 || end > n_elements || first_element % chunk_elems ||
+            (end % chunk_elems && end != n_elements))
+            return df11_fail(DF11_ERR_BADARG,
+                             "range [%lld, %lld) of a unit of %lld elements: it must start on a multiple of %lld "
+                             "elements and end on one or at the end of the unit",
+                             (long long)first_element, (long long)end, (long long)n_elements, (long long)chunk_elems);
+        p.chunk_first = (uint32_t)(first_element / chunk_elems);
+        p.chunk_count = (uint32_t)((range_elements + chunk_elems - 1) / chunk_elems);
+        chunks = p.chunk_count;
+    }
     // work per CTA pass: one chunk (32 groups) per warp
-    const int64_t cta_items = (a.n_chunks + kFastThreads / 32 - 1) / (kFastThreads / 32);
-    if (ept == 32) {
-        const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
+    const int64_t cta_items = (chunks + kFastThreads / 32 - 1) / (kFastThreads / 32);
+    const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
+    if (ept == 32)
         return launch(df11_fast_kernel<kFastTableBits, 32, false>, kFastThreads, 3, smem, cta_items, p, device,
                       (cudaStream_t)stream, max_ctas_per_sm);
-    }
-    const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
     return launch(df11_fast_kernel<kFastTableBits, 16, false>, kFastThreads, 2, smem, cta_items, p, device,
                   (cudaStream_t)stream, max_ctas_per_sm);
 }
@@ -1482,6 +1616,17 @@ extern "C" int df11_decode_prepared_shared(const void *luts, const void *codes, 
     if (ctas_per_sm < 0) return df11_fail(DF11_ERR_BADARG, "ctas_per_sm = %d", ctas_per_sm);
     return decode_prepared(luts, codes, sign_mantissa, output_positions, gaps, aux, out_bf16, n_luts, n_bytes,
                            n_elements, status, device, stream, ctas_per_sm);
+}
+
+extern "C" int df11_decode_range_prepared(const void *luts, const void *codes, const void *sign_mantissa,
+                                          const void *aux, int64_t first_element, int64_t range_elements,
+                                          void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                                          void *status, int32_t device, void *stream)
+{
+    if (range_elements < 0) return df11_fail(DF11_ERR_BADARG, "negative range length");
+    // output_positions and gaps are not read by the fast decoder; any non-null pointer passes the check
+    return decode_prepared(luts, codes, sign_mantissa, luts, luts, aux, out_bf16, n_luts, n_bytes, n_elements, status,
+                           device, stream, 0, first_element, range_elements);
 }
 
 extern "C" int df11_decode_rows_prepared(const void *luts, const void *codes, const void *sign_mantissa,
@@ -1538,6 +1683,29 @@ extern "C" int64_t df11_gemv_partials_bytes(int64_t n_rows, int64_t in_features,
     return (int64_t)m * n_rows * (in_features / 512) * 4;
 }
 
+namespace {
+template <int EPT>
+int launch_gemv_m(bool interior, int m, size_t smem, int64_t cta_items, const Params &p, const GemvArgs &g, int device,
+                  cudaStream_t s)
+{
+    constexpr int base = EPT == 16 ? 6 : 14;  // kernel slots 6..13 and 14..21
+    if (interior) {
+        switch (m) {
+        case 1: return launch_gemv(df11_gemv_kernel<kFastTableBits, EPT, 1, false>, base + 4, 1, smem, cta_items, p, g, device, s);
+        case 2: return launch_gemv(df11_gemv_kernel<kFastTableBits, EPT, 2, false>, base + 5, 2, smem, cta_items, p, g, device, s);
+        case 3: return launch_gemv(df11_gemv_kernel<kFastTableBits, EPT, 3, false>, base + 6, 3, smem, cta_items, p, g, device, s);
+        default: return launch_gemv(df11_gemv_kernel<kFastTableBits, EPT, 4, false>, base + 7, 4, smem, cta_items, p, g, device, s);
+        }
+    }
+    switch (m) {
+    case 1: return launch_gemv(df11_gemv_kernel<kFastTableBits, EPT, 1, true>, base + 0, 1, smem, cta_items, p, g, device, s);
+    case 2: return launch_gemv(df11_gemv_kernel<kFastTableBits, EPT, 2, true>, base + 1, 2, smem, cta_items, p, g, device, s);
+    case 3: return launch_gemv(df11_gemv_kernel<kFastTableBits, EPT, 3, true>, base + 2, 3, smem, cta_items, p, g, device, s);
+    default: return launch_gemv(df11_gemv_kernel<kFastTableBits, EPT, 4, true>, base + 3, 4, smem, cta_items, p, g, device, s);
+    }
+}
+}  // namespace
+
 extern "C" int df11_gemv_prepared(const void *luts, const void *codes, const void *sign_mantissa, const void *aux,
                                   const void *x_bf16, void *y_bf16, const void *bias_bf16, void *partials,
                                   int64_t first_element, int64_t n_rows, int64_t in_features,
@@ -1550,18 +1718,19 @@ extern "C" int df11_gemv_prepared(const void *luts, const void *codes, const voi
     if (n_bytes < 16 || n_elements <= 0 || n_elements > kMaxPreparedElements)
         return df11_fail(DF11_ERR_BADARG, "unit sizes out of range");
     if (m < 1 || m > 4) return df11_fail(DF11_ERR_BADARG, "m = %d: one to four activation vectors", m);
-    if (elements_per_seek_point() != 16)
-        return df11_fail(DF11_ERR_BADARG, "the fused product needs a seek point every 16 elements (DF11_EPT unset)");
-    if (in_features <= 0 || in_features % 512 || first_element < 0 || first_element % 512 || n_rows < 0 ||
-        n_rows > 0x7FFFFFFF / (in_features / 512) || first_element + n_rows * in_features > n_elements)
+    const int ept = elements_per_seek_point();
+    const int64_t chunk_elems = 32 * ept;
+    if (in_features <= 0 || in_features % chunk_elems || first_element < 0 || first_element % chunk_elems ||
+        n_rows < 0 || n_rows > 0x7FFFFFFF / (in_features / chunk_elems) ||
+        first_element + n_rows * in_features > n_elements)
         return df11_fail(DF11_ERR_BADARG,
-                         "matrix [%lld, %lld] at element %lld: rows must be multiples of 512 elements inside the unit",
-                         (long long)n_rows, (long long)in_features, (long long)first_element);
+                         "matrix [%lld, %lld] at element %lld: rows must be multiples of %lld elements inside the unit",
+                         (long long)n_rows, (long long)in_features, (long long)first_element, (long long)chunk_elems);
     if (((uintptr_t)codes & 3) || ((uintptr_t)sign_mantissa & 15) || ((uintptr_t)aux & 15) || ((uintptr_t)x_bf16 & 15) ||
         ((uintptr_t)partials & 3) || ((uintptr_t)y_bf16 & 1))
         return df11_fail(DF11_ERR_BADARG, "misaligned pointer (stream 4, sign_mantissa / aux / x 16 bytes)");
     if (n_rows == 0) return DF11_OK;
-    const AuxLayout a = aux_layout(n_elements, 16);
+    const AuxLayout a = aux_layout(n_elements, ept);
     Params p = {};
     p.luts = (const uint8_t *)luts;
     p.codes = (const uint8_t *)codes;
@@ -1574,35 +1743,22 @@ extern "C" int df11_gemv_prepared(const void *luts, const void *codes, const voi
     p.n_elements = n_elements;
     p.n_chunks = a.n_chunks;
     p.n_luts = n_luts;
-    p.ept = 16;
+    p.ept = ept;
     GemvArgs g;
     g.x = (const uint16_t *)x_bf16;
     g.y = (uint16_t *)y_bf16;
     g.bias = (const uint16_t *)bias_bf16;
     g.partial = (float *)partials;
-    g.first_chunk = (uint32_t)(first_element / 512);
-    g.chunks_per_row = (uint32_t)(in_features / 512);
+    g.first_chunk = (uint32_t)(first_element / chunk_elems);
+    g.chunks_per_row = (uint32_t)(in_features / chunk_elems);
     g.n_rows = (uint32_t)n_rows;
     const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
     const int64_t cta_items = (n_rows * g.chunks_per_row + kGemvThreads / 32 - 1) / (kGemvThreads / 32);
     // A matrix that stays clear of the unit's last two chunks needs no bounds checks on its
     // stream loads (see lean_tasks); the last matrix of a unit keeps them.
     const bool interior = (int64_t)g.first_chunk + n_rows * g.chunks_per_row + 2 <= a.n_chunks && (n_bytes >> 2) >= 4;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (interior) {
-        switch (m) {
-        case 1: return launch_gemv(df11_gemv_kernel<kFastTableBits, 1, false>, 10, 1, smem, cta_items, p, g, device, s);
-        case 2: return launch_gemv(df11_gemv_kernel<kFastTableBits, 2, false>, 11, 2, smem, cta_items, p, g, device, s);
-        case 3: return launch_gemv(df11_gemv_kernel<kFastTableBits, 3, false>, 12, 3, smem, cta_items, p, g, device, s);
-        default: return launch_gemv(df11_gemv_kernel<kFastTableBits, 4, false>, 13, 4, smem, cta_items, p, g, device, s);
-        }
-    }
-    switch (m) {
-    case 1: return launch_gemv(df11_gemv_kernel<kFastTableBits, 1, true>, 6, 1, smem, cta_items, p, g, device, s);
-    case 2: return launch_gemv(df11_gemv_kernel<kFastTableBits, 2, true>, 7, 2, smem, cta_items, p, g, device, s);
-    case 3: return launch_gemv(df11_gemv_kernel<kFastTableBits, 3, true>, 8, 3, smem, cta_items, p, g, device, s);
-    default: return launch_gemv(df11_gemv_kernel<kFastTableBits, 4, true>, 9, 4, smem, cta_items, p, g, device, s);
-    }
+    if (ept == 32) return launch_gemv_m<32>(interior, m, smem, cta_items, p, g, device, (cudaStream_t)stream);
+    return launch_gemv_m<16>(interior, m, smem, cta_items, p, g, device, (cudaStream_t)stream);
 }
 
 
@@ -1646,16 +1802,18 @@ extern "C" int df11_decode_static(const void *luts, const void *codes, const voi
                                   const void *output_positions, const void *gaps, void *out_bf16, int32_t n_luts,
                                   int64_t n_bytes, int64_t n_elements, void *status, int32_t device, void *stream)
 {
+    int rc = check_common(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements);
+    if (rc != DF11_OK) return rc;  // argument errors come first: they must not cost the set-up below
     if (n_elements > (int64_t)DF11_STATIC_MAX_ELEMENTS)
         return df11_fail(DF11_ERR_NOSPACE,
                          "df11_decode_static handles units of up to %lld elements, this one has %lld; "
                          "use df11_prepare + df11_decode_prepared with a buffer of your own, or df11_decode",
                          (long long)DF11_STATIC_MAX_ELEMENTS, (long long)n_elements);
-    if (n_elements >= 0 && n_bytes >= 0 && df11_aux_bytes(n_bytes, n_elements) > kStaticAuxBytes)
+    if (df11_aux_bytes(n_bytes, n_elements) > kStaticAuxBytes)
         return df11_fail(DF11_ERR_NOSPACE, "the built-in buffer (%lld bytes) is too small for this unit",
                          (long long)kStaticAuxBytes);
     void *aux = nullptr;
-    int rc = static_aux_address(device, &aux);
+    rc = static_aux_address(device, &aux);
     if (rc != DF11_OK) return rc;
     // Both steps go to the caller's stream, so the decode sees the seek points of THIS unit;
     // every entry it reads is written by the step before it, nothing needs to start at zero.

@@ -41,6 +41,7 @@ version = "0.5.0"
 bytes_per_thread = 8
 threads_per_block = (512,)
 offloaded_tensor_names = ("encoded_exponent", "sign_mantissa")
+_unit_tensor_names = ("luts", "encoded_exponent", "sign_mantissa", "output_positions", "gaps", "split_positions")
 
 
 class _Flags:
@@ -53,6 +54,8 @@ class _Flags:
     decode_ahead = False
     sparse = True
     fused = False
+    nvtx = False
+    check_status = False
 
     @classmethod
     def read(cls) -> None:
@@ -61,6 +64,8 @@ class _Flags:
         cls.decode_ahead = env("DF11_DECODE_AHEAD", "0") == "1"
         cls.sparse = env("DF11_SPARSE_EMBEDDING", "1") != "0"
         cls.fused = env("DF11_FUSED_GEMV", "0") == "1"
+        cls.nvtx = env("DF11_NVTX", "0") == "1"
+        cls.check_status = env("DF11_CHECK_STATUS", "0") == "1"
 
     @classmethod
     def current(cls):
@@ -115,6 +120,48 @@ class TensorManager:
             device = torch.device(device)
             for key in [k for k in TensorManager._tensors if k[0] == device]:
                 del TensorManager._tensors[key]
+
+
+_status_words: Dict[torch.device, torch.Tensor] = {}
+_counters = dict(decodes=0, decoded_elements=0, prepares=0, sparse_lookups=0, fused_products=0)
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    """One int32 per device into which every decode launched by the hooks ORs its
+    ``DF11_STATUS_*`` bits (the reference's kernel has no such channel: bad tensors make it
+    read out of bounds or spin, decode.cu:116-118)."""
+    word = _status_words.get(device)
+    if word is None:
+        word = _status_words[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return word
+
+
+def check_status(reset: bool = True) -> None:
+    """Raises ``DF11Error`` if a decode launched by the hooks since the last check met
+    inconsistent tensors (bad table, bad positions, truncated block, timed-out copy) or an
+    embedding index outside its table.  Synchronises with the devices, so it is not called per
+    forward unless ``DF11_CHECK_STATUS=1`` is set."""
+    names = {_lib.STATUS_BAD_TABLE: "bad table", _lib.STATUS_BAD_POSITIONS: "bad positions or index",
+             _lib.STATUS_TRUNCATED: "truncated block", _lib.STATUS_TIMEOUT: "copy timed out"}
+    for device, word in _status_words.items():
+        bits = int(word.item())
+        if bits:
+            if reset:
+                word.zero_()
+            what = ", ".join(n for b, n in names.items() if bits & b) or "unknown"
+            raise _lib.DF11Error(_lib.DF11_ERR_CORRUPT, f"decode on {device} reported status {bits} ({what})")
+
+
+def stats() -> dict:
+    """Counters of the host side since import: decodes launched by the hooks, elements they
+    produced, auxiliary buffers built, sparse embedding lookups, fused products, bytes copied
+    host->device by ``cpu_offload`` and how often the next unit's copy was already under way,
+    decode-ahead hits and misses, and the scratch held per device."""
+    out = dict(_counters)
+    out["offload"] = {str(d): dict(s.stats) for d, s in _OffloadStager._by_device.items()}
+    out["decode_ahead"] = {str(d): dict(a.stats) for d, a in _DecodeAhead._by_device.items()}
+    out["scratch_bytes"] = {f"{d}/slot{slot}": t.numel() * 2 for (d, slot), t in TensorManager._tensors.items()}
+    return out
 
 
 class _OffloadStager:
@@ -298,7 +345,8 @@ class _DecodeAhead:
         self.stream.wait_event(queued)
         with torch.cuda.stream(self.stream):
             ops.decode_prepared(nxt.luts, nxt.encoded_exponent, nxt.sign_mantissa, nxt.output_positions,
-                                nxt.gaps, nxt.df11_aux, out=tensor, ctas_per_sm=ctas)
+                                nxt.gaps, nxt.df11_aux, out=tensor, ctas_per_sm=ctas,
+                                status=_status_word(self.device))
             done = torch.cuda.Event()
             done.record(self.stream)
         self.pending = (nxt, slot, done, tensor)
@@ -314,6 +362,8 @@ def _end_of_forward_hook(_module, _inputs, _output):
     _Flags.in_forward = False
     if _DecodeAhead._by_device:
         _DecodeAhead.end_of_forward()
+    if _Flags.check_status:
+        check_status()
 
 
 def _mark_root(model: nn.Module) -> None:
@@ -421,8 +471,10 @@ def _install_fused(module: nn.Module) -> bool:
 
     def product(x, first, n_rows, in_features, bias):
         rows = x.numel() // in_features
+        _counters["fused_products"] += 1
         return ops.gemv_prepared(module.luts, module.encoded_exponent, module.sign_mantissa, module.df11_aux,
-                                 x.reshape(rows, in_features).contiguous(), first, n_rows, in_features, bias=bias)
+                                 x.reshape(rows, in_features).contiguous(), first, n_rows, in_features, bias=bias,
+                                 status=_status_word(module.luts.device))
 
     def ordinary(x, layer):
         if module.__dict__.get("df11_undecoded"):
@@ -471,7 +523,9 @@ def _decode_whole_unit(module: nn.Module, device: torch.device) -> None:
     reconstructed = TensorManager.allocate_bfloat16(device, n_elements)
     ops.decode_prepared(module.luts, module.encoded_exponent, module.sign_mantissa, module.output_positions,
                         module.gaps, module.df11_aux, out=reconstructed,
-                        max_block_elems=getattr(module, "max_block_elems", 0))
+                        max_block_elems=getattr(module, "max_block_elems", 0), status=_status_word(device))
+    _counters["decodes"] += 1
+    _counters["decoded_elements"] += n_elements
     _inject_weights(module, reconstructed)
     module.__dict__["df11_undecoded"] = False
 
@@ -495,19 +549,31 @@ def get_hook(threads_per_block, bytes_per_thread):
         fast = d.get("df11_fast")
         if fast is not None:
             flags = _Flags.current()
-            if (flags.prepared and not flags.fused and not flags.decode_ahead
+            if (flags.prepared and not flags.fused and not flags.decode_ahead and not flags.nvtx
                     and d["_buffers"].get("encoded_exponent") is fast[0] and d.get("df11_aux") is fast[1]
                     and TensorManager._tensors.get(fast[2]) is fast[3]):
                 rc = decode_prepared_c(*fast[4], raw_stream(fast[5]))
                 if rc:
                     _lib.check(rc)
                 d["df11_undecoded"] = False
+                _counters["decodes"] += 1
+                _counters["decoded_elements"] += fast[4][9]
                 return None
+        if _Flags.current().nvtx:                  # DF11_NVTX=1: one range per unit in profiler timelines
+            torch.cuda.nvtx.range_push(f"df11_decode {type(module).__name__} {module.sign_mantissa.numel() if hasattr(module, 'sign_mantissa') else 'offloaded'}")
+            try:
+                return full_path(module, inputs)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        return full_path(module, inputs)
 
+    def full_path(module, inputs):
+        d = module.__dict__
         device = module.luts.device
         if device.type != "cuda":
             raise RuntimeError("DF11 weights can only be decompressed on a CUDA device; move the model to "
                                f"one (this unit's tables are on {device})")
+        status = _status_word(device)
 
         # compressed tensors: resident buffers, or the staging slot of the offload pipeline
         stager = None
@@ -526,8 +592,10 @@ def get_hook(threads_per_block, bytes_per_thread):
             aux = module.__dict__.get("df11_aux")
             if aux is None or aux.device != device:
                 # once per unit and device: decode table + seek points (derived data, never saved)
-                aux = ops.prepare(module.luts, encoded_exponent, module.output_positions, module.gaps, n_elements)
+                aux = ops.prepare(module.luts, encoded_exponent, module.output_positions, module.gaps, n_elements,
+                                  status=status)
                 module.df11_aux = aux
+                _counters["prepares"] += 1
             if _use_fused_gemv() and stager is None:
                 # decode lazily: the unit's Linear layers multiply straight from the compressed
                 # weights while they are called with a few activation vectors (generation), and
@@ -540,14 +608,21 @@ def get_hook(threads_per_block, bytes_per_thread):
                     return None
             ahead = _DecodeAhead.get(device) if _use_decode_ahead() else None
             if _sparse_embedding(module, inputs, n_elements):
-                # a lookup table: decompress only the rows that are asked for (the reference
+                # A lookup table: decompress only the rows that are asked for (the reference
                 # decodes the whole table on every forward, dfloat11.py:158-161) and look them
-                # up by their position in that small result
+                # up by their position in that small result.  During this forward
+                # ``module.weight`` is that [number of ids, embedding_dim] tensor, not the whole
+                # table; an id outside the table yields row 0 and sets the status word (see
+                # check_status), where F.embedding would raise a device-side assert.
                 ids = inputs[0]
+                if ids.device != device:
+                    ids = ids.to(device)
                 rows = ops.decode_rows_prepared(module.luts, encoded_exponent, sign_mantissa, aux,
                                                 ids.reshape(-1).to(torch.int64), module.embedding_dim,
                                                 out=TensorManager.allocate_bfloat16(
-                                                    device, ids.numel() * module.embedding_dim, slot=2))
+                                                    device, ids.numel() * module.embedding_dim, slot=2),
+                                                status=status)
+                _counters["sparse_lookups"] += 1
                 module.weight = rows
                 module.__dict__["df11_injected"] = None        # the whole-table view is gone
                 if stager is not None:
@@ -560,7 +635,9 @@ def get_hook(threads_per_block, bytes_per_thread):
                 slot = ahead.fresh_slot() if ahead is not None else 0
                 reconstructed = TensorManager.allocate_bfloat16(device, n_elements, slot=slot)
                 ops.decode_prepared(module.luts, encoded_exponent, sign_mantissa, module.output_positions,
-                                    module.gaps, aux, out=reconstructed, max_block_elems=widest)
+                                    module.gaps, aux, out=reconstructed, max_block_elems=widest, status=status)
+                _counters["decodes"] += 1
+                _counters["decoded_elements"] += n_elements
             _inject_weights(module, reconstructed)
             if stager is not None:
                 stager.done(module)
@@ -574,13 +651,15 @@ def get_hook(threads_per_block, bytes_per_thread):
                     (module.luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(),
                      module.output_positions.data_ptr(), module.gaps.data_ptr(), aux.data_ptr(),
                      reconstructed.data_ptr(), module.luts.shape[0], encoded_exponent.numel(), n_elements,
-                     int(widest), None, device.index),
+                     int(widest), status.data_ptr(), device.index),
                     device.index)
             return None
 
         reconstructed = TensorManager.allocate_bfloat16(device, n_elements)
         ops.decode(module.luts, encoded_exponent, sign_mantissa, module.output_positions, module.gaps,
-                   out=reconstructed, max_block_elems=widest)
+                   out=reconstructed, max_block_elems=widest, status=status)
+        _counters["decodes"] += 1
+        _counters["decoded_elements"] += n_elements
         _inject_weights(module, reconstructed)
         if stager is not None:
             stager.done(module)
@@ -654,18 +733,24 @@ def load_and_replace_tensors(
             if target is None:
                 target = buffers.get(tensor_name)
             if target is not None:
-                if target.shape == value.shape:
-                    with torch.no_grad():
-                        target.copy_(value)
-                else:
-                    print(f"Shape mismatch for {tensor_name}: model {tuple(target.shape)} vs loaded "
-                          f"{tuple(value.shape)}", file=stderr)
+                if target.shape != value.shape:
+                    # the reference prints and goes on with the uninitialised tensor
+                    # (dfloat11.py:230-232); a model that silently computes with garbage is worse
+                    raise ValueError(f"Shape mismatch for {tensor_name}: model {tuple(target.shape)} vs loaded "
+                                     f"{tuple(value.shape)}")
+                with torch.no_grad():
+                    target.copy_(value)
                 continue
 
             module_path, _, leaf = tensor_name.rpartition(".")
             module = modules.get(module_path)
             if module is None:
                 print(f"Cannot find module path for {tensor_name}", file=stderr)
+                continue
+            if leaf not in _unit_tensor_names:
+                # an ordinary tensor the model has no place for (a bias of a layer that has none
+                # here): not part of a compressed unit, so nothing to arm
+                print(f"No parameter or buffer for {tensor_name}; skipped", file=stderr)
                 continue
             units[module_path] = module
 

@@ -110,10 +110,32 @@ def decode_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_man
     return out
 
 
+def seek_interval(elements: int = 0) -> int:
+    """Elements per seek point of the prepared form (16 or 32), process-wide; a non-zero argument
+    sets it.  Buffers made by ``prepare`` are only valid under the setting they were made under."""
+    return _lib.check(_lib.lib.df11_seek_interval(int(elements)))
+
+
 def chunk_elements() -> int:
-    """Elements per independently decodable chunk of the prepared form (32 groups)."""
-    import os
-    return 32 * (32 if os.environ.get("DF11_EPT") == "32" else 16)
+    """Elements per independently decodable chunk of the prepared form (32 seek intervals)."""
+    return 32 * seek_interval()
+
+
+def decode_range_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_mantissa: torch.Tensor,
+                          aux: torch.Tensor, first_element: int, range_elements: int, out: torch.Tensor,
+                          status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decompress elements ``[first_element, first_element + range_elements)`` of a prepared unit into
+    ``out[:range_elements]``.  The range starts on a multiple of ``chunk_elements()`` and ends on one
+    or at the end of the unit."""
+    device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, sign_mantissa=sign_mantissa,
+                           aux=aux, out=out, status=status)
+    if out.dtype != torch.bfloat16 or out.numel() < range_elements:
+        raise RuntimeError("`out` must be a bfloat16 tensor with at least range_elements elements")
+    _lib.check(_lib.lib.df11_decode_range_prepared(
+        luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(), aux.data_ptr(),
+        int(first_element), int(range_elements), out.data_ptr(), luts.shape[0], encoded_exponent.numel(),
+        sign_mantissa.numel(), status.data_ptr() if status is not None else None, device.index, _stream(device)))
+    return out[:range_elements]
 
 
 def decode_rows_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_mantissa: torch.Tensor,

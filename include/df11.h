@@ -15,7 +15,9 @@
  *   - Nothing here allocates or frees device memory, synchronises the device or
  *     the stream, or keeps a pointer after returning.  Launches go to the given
  *     stream of the given device (the reference launches on cupy's current
- *     stream, dfloat11.py:142).
+ *     stream, dfloat11.py:142).  One exception, df11_decode_static: it works in a
+ *     fixed array that is part of the library image, remembers that array's device
+ *     address per device, and its calls on one device must not overlap (see there).
  *   - Every function returns DF11_OK (0) or a negative DF11_ERR_* code;
  *     df11_last_error() gives the message for the calling thread's last failure.
  *   - Functions are re-entrant and may be called from several threads.
@@ -82,6 +84,22 @@ int df11_decode(const void *luts, const void *codes, const void *sign_mantissa,
                 int32_t max_block_elems, void *status, int32_t device, void *stream);
 
 /*
+ * Self-test of the bounded waits in df11_decode's kernel.  Same arguments and launch as
+ * df11_decode, except that the bulk copy of format block `drop_block`'s stream bytes is
+ * announced to its barrier but never issued, and every wait is cut to 2 ms.  Nothing is in
+ * flight, nothing faults: the CTA that owns that block finds its wait running out, ORs
+ * DF11_STATUS_TIMEOUT into `status`, stops decoding and returns; the other CTAs finish their
+ * blocks.  The call returns DF11_OK (the launch itself succeeded); the elements of the blocks
+ * that CTA did not reach are unspecified.  For tests and for checking an installation; the
+ * reference's kernel has no waits to bound (it loads synchronously, decode.cu:35-78).
+ */
+int df11_selftest_wait_timeout(const void *luts, const void *codes, const void *sign_mantissa,
+                               const void *output_positions, const void *gaps, void *out_bf16,
+                               int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                               int32_t max_block_elems, int64_t drop_block, void *status,
+                               int32_t device, void *stream);
+
+/*
  * Optional two-step form for units that are decoded many times (every forward
  * pass, dfloat11.py:119-151).  df11_prepare() runs once per unit and device: it
  * fills a caller-owned auxiliary device buffer with (a) the multi-symbol decode
@@ -93,12 +111,24 @@ int df11_decode(const void *luts, const void *codes, const void *sign_mantissa,
  * derived data and can be rebuilt at any time.
  *
  * df11_aux_bytes(n_bytes, n_elements) is the size of that buffer (about
- * n_elements/8 + 16 KiB; half of that with DF11_EPT=32 in the environment, which
- * places a seek point every 32 elements).  The buffer must be 16-byte aligned.
+ * n_elements/8 + 32 KiB with a seek point every 16 elements, half of that with one
+ * every 32, see df11_seek_interval).  The buffer must be 16-byte aligned.
  * `max_block_elems` is accepted for symmetry with df11_decode and ignored.  This
  * form has no counterpart in the reference.
  */
 int64_t df11_aux_bytes(int64_t n_bytes, int64_t n_elements);
+
+/*
+ * How many consecutive output elements share one seek point of the prepared form: 16 or 32,
+ * one setting for the whole process.  32 halves the auxiliary buffer (n_elements/16 bytes)
+ * and makes the independently decodable chunk 1024 elements instead of 512.  elements = 0
+ * only asks; 16 or 32 sets it; the return value is the setting in force (or a negative
+ * error).  The initial value comes from DF11_EPT in the environment when it is 16 or 32.
+ * A buffer filled by df11_prepare is only valid for calls made under the setting it was
+ * filled under: change it before the first unit is prepared, not in between.
+ * No counterpart in the reference.
+ */
+int df11_seek_interval(int32_t elements);
 
 int df11_prepare(const void *luts, const void *codes, const void *output_positions,
                  const void *gaps, void *aux, int64_t aux_bytes, int32_t n_luts,
@@ -129,6 +159,21 @@ int df11_decode_rows_prepared(const void *luts, const void *codes, const void *s
                               int64_t n_elements, void *status, int32_t device, void *stream);
 
 /*
+ * Decode a contiguous part of a prepared unit: elements [first_element, first_element +
+ * range_elements) go to out_bf16[0 .. range_elements).  The reference always decompresses a
+ * whole unit into its buffer (dfloat11/dfloat11.py:139-151); decoding one matrix of a unit, or
+ * a slab of its rows, right before the product that reads it lets the BF16 copy stay in the
+ * L2 cache instead of travelling to HBM and back.  first_element must be a multiple of the
+ * chunk (32 seek intervals: 512 or 1024 elements), and the range must end on such a multiple
+ * or at the end of the unit.  Same bits as the matching part of df11_decode_prepared's output.
+ * No counterpart in the reference.
+ */
+int df11_decode_range_prepared(const void *luts, const void *codes, const void *sign_mantissa,
+                               const void *aux, int64_t first_element, int64_t range_elements,
+                               void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                               void *status, int32_t device, void *stream);
+
+/*
  * Decode fused with a matrix-vector product: y[j][r] = sum_c W[r][c] * x[j][c] + bias[r] for
  * one [n_rows, in_features] matrix W that lies inside a prepared unit (its first weight is
  * element `first_element` of the unit) and m = 1..4 activation vectors, without writing W
@@ -137,9 +182,15 @@ int df11_decode_rows_prepared(const void *luts, const void *codes, const void *s
  * writes 2 bytes per weight and reads them again.  x is [m][in_features] bf16, y is
  * [m][n_rows] bf16, bias is [n_rows] bf16 or NULL; products are exact and accumulated in
  * fp32 in a fixed order (bit-reproducible run to run; not the order of a library GEMV, so
- * not bit-identical to one).  in_features and first_element must be multiples of 512,
- * `codes` 4-byte and sign_mantissa / aux / x 16-byte aligned, and the unit prepared with
- * a seek point every 16 elements (the default).  `partials` is caller-owned device scratch
+ * not bit-identical to one).  in_features and first_element must be multiples of the chunk
+ * (32 seek intervals: 512 or 1024 elements, see df11_seek_interval), `codes` 4-byte and
+ * sign_mantissa / aux / x 16-byte aligned.  The kernel is launched with programmatic stream
+ * serialization and reads the unit's tensors and `aux` BEFORE it waits for the kernel ahead
+ * of it in the stream; that is safe behind any kernel of this library (none of those that
+ * write such data signals its dependents early) and behind work that finished earlier, but
+ * not behind a foreign kernel that writes these buffers and triggers dependent launches
+ * before it is done.  x, y, bias and `partials` are only touched after the wait.
+ * `partials` is caller-owned device scratch
  * of df11_gemv_partials_bytes() bytes whose contents do not matter; launches that share it
  * must not overlap.  Two kernels are queued: the products, then a small one that adds each
  * row's partial sums.  No counterpart in the reference.
@@ -179,8 +230,12 @@ int df11_decode_prepared_shared(const void *luts, const void *codes, const void 
  *
  *   - Units of more than DF11_STATIC_MAX_ELEMENTS elements are refused with
  *     DF11_ERR_NOSPACE (the message says what to use instead).
- *   - The first call on each device looks up the array's device address; make that
- *     call outside any stream capture.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); where the CUDA runtime loads modules lazily that lookup
+ *     can make the driver load the library's image, array included, which is a
+ *     driver-side allocation.  So "allocates nothing" holds from the second call on a
+ *     device: make one warm-up call per device at start-up, outside any stream
+ *     capture, before relying on it.  Argument errors are reported before that set-up.
  *   - All calls on one device share the array: two calls whose kernels may overlap on
  *     the GPU (different streams) corrupt each other.  Calls ordered on one stream are fine.
  * This entry point has no counterpart in the reference.

@@ -39,6 +39,15 @@ def _widest(pos_u32):
     return int(np.diff(np.asarray(pos_u32).astype(np.int64)).max())
 
 
+@pytest.fixture(params=[16, 32])
+def seek(request):
+    """Runs a test of the prepared form once per seek interval (a process-wide setting)."""
+    before = ops.seek_interval()
+    ops.seek_interval(request.param)
+    yield request.param
+    ops.seek_interval(before)
+
+
 def _unit_from_weights(weights, n_threads=None):
     t = codec.encode_weights(weights, n_threads=n_threads)
     d = dict(luts=t["luts"].to(DEV), enc=t["encoded_exponent"].to(DEV), sm=t["sign_mantissa"].to(DEV),
@@ -62,7 +71,7 @@ def test_golden_two_pass(golden, exact_cap):
     assert np.array_equal(_bits(out), want)
 
 
-def test_golden_prepared(golden):
+def test_golden_prepared(golden, seek):
     d = _to_dev(golden)
     st = _status()
     aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], golden["w"].size, status=st)
@@ -275,7 +284,7 @@ def test_synthetic_distributions(case):
     assert np.array_equal(_bits(out2), w)
 
 
-def test_row_wise_decode_matches_rows_of_the_full_decode():
+def test_row_wise_decode_matches_rows_of_the_full_decode(seek):
     g = torch.Generator().manual_seed(31)
     table = torch.randn(300, 1024, generator=g).to(torch.bfloat16)          # rows of two 512-element chunks
     t, d, widest = _unit_from_weights([table.flatten()])
@@ -299,7 +308,7 @@ def test_row_wise_decode_matches_rows_of_the_full_decode():
 
 @pytest.mark.parametrize("n", [1025, 1536, 1537, 2048, 2049, 2560, 5000, 16 * 4096 + 3])
 @pytest.mark.parametrize("case", ["one_bit_codes", "gaussian"])
-def test_prepared_decode_around_the_last_chunks(n, case):
+def test_prepared_decode_around_the_last_chunks(n, case, seek):
     """Units of three and more 512-element chunks: all but the last two take the decoder's
     unchecked inner loop, the last two its general loop; both must give the oracle's bits."""
     rng = np.random.default_rng(n)
@@ -323,7 +332,7 @@ def test_prepared_decode_around_the_last_chunks(n, case):
     assert torch.all(buf[n:] == 7.0)
 
 
-def test_prepared_decode_of_inconsistent_inputs_stays_in_bounds():
+def test_prepared_decode_of_inconsistent_inputs_stays_in_bounds(seek):
     """A stream of random bytes, and seek points that belong to another stream: the output is
     meaningless, but every read and write stays inside the tensors and the launch returns."""
     rng = np.random.default_rng(5)
@@ -346,8 +355,78 @@ def test_prepared_decode_of_inconsistent_inputs_stays_in_bounds():
         assert torch.all(buf[n:] == 7.0)
 
 
+@pytest.mark.parametrize("case", ["one_bit_codes", "gaussian", "deep_codes"])
+def test_range_decode_gives_the_same_bits_as_the_whole_decode(case, seek):
+    """df11_decode_range_prepared: any run of whole chunks (and a run that ends with the unit's
+    ragged tail) equals the same elements of the whole-unit decode; nothing is written past it."""
+    n = 700 * 1024 + 37
+    rng = np.random.default_rng(len(case))
+    if case == "one_bit_codes":
+        e = (rng.random(n) < 0.97).astype(np.uint16) * 5 + 90
+    elif case == "gaussian":
+        e = np.clip(np.rint(rng.normal(120, 2.5, size=n)), 1, 239).astype(np.uint16)
+    else:
+        p = 0.5 ** np.arange(1, 41)
+        e = rng.choice(np.arange(60, 100), size=n, p=p / p.sum()).astype(np.uint16)
+    sm = rng.integers(0, 256, size=n).astype(np.uint16)
+    w = (((sm & 0x80) << 8) | (e << 7) | (sm & 0x7F)).astype(np.uint16)
+    t, d, widest = _unit_from_weights([torch.from_numpy(w.view(np.int16)).view(torch.bfloat16)])
+    st = _status()
+    aux = ops.prepare(d["luts"], d["enc"], d["pos"], d["gaps"], n, status=st)
+    ce = ops.chunk_elements()
+    assert ce == 32 * seek
+    n_chunks = -(-n // ce)
+    for first_chunk, chunks in ((0, 1), (0, n_chunks), (3, 200), (n_chunks - 3, 3), (n_chunks - 1, 1),
+                                (n_chunks - 40, 38), (1, n_chunks - 3)):
+        first = first_chunk * ce
+        count = min(n, (first_chunk + chunks) * ce) - first
+        buf = torch.full((count + 64,), 7.0, dtype=torch.bfloat16, device=DEV)
+        got = ops.decode_range_prepared(d["luts"], d["enc"], d["sm"], aux, first, count, out=buf, status=st)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        assert np.array_equal(_bits(got), w[first:first + count]), (first_chunk, chunks)
+        assert torch.all(buf[count:] == 7.0)
+    for first, count in ((5, ce), (0, ce + 1), (ce, n), (-ce, ce)):          # not on chunk boundaries / outside
+        with pytest.raises(_lib.DF11Error):
+            ops.decode_range_prepared(d["luts"], d["enc"], d["sm"], aux, first, count,
+                                      out=torch.empty(n + ce, dtype=torch.bfloat16, device=DEV))
+
+
+def test_a_wait_that_runs_out_sets_the_status_and_the_kernel_returns():
+    """The bounded waits of the self-contained decoder: one format block's input copy is
+    announced but never issued (nothing is in flight, nothing can fault), so the CTA that owns
+    the block gives up after a few milliseconds, reports DF11_STATUS_TIMEOUT and returns.  The
+    context stays usable: the same unit decodes bit-exactly right afterwards."""
+    g = torch.Generator().manual_seed(77)
+    w = (torch.randn(900_000, generator=g) * 0.02).to(torch.bfloat16)
+    t, d, widest = _unit_from_weights([w])
+    n_blocks = -(-d["enc"].numel() // 4096)
+    assert n_blocks > 40
+    st = _status()
+    out = torch.zeros(w.numel(), dtype=torch.bfloat16, device=DEV)
+    stream = torch.cuda.current_stream(torch.device(DEV)).cuda_stream
+    rc = _lib.lib.df11_selftest_wait_timeout(
+        d["luts"].data_ptr(), d["enc"].data_ptr(), d["sm"].data_ptr(), d["pos"].data_ptr(), d["gaps"].data_ptr(),
+        out.data_ptr(), d["luts"].shape[0], d["enc"].numel(), w.numel(), widest, 17, st.data_ptr(), 0, stream)
+    assert rc == _lib.DF11_OK
+    torch.cuda.synchronize()
+    assert st.item() & _lib.STATUS_TIMEOUT
+    pos = t["output_positions"].numpy().view(np.uint32)
+    # blocks of other CTAs are decoded as usual (one CTA per block at this size)
+    assert torch.equal(out[:pos[17]].cpu().view(torch.int16), w[:pos[17]].view(torch.int16))
+    assert torch.equal(out[pos[18]:].cpu().view(torch.int16), w[pos[18]:].view(torch.int16))
+    st.zero_()
+    again = ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], max_block_elems=widest, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0 and torch.equal(again.cpu().view(torch.int16), w.view(torch.int16))
+    assert _lib.lib.df11_selftest_wait_timeout(
+        d["luts"].data_ptr(), d["enc"].data_ptr(), d["sm"].data_ptr(), d["pos"].data_ptr(), d["gaps"].data_ptr(),
+        out.data_ptr(), d["luts"].shape[0], d["enc"].numel(), w.numel(), widest, n_blocks, st.data_ptr(), 0,
+        stream) == _lib.DF11_ERR_BADARG
+
+
 @pytest.mark.parametrize("m", [1, 2, 3, 4])
-def test_fused_matrix_vector_product(m):
+def test_fused_matrix_vector_product(m, seek):
     """df11_gemv_prepared against an fp32 product with the decoded weights: one BF16 rounding of
     the exact-product, fp32-accumulated sum (tolerance: one BF16 unit in the last place of the
     result plus fp32 accumulation noise), for two matrices inside one unit, with and without
@@ -376,7 +455,7 @@ def test_fused_matrix_vector_product(m):
 
 
 @pytest.mark.parametrize("rows,in_features", [(10656, 1024), (7104, 2048), (4096, 4096), (9472, 2048), (4736, 8192)])
-def test_fused_product_with_longer_runs(rows, in_features):
+def test_fused_product_with_longer_runs(rows, in_features, seek):
     """Shapes that make the fused kernel choose its different work splits (on a 148-SM part with
     32 resident warps per SM: single chunks; runs of 2 of a row's 4 chunks plus the adding-up
     kernel; one whole row per warp on a shrunk grid; whole rows in two full rounds; runs of 8 of

@@ -27,17 +27,22 @@ LLAMA_PATTERNS = {
 }
 
 
-def tiny_llama(seed=0):
+def tiny_llama(seed=0, attention_bias=False, bias_seed=None):
     from transformers import LlamaConfig, LlamaForCausalLM
     cfg = LlamaConfig(hidden_size=256, intermediate_size=704, num_hidden_layers=3, num_attention_heads=8,
                       num_key_value_heads=2, vocab_size=1024, max_position_embeddings=256,
-                      tie_word_embeddings=False)
+                      tie_word_embeddings=False, attention_bias=attention_bias)
     torch.manual_seed(seed)
     model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
     with torch.no_grad():
         for name, p in model.named_parameters():
             if p.dim() == 2:
                 p.copy_((torch.randn(p.shape) * (1.0 if "embed" in name else 0.02)).to(torch.bfloat16))
+        if bias_seed is not None:                       # q/k/v/o biases (the Qwen2 layout), seeded
+            g = torch.Generator().manual_seed(bias_seed)
+            for name, p in model.named_parameters():
+                if name.endswith("bias"):
+                    p.copy_((torch.randn(p.shape, generator=g) * 0.1).to(torch.bfloat16))
     return model
 
 
@@ -229,6 +234,30 @@ def test_fused_product_groups_follow_the_layer_families():
     assert host._fused_layers(block) is None
 
 
+def test_from_pretrained_builds_its_own_skeleton(saved):
+    """The call the reference's README shows: only a path.  The skeleton comes from the saved
+    ``config.json`` (AutoConfig -> from_config without weight initialisation, dfloat11.py:409-419),
+    ``dfloat11_config`` is read from that same file, ordinary tensors (norms) come from what
+    ``save_pretrained`` wrote beside the units (dfloat11.py:600-604,619-622)."""
+    path, reference = saved
+    model = df11.DFloat11Model.from_pretrained(path, device="cpu")
+    assert type(model).__name__ == "LlamaForCausalLM" and not model.training
+    assert model.config.dfloat11_config["bytes_per_thread"] == 8
+    ref_params = dict(reference.named_parameters())
+    seen = 0
+    for name, p in model.named_parameters():                     # what is left are the uncompressed tensors
+        assert p.dtype == torch.bfloat16 and torch.equal(p.data, ref_params[name].data), name
+        seen += 1
+    assert seen == 2 * 3 + 1                                      # two norms per layer and the final norm
+    for name, unit in [("model.layers.2", model.model.layers[2]), ("lm_head", model.lm_head)]:
+        out = oracle.decode_c(unit.luts.numpy(), unit.encoded_exponent.numpy(), unit.sign_mantissa.numpy(),
+                              unit.output_positions.numpy(), unit.gaps.numpy())
+        ref_unit = reference.get_submodule(name)
+        want = torch.cat([p.data.flatten() for _, p in ref_unit.named_parameters() if p.dim() == 2])
+        assert np.array_equal(out.view(np.int16), want.view(torch.int16).numpy()), name
+        assert not any(n.endswith("weight") and p.dim() == 2 for n, p in unit.named_parameters())
+
+
 def test_graphed_decoder_refuses_a_model_that_is_not_on_a_gpu():
     with pytest.raises(RuntimeError):
         df11.GraphedGreedyDecoder(nn.Linear(2, 2))
@@ -274,6 +303,21 @@ def test_logits_identical_to_bf16_model(saved, mode, monkeypatch):
         assert ahead is not None and ahead.stats["hits"] > 0 and ahead.pending is None
     else:
         assert ahead is None or ahead.stats["launched"] == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("offload", [False, True])
+def test_from_pretrained_without_a_skeleton_gives_bf16_logits(saved, offload):
+    """Default branch of ``from_pretrained`` (no ``bfloat16_model``) end to end on the GPU."""
+    path, reference = saved
+    model = df11.DFloat11Model.from_pretrained(path, device="cuda:0", cpu_offload=offload)
+    ref = copy.deepcopy(reference).to("cuda:0")
+    ids = torch.randint(0, 1024, (2, 21), generator=torch.Generator().manual_seed(11)).to("cuda:0")
+    with torch.no_grad():
+        for _ in range(2):
+            assert torch.equal(model(input_ids=ids).logits, ref(input_ids=ids).logits)
+        assert torch.equal(model.generate(ids[:1, :6], max_new_tokens=10, do_sample=False),
+                           ref.generate(ids[:1, :6], max_new_tokens=10, do_sample=False))
 
 
 @pytest.mark.gpu

@@ -49,7 +49,43 @@ def test_compress_model_tp_writes_one_directory_per_rank(tmp_path):
     assert (q.out_features, q.in_features) == (128, 256) and (o.out_features, o.in_features) == (256, 128)
     n = sum(m.out_features * m.in_features for m in loaded.model.layers[0].weight_injection_modules)
     assert loaded.model.layers[0].sign_mantissa.numel() == n
-    assert loaded.lm_head.sign_mantissa.numel() == 1024 * 256           # replicated, not sharded
+    assert loaded.lm_head.sign_mantissa.numel() == 512 * 256            # this rank's half of the vocabulary
+    assert loaded.model.embed_tokens.sign_mantissa.numel() == 512 * 256
+    assert loaded.model.embed_tokens.num_embeddings == 512 and loaded.lm_head.out_features == 512
+
+
+def _unit_weights_by_oracle(module):
+    out = oracle.decode_c(module.luts.numpy(), module.encoded_exponent.numpy(), module.sign_mantissa.numpy(),
+                          module.output_positions.numpy(), module.gaps.numpy())
+    return torch.from_numpy(out.view(np.int16)).view(torch.bfloat16)
+
+
+def test_biases_are_sharded_with_their_layers(tmp_path):
+    """Column-parallel biases are cut like the rows they belong to, a row-parallel bias lives on
+    rank 0 only, and the default loader path (no ``bfloat16_model``) ends up with exactly those."""
+    full = tiny_llama(attention_bias=True)
+    with torch.no_grad():
+        for name, p in full.named_parameters():
+            if name.endswith("bias"):
+                p.copy_(torch.randn(p.shape).to(torch.bfloat16))
+    want = copy.deepcopy(full)
+    tp.compress_model_tp(full, LLAMA_PATTERNS, str(tmp_path), tp_size=2)
+    for rank in range(2):
+        loaded = df11.DFloat11Model.from_pretrained(str(tmp_path), device="cpu", tp_size=2, tp_rank=rank)
+        for i, layer in enumerate(loaded.model.layers):
+            ref = want.model.layers[i].self_attn
+            att = layer.self_attn
+            assert torch.equal(att.q_proj.bias.data, ref.q_proj.bias.data.chunk(2)[rank])
+            assert torch.equal(att.k_proj.bias.data, ref.k_proj.bias.data.chunk(2)[rank])
+            if rank == 0:
+                assert torch.equal(att.o_proj.bias.data, ref.o_proj.bias.data)
+            else:
+                assert att.o_proj.bias is None
+            flat = _unit_weights_by_oracle(layer)
+            q = flat[:att.q_proj.out_features * att.q_proj.in_features].view(att.q_proj.out_features, -1)
+            assert torch.equal(q, ref.q_proj.weight.data.chunk(2, dim=0)[rank])
+        emb = _unit_weights_by_oracle(loaded.model.embed_tokens).view(512, 256)
+        assert torch.equal(emb, want.model.embed_tokens.weight.data[rank * 512:(rank + 1) * 512])
 
 
 def _tp_worker(rank, world, port, use_cuda, path, ids, want, q):
@@ -68,18 +104,19 @@ def _tp_worker(rank, world, port, use_cuda, path, ids, want, q):
                 b = df(input_ids=ids.to(dev)).logits
             q.put((rank, bool(torch.equal(a, b)), float((a.float().cpu() - want).abs().max())))
         else:
-            model = tiny_llama().float()
+            model = tiny_llama(attention_bias=True, bias_seed=3).float()
             tp.apply_tensor_parallel(model, LLAMA_PATTERNS, world, rank)
+            assert model.model.embed_tokens.num_embeddings == 1024 // world
             with torch.no_grad():
                 got = model(input_ids=ids).logits
-            q.put((rank, True, float((got - want).abs().max())))
+            q.put((rank, got.shape[-1] == 1024, float((got - want).abs().max())))
     finally:
         dist.destroy_process_group()
 
 
 def _run_ranks(world, use_cuda, path=None):
     ids = torch.randint(0, 1024, (2, 17), generator=torch.Generator().manual_seed(4))
-    ref = tiny_llama().float() if not use_cuda else tiny_llama()
+    ref = tiny_llama(attention_bias=True, bias_seed=3).float() if not use_cuda else tiny_llama()
     with torch.no_grad():
         want = ref(input_ids=ids).logits.float()
     ctx = mp.get_context("spawn")
@@ -98,8 +135,8 @@ def _run_ranks(world, use_cuda, path=None):
 def test_all_reduce_wiring_on_two_gloo_ranks():
     results = _run_ranks(2, use_cuda=False)
     assert [r[0] for r in results] == [0, 1]
-    for _, _, err in results:                       # fp32 on CPU: only the summation order differs
-        assert err < 1e-3
+    for _, gathered, err in results:                # fp32 on CPU: only the summation order differs
+        assert gathered and err < 1e-3              # full-vocabulary logits on every rank
 
 
 @pytest.mark.gpu
