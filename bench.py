@@ -58,6 +58,11 @@ WORKLOADS = {"flux-dit": FLUX_DIT, "qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "
              "llama-405b-tp": LLAMA_405B_TP}
 
 
+# DRAM bytes per element of one df11_fast_kernel launch on a 192.9 M-element Qwen3-8B block unit,
+# from the ncu capture summarised in profiles/df11_fast_kernel_one_qwen3_block.md, by seek interval.
+DRAM_BYTES_PER_ELEMENT = {16: None, 32: None}
+
+
 def block_shapes(cfg):
     h, kv, it = cfg["hidden"], cfg["kv"], cfg["inter"]
     return [(h, h), (kv, h), (kv, h), (h, h), (it, h), (it, h), (h, it)]
@@ -172,7 +177,7 @@ def measured_hbm_peak():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json, stream copy)"
     except Exception:  # noqa: BLE001
-        return 6650.0, "fallback (earlier measurement on this pool)"
+        return 6650.0, "fallback (no MEASURED_PEAKS.json beside bench.py)"
 
 
 def dist_setup(n_gpus):
@@ -211,7 +216,7 @@ def barrier(world, device):
     torch.cuda.synchronize(device)
 
 
-def time_reference_gpu_kernel(unit, scratch, iters=10):
+def time_reference_gpu_kernel(unit, scratch, iters=100, warmup=20):
     """The reference's shipped PTX on one unit: ms per launch, bit-compared with the new kernel."""
     from oracle import ref_kernel
     from dfloat11_b200 import ops
@@ -228,7 +233,7 @@ def time_reference_gpu_kernel(unit, scratch, iters=10):
         if not ref_kernel.available(variant):
             continue
         buf = scratch[:n]
-        for _ in range(3):
+        for _ in range(warmup):
             ref_kernel.decode(unit["luts"], unit["enc"], unit["sm"], unit["pos"], unit["gaps"], buf, smem, variant)
         torch.cuda.synchronize()
         same = bool(torch.equal(buf.view(torch.int16), mine.view(torch.int16)))
@@ -240,55 +245,106 @@ def time_reference_gpu_kernel(unit, scratch, iters=10):
         torch.cuda.synchronize()
         ms = a.elapsed_time(b) / iters
         out[variant] = {"ms_per_launch": round(ms, 4), "GBps": round(algorithmic_bytes(unit) / ms / 1e6, 1),
-                        "bit_identical_to_ours": same}
+                        "bit_identical_to_ours": same, "warmup": warmup, "launches": iters}
     out["unit"] = f"{n} elements"
     return out
 
 
-def cpu_decode_sample(host, n_threads, repeats):
-    """Times the oracle's C decoder on host tensors; returns (best seconds, out checksum)."""
+def cpu_decode_sample(host, n_threads, repeats, warmup=0):
+    """Times the oracle's C decoder on host tensors; returns (mean seconds per decode over
+    `repeats` runs after `warmup` untimed ones, out checksum)."""
     from oracle import df11_oracle as oracle
-    best = None
     out = host.get("_out")
     if out is None:                       # one output buffer, touched once: no page faults in the timings
         out = host["_out"] = np.ones(host["sm"].size, dtype=np.uint16)
-    for _ in range(repeats):
+    times = []
+    for i in range(warmup + repeats):
         t0 = time.perf_counter()
         oracle.decode_c(host["luts"], host["enc"], host["sm"], host["pos"], host["gaps"],
                         n_threads=n_threads, strict=False, out=out)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return best, int(out.view(np.int16).astype(np.int64).sum())
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return sum(times) / len(times), int(out.view(np.int16).astype(np.int64).sum())
+
+
+_HOST_UNIT_SCRIPT = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+from dfloat11_b200 import codec
+n, seed, threads, out = int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
+g = torch.Generator().manual_seed(seed)
+w = torch.empty(n, dtype=torch.bfloat16)
+for s in range(0, n, 1 << 24):
+    e = min(n, s + (1 << 24))
+    w[s:e] = (torch.randn(e - s, generator=g) * 0.02).to(torch.bfloat16)
+t = codec.encode_weights([w], n_threads=threads)
+np.savez(out, luts=t["luts"].numpy(), enc=t["encoded_exponent"].numpy(), sm=t["sign_mantissa"].numpy(),
+         pos=t["output_positions"].numpy().view(np.uint32), gaps=t["gaps"].numpy(),
+         checksum=np.int64(w.view(torch.int16).numpy().astype(np.int64).sum()))
+"""
+
+
+def host_unit_from_subprocess(n, seed, threads):
+    """One compressed unit as host arrays, made by a child process: the process that times the CPU
+    decoder then never loads the package's native library, only the oracle's."""
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "unit.npz")
+        subprocess.run([sys.executable, "-c", _HOST_UNIT_SCRIPT, ROOT, str(n), str(seed), str(threads), path],
+                       check=True, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+        with np.load(path) as z:
+            return {k: z[k].copy() for k in z.files}
+
+
+def cpu_compress_sample(n=1 << 24, seed=5):
+    """The reference's CPU compression rate (its per-symbol Python bit packer,
+    dfloat11_utils.py:118-170,173-187, restated in oracle/): elements per second on one core,
+    on `n` exponents of N(0, 0.02) weights, with the package's packers beside it."""
+    from oracle import df11_oracle as oracle
+    from dfloat11_b200 import codec
+    g = torch.Generator().manual_seed(seed)
+    w = (torch.randn(n, generator=g) * 0.02).to(torch.bfloat16)
+    exponent, _ = codec.split_bf16(w)
+    lens = codec.code_lengths(codec.exponent_histogram(exponent))
+    vals = codec.canonical_codes(lens)
+    symbols = exponent.numpy().tolist()                 # as the reference does (`exponent_8bits.tolist()`)
+    t0 = time.perf_counter()
+    enc, gaps, pos = oracle.encode_stream_py(symbols, lens, vals, 0, 0)
+    t_py = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    enc_h, gaps_h, pos_h = codec.pack_exponents(exponent.numpy(), lens, vals)
+    t_host = time.perf_counter() - t0
+    out = {"value": round(n / t_py / 1e6, 3), "unit": "M elements/s", "cores": 1, "kind": "port",
+           "sample": f"{n} exponents of N(0, 0.02) BF16 weights, per-symbol Python bit packer (one pass)",
+           "host_packer_M_elements_per_s": round(n / t_host / 1e6, 1),
+           "byte_identical": bool(np.array_equal(enc, np.asarray(enc_h)) and np.array_equal(gaps, np.asarray(gaps_h))
+                                  and np.array_equal(pos, np.asarray(pos_h).view(np.uint32)))}
+    if torch.cuda.is_available():
+        dev_e = exponent.to("cuda")
+        codec.pack_exponents_gpu(dev_e, lens, vals)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        codec.pack_exponents_gpu(dev_e, lens, vals)
+        torch.cuda.synchronize()
+        out["gpu_packer_M_elements_per_s"] = round(n / (time.perf_counter() - t0) / 1e6, 1)
+    return out
 
 
 def run_reference_arm(args, cfg):
-    """--impl reference: the CPU decode (oracle port; the reference ships no CPU decoder)."""
+    """--impl reference: the CPU decode (oracle port; the reference ships no CPU decoder) on all
+    host threads.  The unit it decodes is made by a child process, so this process loads the
+    oracle's library only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from oracle import df11_oracle as oracle
-    from dfloat11_b200 import codec
     oracle.build()
     cores = oracle.max_threads()
     n = sum(a * b for a, b in block_shapes(cfg))
-    g = torch.Generator().manual_seed(1)
-    w = torch.empty(n, dtype=torch.bfloat16)
-    for s in range(0, n, 1 << 24):
-        e = min(n, s + (1 << 24))
-        w[s:e] = (torch.randn(e - s, generator=g) * 0.02).to(torch.bfloat16)
-    t = codec.encode_weights([w], n_threads=cores)
+    host = host_unit_from_subprocess(n, 1, cores)
     torch.set_num_threads(1)              # torch's worker threads must not compete with the decoder's
-    host = dict(luts=t["luts"].numpy(), enc=t["encoded_exponent"].numpy(), sm=t["sign_mantissa"].numpy(),
-                pos=t["output_positions"].numpy().view(np.uint32), gaps=t["gaps"].numpy())
     nbytes = (host["enc"].size + n + host["gaps"].size + host["pos"].size * 4 + host["luts"].size + 2 * n)
-    for _ in range(args.warmup):
-        cpu_decode_sample(host, cores, 1)
-    times = []
-    for _ in range(args.steps):
-        seconds, checksum = cpu_decode_sample(host, cores, 1)      # the decode alone is timed
-        times.append(seconds)
-    dt = sum(times) / max(1, len(times))
-    assert checksum == int(w.view(torch.int16).numpy().astype(np.int64).sum()), "CPU decode is not bit-exact"
+    dt, checksum = cpu_decode_sample(host, cores, repeats=args.steps, warmup=args.warmup)   # the decode alone is timed
+    assert checksum == int(host["checksum"]), "CPU decode is not bit-exact"
     gbps = nbytes / dt / 1e9
     sample = f"one transformer-block unit of {cfg['name']} ({n} elements) per step, {cores} threads"
     print(json.dumps({
@@ -296,7 +352,8 @@ def run_reference_arm(args, cfg):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8/u16 integer",
         "data": "synthetic", "config": {"workload": cfg["name"], "sample": sample},
-        "cpu_baseline": {"value": round(gbps, 3), "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": round(gbps, 3), "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
+                         "statistic": f"mean of {args.steps} decodes after {args.warmup} untimed"},
         "e2e": {"value": round(gbps, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -456,20 +513,33 @@ def main():
         "two_pass": {"path": "df11_decode", "ms_per_step": round(ms_two_pass, 4),
                      "GBps": round(total_bytes / ms_two_pass / 1e6, 1)},
     }
+    tp_result = None
+    if world > 1 and not args.skip_extras and not cfg.get("tp"):
+        tp_result = tp_block(args, rank, world, device)
     if rank == 0:
         peak, how = measured_hbm_peak()
         per_gpu = step_bytes / ms / 1e6
         result["roofline"] = {
             "bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
             "frac": round(per_gpu / peak, 4),
-            # DRAM bytes per launch: 3.229 B/element measured by ncu (dram read + write) on a
-            # 218 M-element unit, scaled to this workload's average unit (traffic grows with elements)
-            "traffic": int(3.229 * step_elems / len(units)), "algorithmic_bytes_per_launch": step_bytes // len(units),
+            # what the kernel really asks of memory per launch: stream + sign/mantissa + seek points in,
+            # BF16 out (it never reads gaps / output_positions, which `algorithmic` counts)
+            "actual_bytes_per_launch": int(sum(u["n_bytes"] + 3 * u["n_elements"] + u["aux"].numel() - (8 << 12)
+                                               for u in units) / len(units)),
+            "actual_GBps": round(sum(u["n_bytes"] + 3 * u["n_elements"] + u["aux"].numel() - (8 << 12)
+                                     for u in units) / ms / 1e6, 1),
+            # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of one launch on one
+            # transformer-block unit of this workload under ncu, per element, scaled to the average unit
+            "traffic": (int(DRAM_BYTES_PER_ELEMENT[ops.seek_interval()] * step_elems / len(units))
+                        if DRAM_BYTES_PER_ELEMENT.get(ops.seek_interval()) else None),
+            "algorithmic_bytes_per_launch": step_bytes // len(units),
             "peak_source": how,
-            "kernel": "df11_fast_kernel<12,16>", "frac_of_nominal_8000": round(per_gpu / 8000.0, 4),
+            "kernel": f"df11_fast_kernel<12,{ops.seek_interval()}>", "frac_of_nominal_8000": round(per_gpu / 8000.0, 4),
             "avg_launch_ms": round(ms / len(units), 4),
         }
         result["clocks"] = clocks
+        if tp_result is not None:
+            result["tp"] = tp_result
         if e2e is not None:
             result["e2e"] = e2e
         if not args.skip_extras:
@@ -478,17 +548,25 @@ def main():
             from oracle import df11_oracle as oracle
             oracle.build()
             cores = oracle.max_threads()
-            best, checksum = cpu_decode_sample(block["host"], cores, repeats=3)
+            mean, checksum = cpu_decode_sample(block["host"], cores, repeats=5, warmup=1)
             one, _ = cpu_decode_sample(block["host"], 1, repeats=1)
             ok = checksum == block["checksum"]
             result["cpu_baseline"] = {
-                "value": round(algorithmic_bytes(block) / best / 1e9, 3), "unit": "GB/s", "cores": cores,
+                "value": round(algorithmic_bytes(block) / mean / 1e9, 3), "unit": "GB/s", "cores": cores,
                 "kind": "port", "single_core_GBps": round(algorithmic_bytes(block) / one / 1e9, 3),
                 "bit_exact": ok,
-                "sample": f"one transformer-block unit ({block['n_elements']} elements), best of 3, "
-                          f"{cores} threads; CPU restatement of the reference decode rule "
+                "sample": f"one transformer-block unit ({block['n_elements']} elements), mean of 5 decodes after "
+                          f"1 untimed, {cores} threads; CPU restatement of the reference decode rule "
                           "(the reference has no CPU decoder)",
+                "compress": cpu_compress_sample(),
             }
+            if world == 1 and cfg.get("vocab"):
+                del units, u, block
+                scratch = None
+                try:
+                    result["generation"] = generation_block(cfg, device)
+                except Exception as exc:                    # report, do not hide
+                    result["generation"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
         print(json.dumps(result))
     if world > 1:
         import torch.distributed as dist
@@ -732,6 +810,243 @@ def run_generation(args, cfg):
         "peak_mem_GB": {"bf16": round(mem_bf16, 2), "df11": round(mem_df11, 2)},
         "compress_s": round(t_compress, 1), "data": "synthetic",
     }))
+
+
+def _random_init_model(cfg, dev, layers=None):
+    from transformers import Qwen3Config, Qwen3ForCausalLM, LlamaConfig, LlamaForCausalLM
+    common = dict(hidden_size=cfg["hidden"], intermediate_size=cfg["inter"],
+                  num_hidden_layers=layers or cfg["layers"],
+                  num_attention_heads=cfg["hidden"] // 128, num_key_value_heads=cfg["kv"] // 128,
+                  vocab_size=max(cfg["vocab"], 1024), tie_word_embeddings=False, max_position_embeddings=4096)
+    torch.manual_seed(1)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with dev:
+            if "qwen" in cfg["name"]:
+                model = Qwen3ForCausalLM(Qwen3Config(head_dim=128, **common))
+            else:
+                model = LlamaForCausalLM(LlamaConfig(**common))
+    finally:
+        torch.set_default_dtype(old)
+    model.eval()
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 2:
+                p.normal_(0.0, 1.0 if "embed_tokens" in name else 0.02)
+    return model, common["vocab_size"]
+
+
+def _graph_generate(model, ids, n_new):
+    """Greedy generation through GraphedGreedyDecoder (static KV cache, one CUDA graph per
+    single-token step): the reference's protocol (warm-up, synchronize, wall clock, tokens /
+    latency, inference.py:45-95) with the host taken out of the per-token loop."""
+    import dfloat11_b200 as df11
+    n_prompt = ids.shape[1]
+    torch.cuda.reset_peak_memory_stats()
+    decoder = df11.GraphedGreedyDecoder(model, max_cache_len=n_prompt + n_new + 16)
+    decoder.generate(ids, 8)                            # warm-up steps and the capture
+    torch.cuda.synchronize()
+    t0 = time.time()
+    out = decoder.generate(ids, n_new)
+    torch.cuda.synchronize()
+    dt = time.time() - t0
+    return dict(tok_s=n_new / dt, ids=out[0, n_prompt:].cpu(), peak=torch.cuda.max_memory_allocated() / 1e9)
+
+
+def generation_block(cfg, dev, new_tokens=128, prompt_tokens=64):
+    """Batch-1 greedy generation on the workload's architecture (random init): uncompressed BF16,
+    then the same model object compressed in place (the default, bit-identical path), then the
+    opt-in fused products.  tok/s, ratio to BF16, whether the ids are BF16's, peak device memory."""
+    import dfloat11_b200 as df11
+    from dfloat11_b200.dfloat11 import TensorManager, _OffloadStager
+    TensorManager.release()                 # nothing of the decode legs above may count in the peaks below
+    _OffloadStager._by_device.clear()
+    torch.cuda.empty_cache()
+    model, vocab = _random_init_model(cfg, dev)
+    ids = torch.randint(0, vocab, (1, prompt_tokens), device=dev, generator=torch.Generator(device=dev).manual_seed(2))
+    out = {"workload": cfg["name"], "prompt_tokens": prompt_tokens, "new_tokens": new_tokens,
+           "harness": "greedy, static KV cache, one CUDA graph per single-token step (GraphedGreedyDecoder); "
+                      "wall clock of prefill + steps"}
+    with torch.no_grad():
+        bf16 = _graph_generate(model, ids, new_tokens)
+        out["bf16"] = {"tok_s": round(bf16["tok_s"], 2), "peak_mem_GB": round(bf16["peak"], 2)}
+        t0 = time.time()
+        df11.compress_in_place(model, GEN_PATTERNS)
+        torch.cuda.empty_cache()
+        out["compress_s"] = round(time.time() - t0, 1)
+        legs = [("df11", {}), ("df11_fused_gemv", {"DF11_FUSED_GEMV": "1"})]
+        for name, env in legs:
+            os.environ.update(env)
+            try:
+                r = _graph_generate(model, ids, new_tokens)
+                same = r["ids"] == bf16["ids"]
+                out[name] = {"tok_s": round(r["tok_s"], 2), "slowdown_vs_bf16": round(bf16["tok_s"] / r["tok_s"], 3),
+                             "ids_identical": bool(same.all()), "ids_equal": int(same.sum()),
+                             "peak_mem_GB": round(r["peak"], 2),
+                             "peak_mem_vs_bf16": round(r["peak"] / bf16["peak"], 3)}
+            except Exception as exc:                        # report, do not hide
+                out[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            finally:
+                for k in env:
+                    os.environ.pop(k, None)
+        held = {"compressed": 0, "seek_points_and_tables": 0, "gaps_positions_luts": 0}
+        for m in model.modules():
+            if hasattr(m, "sign_mantissa") and isinstance(getattr(m, "sign_mantissa"), torch.Tensor):
+                held["compressed"] += m.encoded_exponent.numel() + m.sign_mantissa.numel()
+                held["gaps_positions_luts"] += sum(getattr(m, k).numel() for k in ("gaps", "output_positions", "luts")
+                                                   if getattr(m, k).is_cuda)
+                aux = m.__dict__.get("df11_aux")
+                held["seek_points_and_tables"] += aux.numel() if aux is not None else 0
+        held["scratch"] = sum(t.numel() * 2 for t in TensorManager._tensors.values())
+        held["everything_else"] = torch.cuda.memory_allocated() - sum(held.values())
+        out["df11_memory_GB"] = {k: round(v / 1e9, 3) for k, v in held.items()}
+        out["df11_stats"] = {k: v for k, v in df11.stats().items() if k in ("decodes", "prepares", "sparse_lookups",
+                                                                            "fused_products", "l2_slab_products")}
+    del model
+    TensorManager.release()
+    torch.cuda.empty_cache()
+    return out
+
+
+TOY_TP = dict(hidden_size=1024, intermediate_size=3072, num_hidden_layers=3, num_attention_heads=8,
+              num_key_value_heads=8, vocab_size=8192, max_position_embeddings=256, tie_word_embeddings=False)
+
+
+def tp_block(args, rank, world, device):
+    """The partitioned mode on the job's own ranks (N > 1): (1) a small Llama, sharded then
+    compressed by rank 0 into one directory per rank, loaded by every rank through
+    DFloat11Model.from_pretrained(tp_size=N): logits of the DF11 shards against BF16 shards of the
+    same model, bit for bit; (2) per-rank decode of Llama-3.1-405B block shards (one shard per
+    rank compressed once and cloned for the layers) with the two activation all-reduces per
+    layer, per-GPU GB/s, and the cost of one such all-reduce; (3) whole units placed on two
+    devices by device_map="auto" (rank 0 only, devices 0 and 1) against the one-GPU BF16 model."""
+    import torch.distributed as dist
+    import dfloat11_b200 as df11
+    from dfloat11_b200 import ops, tp
+    from dfloat11_b200.dfloat11 import TensorManager
+    from transformers import LlamaConfig, LlamaForCausalLM
+    out = {}
+
+    def toy(seed):
+        torch.manual_seed(seed)
+        m = LlamaForCausalLM(LlamaConfig(**TOY_TP)).to(torch.bfloat16).eval()
+        with torch.no_grad():
+            for name, p in m.named_parameters():
+                if p.dim() == 2:
+                    p.copy_((torch.randn(p.shape) * (1.0 if "embed" in name else 0.02)).to(torch.bfloat16))
+        return m
+
+    # (1) parity of the partitioned mode
+    shared = [None]
+    if rank == 0:
+        shared[0] = tempfile.mkdtemp(prefix="df11_tp_")
+        tp.compress_model_tp(toy(0), GEN_PATTERNS, shared[0], tp_size=world)
+    dist.broadcast_object_list(shared, src=0)
+    bf16 = toy(0).to(device)
+    tp.apply_tensor_parallel(bf16, GEN_PATTERNS, world, rank)
+    model = df11.DFloat11Model.from_pretrained(shared[0], device=str(device), tp_size=world, tp_rank=rank)
+    ids = torch.randint(0, TOY_TP["vocab_size"], (2, 40), generator=torch.Generator().manual_seed(4)).to(device)
+    with torch.no_grad():
+        same = bool(torch.equal(model(input_ids=ids).logits, bf16(input_ids=ids).logits))
+        tok = bool(torch.equal(model.generate(ids[:1, :8], max_new_tokens=16, do_sample=False),
+                               bf16.generate(ids[:1, :8], max_new_tokens=16, do_sample=False)))
+    flag = torch.tensor([int(same), int(tok)], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    out["parity"] = {"model": "3-layer Llama, hidden 1024, vocabulary 8192, sharded before compression",
+                     "logits_identical_to_bf16_shards": bool(flag[0].item()),
+                     "generated_ids_identical": bool(flag[1].item()),
+                     "vocabulary_parallel": model.lm_head.out_features == TOY_TP["vocab_size"] // world}
+    del model, bf16
+    TensorManager.release()
+    torch.cuda.empty_cache()
+    dist.barrier(device_ids=[device.index])
+    if rank == 0:
+        import shutil
+        shutil.rmtree(shared[0], ignore_errors=True)
+
+    # (2) 405B block shards: decode + all-reduces
+    cfg = LLAMA_405B_TP
+    n_shard = sum(a * b for a, b in block_shapes(cfg)) // world
+    layers = 16
+    first = make_unit(n_shard, 0.02, seed=7000 + rank, device=device)
+    units = [first] + [dict(first, enc=first["enc"].clone(), sm=first["sm"].clone()) for _ in range(layers - 1)]
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    for u in units:
+        u["aux"] = ops.prepare(u["luts"], u["enc"], u["pos"], u["gaps"], u["n_elements"], status=status)
+    scratch = torch.empty(n_shard, dtype=torch.bfloat16, device=device)
+    act = torch.zeros(args.batch, cfg["hidden"], dtype=torch.bfloat16, device=device)
+
+    def step(reduce):
+        for u in units:
+            ops.decode_prepared(u["luts"], u["enc"], u["sm"], u["pos"], u["gaps"], u["aux"], out=scratch, status=status)
+            if reduce:
+                dist.all_reduce(act)
+                dist.all_reduce(act)
+
+    def timed(fn, steps=10, warmup=3):
+        for _ in range(warmup):
+            fn()
+        barrier(world, device)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier(world, device)
+        return all_max(a.elapsed_time(b) / steps, world, device)
+
+    ms_with = timed(lambda: step(True))
+    ms_without = timed(lambda: step(False))
+    ms_reduce = timed(lambda: [dist.all_reduce(act) for _ in range(2 * layers)])
+    ok = int(scratch.view(torch.int16).to(torch.int64).sum().item()) == first["checksum"] and status.item() == 0
+    total = all_sum(sum(algorithmic_bytes(u) for u in units), world, device)
+    peak, _ = measured_hbm_peak()
+    out["llama_405b_shards"] = {
+        "parallelism": f"tp{world}", "layers": layers, "elements_per_rank_and_layer": n_shard,
+        "all_reduces_per_step": 2 * layers, "all_reduce_shape": [args.batch, cfg["hidden"]],
+        "ms_per_step": round(ms_with, 3), "aggregate_GBps": round(total / ms_with / 1e6, 1),
+        "per_gpu_GBps": round(total / ms_with / 1e6 / world, 1),
+        "per_gpu_frac_of_measured_peak": round(total / ms_with / 1e6 / world / peak, 4),
+        "decode_only_ms_per_step": round(ms_without, 3),
+        "us_per_all_reduce_back_to_back": round(ms_reduce * 1e3 / (2 * layers), 2),
+        "us_per_all_reduce_in_step": round((ms_with - ms_without) * 1e3 / (2 * layers), 2),
+        "bit_exact": bool(ok),
+        "note": "one block-shard per rank compressed once and cloned per layer; NCCL all-reduce"}
+    del units, first, scratch
+    torch.cuda.empty_cache()
+
+    # (3) layer placement over two devices, one process (what the reference does with accelerate).
+    # Rank 0 borrows rank 1's GPU for it, so the other ranks wait on the host (the job's key-value
+    # store), not inside a collective: no kernel of theirs sits on a GPU that rank 0 is using.
+    barrier(world, device)
+    store = dist.distributed_c10d._get_default_store()
+    if rank != 0:
+        store.wait(["df11_bench_placement_done"])
+    if rank == 0 and torch.cuda.device_count() >= 2:
+        try:
+            with tempfile.TemporaryDirectory() as tmp:
+                ref = toy(3)
+                import copy
+                df11.compress_model(copy.deepcopy(ref), GEN_PATTERNS, tmp, save_single_file=False, check_correctness=False)
+                placed = df11.DFloat11Model.from_pretrained(tmp, device=None, device_map="auto")
+                ref = ref.to(device)
+                with torch.no_grad():
+                    a = placed(input_ids=ids.to(device)).logits
+                    b = ref(input_ids=ids.to(device)).logits
+                devices = sorted({str(t.device) for t in placed.state_dict().values() if t.is_cuda})
+                out["device_map_auto"] = {"devices_used": devices, "logits_identical_to_one_gpu_bf16": bool(torch.equal(a.to(b.device), b))}
+                del placed, ref
+        except Exception as exc:                            # report, do not hide
+            out["device_map_auto"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        TensorManager.release()
+        torch.cuda.empty_cache()
+        for d in range(torch.cuda.device_count()):
+            torch.cuda.synchronize(d)
+    if rank == 0:
+        store.set("df11_bench_placement_done", "1")
+    barrier(world, device)
+    return out
 
 
 class _Unit(torch.nn.Module):

@@ -104,8 +104,8 @@ struct Params {
     int stage_bytes;  // shared staging area (and sign/mantissa tile), multiple of 16
     int codes_aligned;  // bit 0: codes 16-byte aligned, bit 1: gaps 16-byte aligned (bulk copies allowed),
                         // bit 2: codes 4-byte aligned (word loads allowed)
-    int sm_aligned;     // sign_mantissa 16-byte aligned: bulk copies / 16-byte loads allowed
-    int out_aligned;    // out 16-byte aligned: vector stores allowed
+    int sm_aligned;     // bit 0: sign_mantissa 16-byte aligned (bulk copies / 16-byte loads allowed), bit 1: 32-byte
+    int out_aligned;    // bit 0: out 16-byte aligned (vector stores allowed), bit 1: 32-byte (256-bit stores)
     // self-test of the bounded waits (df11_selftest_wait_timeout): the producer announces the
     // bytes of format block `drop_block`'s input copy but never issues it, and waits are cut to
     // `wait_ns`.  0 / -1 in every ordinary launch.
@@ -136,6 +136,21 @@ template <int OFF>
 __device__ __forceinline__ void sts8(uint32_t a, uint32_t v)
 {
     asm volatile("st.shared.u8 [%0+%2], %1;" ::"r"(a), "r"(v), "n"(OFF) : "memory");
+}
+
+// ---- 256-bit global accesses (one instruction for 32 bytes per lane; address 32-byte aligned):
+// half the load/store instructions and memory-pipe wavefronts of two 16-byte accesses.
+__device__ __forceinline__ void stg256(void *dst, const uint4 &a, const uint4 &b)
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(a.x), "r"(a.y), "r"(a.z),
+                 "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+__device__ __forceinline__ void ldg256(const void *src, uint4 &a, uint4 &b)
+{
+    asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+                 : "l"(src));
 }
 
 // ---- programmatic dependent launch: a kernel launched with the stream-serialization attribute
@@ -474,8 +489,12 @@ __device__ __forceinline__ void lean_tasks(const Params &p, const FastTables &ta
         in.bit = lo & 31u;
         in.words = words_at(in.wi);
         const uint4 *sm16 = reinterpret_cast<const uint4 *>(p.sm) + (chunk * 32u + lane) * (EPT / 16);
+        if (EPT == 32 && (p.sm_aligned & 2)) {
+            ldg256(sm16, in.sm[0], in.sm[EPT / 16 - 1]);
+        } else {
 #pragma unroll
-        for (int part = 0; part < EPT / 16; ++part) in.sm[part] = __ldg(sm16 + part);
+            for (int part = 0; part < EPT / 16; ++part) in.sm[part] = __ldg(sm16 + part);
+        }
     };
     ExpShift X = {0, 0, 0, 0, 0};
     auto run_task = [&](uint32_t t, const Inputs &cur, Inputs &nxt) {
@@ -567,7 +586,8 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
     // words that can be loaded whole; 0 sends every word of an unaligned stream the slow way
     const uint32_t n_words = (p.codes_aligned & 4) ? (uint32_t)(p.n_bytes >> 2) : 0u;
     const uint32_t n_whole = n_words > 3u ? n_words - 3u : 0u;  // word indices with three whole words after them
-    const bool vec = p.sm_aligned && p.out_aligned;  // 16-byte loads and stores allowed
+    const bool vec = (p.sm_aligned & 1) && (p.out_aligned & 1);  // 16-byte loads and stores allowed
+    const bool wide = (p.out_aligned & 2) != 0;                  // 32-byte stores allowed
     int bad = 0;
 
     // Four raw stream words starting at word `wi` (bytes past the end read as 0), and the 96-bit
@@ -657,8 +677,12 @@ __global__ void __launch_bounds__(kFastThreads, DF11_FAST_MIN_CTAS) df11_fast_ke
                 df11_merge4(e3, m.w, &r1.z, &r1.w);
                 uint4 *dst = reinterpret_cast<uint4 *>(p.out) +
                              ((task0 + j * warps) * 32u + lane) * (EPT / 8) + 2u * part;
-                dst[0] = r0;
-                dst[1] = r1;
+                if (wide) {
+                    stg256(dst, r0, r1);
+                } else {
+                    dst[0] = r0;
+                    dst[1] = r1;
+                }
             });
         task += mine * warps;  // this warp's first task after them
     }
@@ -1448,8 +1472,8 @@ extern "C" int df11_decode(const void *luts, const void *codes, const void *sign
     p.sm = (const uint8_t *)sign_mantissa;
     p.out = (uint16_t *)out_bf16;
     p.stage_bytes = stage_bytes_for(max_block_elems);
-    p.sm_aligned = ((uintptr_t)sign_mantissa & 15) == 0;
-    p.out_aligned = ((uintptr_t)out_bf16 & 15) == 0;
+    p.sm_aligned = (((uintptr_t)sign_mantissa & 15) == 0 ? 1 : 0) | (((uintptr_t)sign_mantissa & 31) == 0 ? 2 : 0);
+    p.out_aligned = (((uintptr_t)out_bf16 & 15) == 0 ? 1 : 0) | (((uintptr_t)out_bf16 & 31) == 0 ? 2 : 0);
     return launch_decode(p, device, (cudaStream_t)stream);
 }
 
@@ -1470,8 +1494,8 @@ extern "C" int df11_selftest_wait_timeout(const void *luts, const void *codes, c
     p.sm = (const uint8_t *)sign_mantissa;
     p.out = (uint16_t *)out_bf16;
     p.stage_bytes = stage_bytes_for(max_block_elems);
-    p.sm_aligned = ((uintptr_t)sign_mantissa & 15) == 0;
-    p.out_aligned = ((uintptr_t)out_bf16 & 15) == 0;
+    p.sm_aligned = (((uintptr_t)sign_mantissa & 15) == 0 ? 1 : 0) | (((uintptr_t)sign_mantissa & 31) == 0 ? 2 : 0);
+    p.out_aligned = (((uintptr_t)out_bf16 & 15) == 0 ? 1 : 0) | (((uintptr_t)out_bf16 & 31) == 0 ? 2 : 0);
     if (!(p.codes_aligned & 1) && !(p.codes_aligned & 2))
         return df11_fail(DF11_ERR_BADARG, "the self-test needs 16-byte aligned tensors (no bulk copy otherwise)");
     p.drop_block = drop_block;
@@ -1571,8 +1595,8 @@ int decode_prepared(const void *luts, const void *codes, const void *sign_mantis
     p.sync_lo = (uint16_t *)((uint8_t *)aux + a.lo_off);
     p.n_chunks = a.n_chunks;
     p.ept = ept;
-    p.sm_aligned = ((uintptr_t)sign_mantissa & 15) == 0;
-    p.out_aligned = ((uintptr_t)out_bf16 & 15) == 0;
+    p.sm_aligned = (((uintptr_t)sign_mantissa & 15) == 0 ? 1 : 0) | (((uintptr_t)sign_mantissa & 31) == 0 ? 2 : 0);
+    p.out_aligned = (((uintptr_t)out_bf16 & 15) == 0 ? 1 : 0) | (((uintptr_t)out_bf16 & 31) == 0 ? 2 : 0);
     int64_t chunks = a.n_chunks;
     if (range_elements >= 0) {
         const int64_t chunk_elems = 32 * ept;
@@ -1664,8 +1688,8 @@ extern "C" int df11_decode_rows_prepared(const void *luts, const void *codes, co
     p.chunks_per_row = (uint32_t)(row_elements / chunk_elems);
     p.n_tasks = (uint32_t)(n_rows * p.chunks_per_row);
     p.n_rows_total = (uint32_t)(n_elements / row_elements);
-    p.sm_aligned = ((uintptr_t)sign_mantissa & 15) == 0;
-    p.out_aligned = ((uintptr_t)out_bf16 & 15) == 0;
+    p.sm_aligned = (((uintptr_t)sign_mantissa & 15) == 0 ? 1 : 0) | (((uintptr_t)sign_mantissa & 31) == 0 ? 2 : 0);
+    p.out_aligned = (((uintptr_t)out_bf16 & 15) == 0 ? 1 : 0) | (((uintptr_t)out_bf16 & 31) == 0 ? 2 : 0);
     const int64_t cta_items = ((int64_t)p.n_tasks + kFastThreads / 32 - 1) / (kFastThreads / 32);
     const size_t smem = (8u << kFastTableBits) + (size_t)n_luts * 256;
     if (ept == 32)
@@ -1744,6 +1768,7 @@ extern "C" int df11_gemv_prepared(const void *luts, const void *codes, const voi
     p.n_chunks = a.n_chunks;
     p.n_luts = n_luts;
     p.ept = ept;
+    p.sm_aligned = 1 | (((uintptr_t)sign_mantissa & 31) == 0 ? 2 : 0);
     GemvArgs g;
     g.x = (const uint16_t *)x_bf16;
     g.y = (uint16_t *)y_bf16;

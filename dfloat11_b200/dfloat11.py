@@ -25,6 +25,7 @@ import json
 import logging
 import os
 import re
+import weakref
 from sys import stderr
 from typing import Dict, List, Optional, Union
 
@@ -56,6 +57,8 @@ class _Flags:
     fused = False
     nvtx = False
     check_status = False
+    slab_head = True
+    side_on_host = True
 
     @classmethod
     def read(cls) -> None:
@@ -66,6 +69,8 @@ class _Flags:
         cls.fused = env("DF11_FUSED_GEMV", "0") == "1"
         cls.nvtx = env("DF11_NVTX", "0") == "1"
         cls.check_status = env("DF11_CHECK_STATUS", "0") == "1"
+        cls.slab_head = env("DF11_SLAB_HEAD", "1") != "0"
+        cls.side_on_host = env("DF11_SIDE_TENSORS_ON_HOST", "1") != "0"
 
     @classmethod
     def current(cls):
@@ -89,6 +94,11 @@ class TensorManager:
     """
 
     _tensors: Dict[tuple, torch.Tensor] = {}
+    _users: Dict[tuple, "weakref.WeakSet"] = {}
+    # Elements the scratch of slots 0 / 1 is given at least: the largest unit that is decoded as a
+    # whole among the models loaded so far, so that the scratch is allocated once instead of
+    # growing unit by unit (a grown-out-of tensor stays alive as long as a layer holds a view of it).
+    min_elements = 0
 
     @staticmethod
     def allocate_bfloat16(device, n_elements: int, slot: int = 0) -> torch.Tensor:
@@ -104,18 +114,33 @@ class TensorManager:
                 return existing[:n_elements]
             del TensorManager._tensors[key]
             del existing
+            # the layers that still hold views of the old tensor let go of them (their hooks make new
+            # ones before their next forward), or the old tensor would stay allocated beside the new
+            for user in list(TensorManager._users.pop(key, ())):
+                _drop_views(user)
             if device.type == "cuda":
                 torch.cuda.empty_cache()
-        new_tensor = torch.empty(n_elements, dtype=torch.bfloat16, device=device)
-        log.info("Allocated %d bf16 on device %s (slot %d)", n_elements, device, slot)
+        size = max(n_elements, TensorManager.min_elements) if slot in (0, 1) else n_elements
+        new_tensor = torch.empty(size, dtype=torch.bfloat16, device=device)
+        log.info("Allocated %d bf16 on device %s (slot %d)", size, device, slot)
         TensorManager._tensors[key] = new_tensor
-        return new_tensor
+        return new_tensor[:n_elements]
+
+    @staticmethod
+    def note_user(module: nn.Module, tensor: torch.Tensor) -> None:
+        """Remembers that ``module``'s layers hold views of the scratch ``tensor`` is a slice of."""
+        for key, scratch in TensorManager._tensors.items():
+            if scratch.data_ptr() == tensor.data_ptr():
+                TensorManager._users.setdefault(key, weakref.WeakSet()).add(module)
+                return
 
     @staticmethod
     def release(device=None) -> None:
         """Drop the scratch of one device (or of all)."""
         if device is None:
             TensorManager._tensors.clear()
+            TensorManager._users.clear()
+            TensorManager.min_elements = 0
         else:
             device = torch.device(device)
             for key in [k for k in TensorManager._tensors if k[0] == device]:
@@ -123,7 +148,7 @@ class TensorManager:
 
 
 _status_words: Dict[torch.device, torch.Tensor] = {}
-_counters = dict(decodes=0, decoded_elements=0, prepares=0, sparse_lookups=0, fused_products=0)
+_counters = dict(decodes=0, decoded_elements=0, prepares=0, sparse_lookups=0, fused_products=0, slab_products=0)
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -344,9 +369,9 @@ class _DecodeAhead:
         queued.record(main)                            # the slot's previous reader has been queued before this
         self.stream.wait_event(queued)
         with torch.cuda.stream(self.stream):
-            ops.decode_prepared(nxt.luts, nxt.encoded_exponent, nxt.sign_mantissa, nxt.output_positions,
-                                nxt.gaps, nxt.df11_aux, out=tensor, ctas_per_sm=ctas,
-                                status=_status_word(self.device))
+            pos, gaps = _side_tensors(nxt, self.device)
+            ops.decode_prepared(nxt.luts, nxt.encoded_exponent, nxt.sign_mantissa, pos, gaps, nxt.df11_aux,
+                                out=tensor, ctas_per_sm=ctas, status=_status_word(self.device))
             done = torch.cuda.Event()
             done.record(self.stream)
         self.pending = (nxt, slot, done, tensor)
@@ -367,12 +392,46 @@ def _end_of_forward_hook(_module, _inputs, _output):
 
 
 def _mark_root(model: nn.Module) -> None:
-    """Lets the hooks see where a forward pass of the whole model starts and ends (the
-    environment switches are read once per pass; decode-ahead joins what is in flight)."""
+    """Called once all units of a model are armed.  Lets the hooks see where a forward pass of the
+    whole model starts and ends (the environment switches are read once per pass; decode-ahead
+    joins what is in flight), sizes the shared scratch for the largest unit that is decoded as a
+    whole, gives large single-Linear units their slab-wise forward and links the offloaded units
+    in forward order for the prefetcher."""
+    units = [m for m in model.modules() if isinstance(getattr(m, "split_positions", None), list)
+             and (hasattr(m, "luts") or hasattr(m, "offloaded_tensors"))]
+    def elements(m):
+        t = m.offloaded_tensors.get("sign_mantissa") if hasattr(m, "offloaded_tensors") else None
+        return (t if t is not None else m.sign_mantissa).numel()
+    whole = [elements(m) for m in units
+             if not isinstance(m, (nn.Embedding, nn.Linear)) or elements(m) < SLAB_MIN_ELEMENTS]
+    if whole:
+        TensorManager.min_elements = max(TensorManager.min_elements, max(whole))
+    for m in units:
+        if _slab_rows(m):
+            _install_slabbed(m)
+    # offloaded units in definition (= forward) order; a lookup table that can be read row by row out
+    # of pinned memory is never staged, so it is not part of the ring
+    ring = [m for m in units if hasattr(m, "offloaded_tensors")
+            and not (isinstance(m, nn.Embedding) and m.max_norm is None and m.embedding_dim % 1024 == 0)]
+    for a, b in zip(ring, ring[1:] + ring[:1]):
+        a.__dict__["df11_next_offloaded"] = b          # a plain reference, not a registered submodule
     if not model.__dict__.get("df11_root_hooked"):
         model.register_forward_pre_hook(_start_of_forward_hook)
         model.register_forward_hook(_end_of_forward_hook, always_call=True)
         model.__dict__["df11_root_hooked"] = True
+
+
+def _drop_views(module: nn.Module) -> None:
+    """Takes back the weight views handed to a unit's layers (the scratch they point into is
+    going away); the unit's hook hands out new ones before its next forward."""
+    d = module.__dict__
+    d["df11_injected"] = None
+    d["df11_fast"] = None
+    layers = [module] if isinstance(module, (nn.Linear, nn.Embedding)) else getattr(module, "weight_injection_modules", [])
+    for layer in layers:
+        if "weight" not in layer._parameters:
+            layer.__dict__.pop("weight", None)
+            layer.weight = None
 
 
 def _inject_weights(module: nn.Module, reconstructed: torch.Tensor) -> None:
@@ -394,6 +453,7 @@ def _inject_weights(module: nn.Module, reconstructed: torch.Tensor) -> None:
         for sub_module, weight in zip(module.weight_injection_modules, weights):
             sub_module.weight = weight.view(sub_module.out_features, sub_module.in_features)
     module.__dict__["df11_injected"] = key
+    TensorManager.note_user(module, reconstructed)
 
 
 def _sparse_embedding(module: nn.Module, inputs, n_elements: int) -> bool:
@@ -517,13 +577,100 @@ def _install_fused(module: nn.Module) -> bool:
     return True
 
 
+def _side_tensors(module: nn.Module, device: torch.device):
+    """(output_positions, gaps) as the launches want them.  Only ``df11_prepare`` and the
+    self-contained decoder read these two; once a unit's auxiliary buffer exists they are kept on
+    the host (0.026 bytes per weight given back to the device) and the fast decoder's entry
+    points, which never read them, get another device tensor of the unit in their place."""
+    pos, gaps = module.output_positions, module.gaps
+    if pos.device == device and gaps.device == device:
+        return pos, gaps
+    return module.luts, module.luts
+
+
+def _side_tensors_on_device(module: nn.Module, device: torch.device):
+    """The real ``output_positions`` / ``gaps`` on ``device`` (moved back if they were parked on the host)."""
+    if module.output_positions.device != device:
+        module.output_positions = module.output_positions.to(device)
+    if module.gaps.device != device:
+        module.gaps = module.gaps.to(device)
+    return module.output_positions, module.gaps
+
+
+def _park_side_tensors(module: nn.Module) -> None:
+    if _Flags.current().side_on_host and module.gaps.is_cuda and not torch.cuda.is_current_stream_capturing():
+        module.gaps = module.gaps.cpu()
+        module.output_positions = module.output_positions.cpu()
+
+
+# A unit that is one large Linear layer (an output head over a vocabulary of 100 000 and more) is
+# multiplied slab by slab when it is called with a few activation vectors: a slab of its rows is
+# decompressed into the scratch the transformer blocks use, multiplied, and overwritten by the
+# next slab.  Each output row is the same dot product whether the library multiplies the whole
+# matrix or a block of its rows (checked bit for bit on the GPU for these shapes by
+# tests/test_model_api.py), and the scratch never has to hold the whole matrix: 0.4 GB instead of
+# 1.24 GB for a Qwen3-8B head.
+SLAB_MIN_ELEMENTS = 1 << 27
+SLAB_MAX_ROWS_IN = 4            # activation vectors up to which the slab path is taken
+
+
+def _slab_rows(module: nn.Module) -> int:
+    """Rows per slab of a slab-capable unit, 0 if the unit is not one."""
+    if not isinstance(module, nn.Linear) or module.in_features % 1024:
+        return 0
+    if module.out_features * module.in_features < SLAB_MIN_ELEMENTS:
+        return 0
+    budget = TensorManager.min_elements or (1 << 26)
+    rows = min(module.out_features, max(8, budget // module.in_features // 8 * 8))
+    n_slabs = -(-module.out_features // rows)
+    return min(module.out_features, (-(-module.out_features // n_slabs) + 7) // 8 * 8)
+
+
+def _install_slabbed(module: nn.Module) -> None:
+    """Gives a slab-capable Linear unit a forward that multiplies slab by slab when the hook left
+    the unit undecoded (``df11_pending``), and calls the ordinary product otherwise."""
+    if module.__dict__.get("df11_slabbed") is not None:
+        return
+    module.__dict__["df11_slabbed"] = True
+    import torch.nn.functional as F
+
+    def forward(x):
+        pending = module.__dict__.pop("df11_pending", None)
+        if pending is None:
+            return F.linear(x, module.weight, module.bias)
+        encoded_exponent, sign_mantissa, aux, stager, device = pending
+        n_in, n_out = module.in_features, module.out_features
+        rows = _slab_rows(module) or n_out
+        m = x.numel() // n_in
+        x2 = x.reshape(m, n_in)
+        y = torch.empty(m, n_out, dtype=x.dtype, device=x.device)
+        scratch = TensorManager.allocate_bfloat16(device, min(rows, n_out) * n_in)
+        status = _status_word(device)
+        for r0 in range(0, n_out, rows):
+            r1 = min(n_out, r0 + rows)
+            ops.decode_range_prepared(module.luts, encoded_exponent, sign_mantissa, aux, r0 * n_in, (r1 - r0) * n_in,
+                                      out=scratch, status=status)
+            w = scratch[:(r1 - r0) * n_in].view(r1 - r0, n_in)
+            if m == 1 and module.bias is None:
+                torch.mm(x2, w.t(), out=y[:, r0:r1])
+            else:
+                y[:, r0:r1] = F.linear(x2, w, None if module.bias is None else module.bias[r0:r1])
+        _counters["slab_products"] += 1
+        if stager is not None:
+            stager.done(module)
+        return y.view(*x.shape[:-1], n_out)
+
+    module.forward = forward
+
+
 def _decode_whole_unit(module: nn.Module, device: torch.device) -> None:
     """Decompress a resident, prepared unit into the scratch tensor and hand out the views."""
     n_elements = module.sign_mantissa.numel()
     reconstructed = TensorManager.allocate_bfloat16(device, n_elements)
-    ops.decode_prepared(module.luts, module.encoded_exponent, module.sign_mantissa, module.output_positions,
-                        module.gaps, module.df11_aux, out=reconstructed,
-                        max_block_elems=getattr(module, "max_block_elems", 0), status=_status_word(device))
+    pos, gaps = _side_tensors(module, device)
+    ops.decode_prepared(module.luts, module.encoded_exponent, module.sign_mantissa, pos, gaps, module.df11_aux,
+                        out=reconstructed, max_block_elems=getattr(module, "max_block_elems", 0),
+                        status=_status_word(device))
     _counters["decodes"] += 1
     _counters["decoded_elements"] += n_elements
     _inject_weights(module, reconstructed)
@@ -574,10 +721,32 @@ def get_hook(threads_per_block, bytes_per_thread):
             raise RuntimeError("DF11 weights can only be decompressed on a CUDA device; move the model to "
                                f"one (this unit's tables are on {device})")
         status = _status_word(device)
+        flags = _Flags.current()
+        offloaded = hasattr(module, "offloaded_tensors")
+        d["df11_undecoded"] = False
+        d.pop("df11_pending", None)
+
+        if flags.prepared and offloaded and _sparse_embedding(module, inputs, module.offloaded_tensors[
+                "sign_mantissa"].numel()) and all(t.is_pinned() for t in module.offloaded_tensors.values()):
+            # An offloaded lookup table: the kernel reads the few rows it needs straight out of the
+            # pinned host tensors (page-locked memory is addressable from the device), instead of
+            # staging the whole compressed table on the device first as dfloat11.py:122-128 does
+            # (0.83 GB per forward for a 152 k-row table of 4096 columns).
+            host = module.offloaded_tensors
+            aux = d.get("df11_aux")
+            if aux is None or aux.device != device:
+                pos, gaps = _side_tensors_on_device(module, device)
+                aux = ops.prepare(module.luts, host["encoded_exponent"], pos, gaps, host["sign_mantissa"].numel(),
+                                  status=status)
+                module.df11_aux = aux
+                _counters["prepares"] += 1
+                _park_side_tensors(module)
+            return sparse_lookup(module, inputs, host["encoded_exponent"], host["sign_mantissa"], aux, device, status,
+                                 None, None)
 
         # compressed tensors: resident buffers, or the staging slot of the offload pipeline
         stager = None
-        if hasattr(module, "offloaded_tensors"):
+        if offloaded:
             stager = _OffloadStager.get(device)
             staged = stager.fetch(module)
             encoded_exponent, sign_mantissa = staged["encoded_exponent"], staged["sign_mantissa"]
@@ -586,56 +755,44 @@ def get_hook(threads_per_block, bytes_per_thread):
 
         n_elements = sign_mantissa.numel()
         widest = getattr(module, "max_block_elems", 0)
-        module.__dict__["df11_undecoded"] = False
 
-        if _use_prepared():
-            aux = module.__dict__.get("df11_aux")
+        if flags.prepared:
+            aux = d.get("df11_aux")
             if aux is None or aux.device != device:
                 # once per unit and device: decode table + seek points (derived data, never saved)
-                aux = ops.prepare(module.luts, encoded_exponent, module.output_positions, module.gaps, n_elements,
-                                  status=status)
+                pos, gaps = _side_tensors_on_device(module, device)
+                aux = ops.prepare(module.luts, encoded_exponent, pos, gaps, n_elements, status=status)
                 module.df11_aux = aux
                 _counters["prepares"] += 1
-            if _use_fused_gemv() and stager is None:
+                _park_side_tensors(module)
+            if flags.fused and stager is None:
                 # decode lazily: the unit's Linear layers multiply straight from the compressed
                 # weights while they are called with a few activation vectors (generation), and
                 # decompress the whole unit the first time one of them is not (prefill).  A unit
                 # that is itself the Linear runs its first such call the ordinary way: torch has
                 # already picked that call's forward when this hook installs the new one.
-                fresh = module.__dict__.get("df11_fused") is None
+                fresh = d.get("df11_fused") is None
                 if _install_fused(module) and not (fresh and isinstance(module, nn.Linear)):
-                    module.__dict__["df11_undecoded"] = True
+                    d["df11_undecoded"] = True
                     return None
-            ahead = _DecodeAhead.get(device) if _use_decode_ahead() else None
+            if (flags.slab_head and d.get("df11_slabbed") and not d.get("df11_fused") and inputs
+                    and isinstance(inputs[0], torch.Tensor)
+                    and 0 < inputs[0].numel() // module.in_features <= SLAB_MAX_ROWS_IN):
+                # a large single Linear called with a few activation vectors: its forward (installed at
+                # load time) decompresses and multiplies slab by slab
+                d["df11_pending"] = (encoded_exponent, sign_mantissa, aux, stager, device)
+                d["df11_undecoded"] = True
+                return None
+            ahead = _DecodeAhead.get(device) if flags.decode_ahead else None
             if _sparse_embedding(module, inputs, n_elements):
-                # A lookup table: decompress only the rows that are asked for (the reference
-                # decodes the whole table on every forward, dfloat11.py:158-161) and look them
-                # up by their position in that small result.  During this forward
-                # ``module.weight`` is that [number of ids, embedding_dim] tensor, not the whole
-                # table; an id outside the table yields row 0 and sets the status word (see
-                # check_status), where F.embedding would raise a device-side assert.
-                ids = inputs[0]
-                if ids.device != device:
-                    ids = ids.to(device)
-                rows = ops.decode_rows_prepared(module.luts, encoded_exponent, sign_mantissa, aux,
-                                                ids.reshape(-1).to(torch.int64), module.embedding_dim,
-                                                out=TensorManager.allocate_bfloat16(
-                                                    device, ids.numel() * module.embedding_dim, slot=2),
-                                                status=status)
-                _counters["sparse_lookups"] += 1
-                module.weight = rows
-                module.__dict__["df11_injected"] = None        # the whole-table view is gone
-                if stager is not None:
-                    stager.done(module)
-                if ahead is not None:
-                    ahead.after(module, light=True)
-                return (torch.arange(ids.numel(), device=device).view(ids.shape),) + tuple(inputs[1:])
+                return sparse_lookup(module, inputs, encoded_exponent, sign_mantissa, aux, device, status, stager, ahead)
             reconstructed = ahead.claim(module, n_elements) if ahead is not None else None
+            pos, gaps = _side_tensors(module, device)
             if reconstructed is None:
                 slot = ahead.fresh_slot() if ahead is not None else 0
                 reconstructed = TensorManager.allocate_bfloat16(device, n_elements, slot=slot)
-                ops.decode_prepared(module.luts, encoded_exponent, sign_mantissa, module.output_positions,
-                                    module.gaps, aux, out=reconstructed, max_block_elems=widest, status=status)
+                ops.decode_prepared(module.luts, encoded_exponent, sign_mantissa, pos, gaps, aux, out=reconstructed,
+                                    max_block_elems=widest, status=status)
                 _counters["decodes"] += 1
                 _counters["decoded_elements"] += n_elements
             _inject_weights(module, reconstructed)
@@ -643,26 +800,50 @@ def get_hook(threads_per_block, bytes_per_thread):
                 stager.done(module)
             if ahead is not None:
                 ahead.after(module)
-            elif stager is None and not isinstance(module, nn.Embedding):
+            elif stager is None and not isinstance(module, nn.Embedding) and not d.get("df11_slabbed"):
                 # remember what the next call of this unit can reuse as it is
                 key = (device, slot)
                 d["df11_fast"] = (
                     encoded_exponent, aux, key, TensorManager._tensors.get(key),
                     (module.luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(),
-                     module.output_positions.data_ptr(), module.gaps.data_ptr(), aux.data_ptr(),
+                     pos.data_ptr(), gaps.data_ptr(), aux.data_ptr(),
                      reconstructed.data_ptr(), module.luts.shape[0], encoded_exponent.numel(), n_elements,
                      int(widest), status.data_ptr(), device.index),
                     device.index)
             return None
 
+        pos, gaps = _side_tensors_on_device(module, device)
         reconstructed = TensorManager.allocate_bfloat16(device, n_elements)
-        ops.decode(module.luts, encoded_exponent, sign_mantissa, module.output_positions, module.gaps,
+        ops.decode(module.luts, encoded_exponent, sign_mantissa, pos, gaps,
                    out=reconstructed, max_block_elems=widest, status=status)
         _counters["decodes"] += 1
         _counters["decoded_elements"] += n_elements
         _inject_weights(module, reconstructed)
         if stager is not None:
             stager.done(module)
+
+    def sparse_lookup(module, inputs, encoded_exponent, sign_mantissa, aux, device, status, stager, ahead):
+        # A lookup table: decompress only the rows that are asked for (the reference decodes the
+        # whole table on every forward, dfloat11.py:158-161) and look them up by their position in
+        # that small result.  During this forward ``module.weight`` is that [number of ids,
+        # embedding_dim] tensor, not the whole table; an id outside the table yields row 0 and sets
+        # the status word (see check_status), where F.embedding would raise a device-side assert.
+        ids = inputs[0]
+        if ids.device != device:
+            ids = ids.to(device)
+        rows = ops.decode_rows_prepared(module.luts, encoded_exponent, sign_mantissa, aux,
+                                        ids.reshape(-1).to(torch.int64), module.embedding_dim,
+                                        out=TensorManager.allocate_bfloat16(
+                                            device, ids.numel() * module.embedding_dim, slot=2),
+                                        status=status)
+        _counters["sparse_lookups"] += 1
+        module.weight = rows
+        module.__dict__["df11_injected"] = None        # the whole-table view is gone
+        if stager is not None:
+            stager.done(module)
+        if ahead is not None:
+            ahead.after(module, light=True)
+        return (torch.arange(ids.numel(), device=device).view(ids.shape),) + tuple(inputs[1:])
 
     return decode_hook
 
@@ -700,6 +881,7 @@ def load_and_replace_tensors(
     cpu_offload_blocks=None,
     pin_memory=True,
     from_single_file=False,
+    device=None,
 ):
     """Loads DF11 safetensors into ``model`` and arms on-the-fly decompression (dfloat11.py:179-308).
 
@@ -708,8 +890,14 @@ def load_and_replace_tensors(
     a Python list); with ``cpu_offload`` the two large ones stay in (pinned) host memory in
     ``module.offloaded_tensors``.  The module gets the decode hook and loses the ``weight``
     attributes the hook will supply.
+
+    Files are memory-mapped and every tensor is copied once, to where it will live
+    (``safetensors_io``): offloaded tensors into pinned memory of their own, and -- when
+    ``device`` names the CUDA device the model is about to be moved to (not in the reference's
+    signature) -- the large tensors of resident units straight to that device through pinned
+    staging, the copy of one overlapping the host-side read of the next.
     """
-    from safetensors.torch import load_file
+    from .safetensors_io import DeviceUploader, MappedFile
 
     tpb = dfloat11_config["threads_per_block"]
     bpt = dfloat11_config["bytes_per_thread"]
@@ -725,59 +913,67 @@ def load_and_replace_tensors(
     buffers = dict(model.named_buffers())
     modules = dict(model.named_modules())
     units: Dict[str, nn.Module] = {}
+    uploader = None
+    if device is not None and torch.device(device).type == "cuda" and torch.cuda.is_available():
+        uploader = DeviceUploader(torch.device(device))
 
     for file_path in files:
-        loaded = load_file(file_path)
-        for tensor_name, value in loaded.items():
-            target = params.get(tensor_name)
-            if target is None:
-                target = buffers.get(tensor_name)
-            if target is not None:
-                if target.shape != value.shape:
-                    # the reference prints and goes on with the uninitialised tensor
-                    # (dfloat11.py:230-232); a model that silently computes with garbage is worse
-                    raise ValueError(f"Shape mismatch for {tensor_name}: model {tuple(target.shape)} vs loaded "
-                                     f"{tuple(value.shape)}")
-                with torch.no_grad():
-                    target.copy_(value)
-                continue
+        with MappedFile(file_path) as mapped:
+            for tensor_name in mapped.names():
+                target = params.get(tensor_name)
+                if target is None:
+                    target = buffers.get(tensor_name)
+                if target is not None:
+                    shape = mapped.shape(tensor_name)
+                    if tuple(target.shape) != shape:
+                        # the reference prints and goes on with the uninitialised tensor
+                        # (dfloat11.py:230-232); a model that silently computes with garbage is worse
+                        raise ValueError(f"Shape mismatch for {tensor_name}: model {tuple(target.shape)} vs loaded "
+                                         f"{shape}")
+                    with torch.no_grad():
+                        target.copy_(torch.from_numpy(mapped.raw(tensor_name)).view(mapped.torch_dtype(tensor_name))
+                                     .reshape(shape))
+                    continue
 
-            module_path, _, leaf = tensor_name.rpartition(".")
-            module = modules.get(module_path)
-            if module is None:
-                print(f"Cannot find module path for {tensor_name}", file=stderr)
-                continue
-            if leaf not in _unit_tensor_names:
-                # an ordinary tensor the model has no place for (a bias of a layer that has none
-                # here): not part of a compressed unit, so nothing to arm
-                print(f"No parameter or buffer for {tensor_name}; skipped", file=stderr)
-                continue
-            units[module_path] = module
+                module_path, _, leaf = tensor_name.rpartition(".")
+                module = modules.get(module_path)
+                if module is None:
+                    print(f"Cannot find module path for {tensor_name}", file=stderr)
+                    continue
+                if leaf not in _unit_tensor_names:
+                    # an ordinary tensor the model has no place for (a bias of a layer that has none
+                    # here): not part of a compressed unit, so nothing to arm
+                    print(f"No parameter or buffer for {tensor_name}; skipped", file=stderr)
+                    continue
+                units[module_path] = module
 
-            if leaf == "split_positions":
-                module.split_positions = value.tolist()
-            elif (cpu_offload and (cpu_offload_blocks is None or cpu_offload_blocks > 0)
-                  and leaf in offloaded_tensor_names):
-                if not hasattr(module, "offloaded_tensors"):
-                    module.offloaded_tensors = {}
-                module.offloaded_tensors[leaf] = value.pin_memory() if pin_memory else value
-                if (cpu_offload_blocks is not None and cpu_offload_blocks > 0
-                        and len(module.offloaded_tensors) == len(offloaded_tensor_names)):
-                    cpu_offload_blocks -= 1
-            else:
-                module.register_buffer(leaf, value)
+                if leaf == "split_positions":
+                    module.split_positions = mapped.tensor(tensor_name).tolist()
+                elif (cpu_offload and (cpu_offload_blocks is None or cpu_offload_blocks > 0)
+                      and leaf in offloaded_tensor_names):
+                    if not hasattr(module, "offloaded_tensors"):
+                        module.offloaded_tensors = {}
+                    module.offloaded_tensors[leaf] = mapped.tensor(tensor_name, pin=pin_memory)
+                    if (cpu_offload_blocks is not None and cpu_offload_blocks > 0
+                            and len(module.offloaded_tensors) == len(offloaded_tensor_names)):
+                        cpu_offload_blocks -= 1
+                elif uploader is not None and leaf in offloaded_tensor_names:
+                    module.register_buffer(leaf, uploader.upload(mapped.raw(tensor_name), mapped.torch_dtype(tensor_name),
+                                                                 mapped.shape(tensor_name)))
+                else:
+                    module.register_buffer(leaf, mapped.tensor(tensor_name))
 
-            if leaf == "encoded_exponent":
-                module.register_forward_pre_hook(hook)
-                _remove_weights(module, module_path, pattern_dict)
+                if leaf == "encoded_exponent":
+                    module.register_forward_pre_hook(hook)
+                    _remove_weights(module, module_path, pattern_dict)
+    if uploader is not None:
+        uploader.finish()
+        log.info("loader: %d large tensors, %.2f GB, host -> %s through pinned staging", uploader.stats["tensors"],
+                 uploader.stats["bytes"] / 1e9, uploader.device)
 
     for name, module in units.items():
         _finish_unit(module, name)
 
-    # offloaded units, linked in forward (definition) order for the prefetcher
-    offloaded = [m for m in modules.values() if hasattr(m, "offloaded_tensors")]
-    for a, b in zip(offloaded, offloaded[1:] + offloaded[:1]):
-        a.__dict__["df11_next_offloaded"] = b          # a plain reference, not a registered submodule
     _mark_root(model)
     return model
 
@@ -896,7 +1092,7 @@ class DFloat11Model:
 
         load_and_replace_tensors(model, path, dfloat11_config, cpu_offload=cpu_offload,
                                  cpu_offload_blocks=cpu_offload_blocks, pin_memory=pin_memory,
-                                 from_single_file=from_single_file)
+                                 from_single_file=from_single_file, device=device)
 
         if not cpu_offload:
             model_bytes = sum(t.numel() * t.element_size() for t in model.state_dict().values())
@@ -1116,8 +1312,5 @@ def compress_in_place(model, pattern_dict: Dict[str, List[str]], cpu_offload: bo
                     sub_module.weight_injection_modules.append(target)
             _finish_unit(sub_module, full_name)
             sub_module.register_forward_pre_hook(hook)
-    offloaded = [m for m in model.modules() if hasattr(m, "offloaded_tensors")]
-    for a, b in zip(offloaded, offloaded[1:] + offloaded[:1]):
-        a.__dict__["df11_next_offloaded"] = b
     _mark_root(model)
     return model

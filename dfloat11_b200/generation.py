@@ -27,6 +27,11 @@ class GraphedGreedyDecoder:
         self.device = next(model.parameters()).device
         if self.device.type != "cuda":
             raise RuntimeError("GraphedGreedyDecoder needs the model on a CUDA device")
+        import inspect
+        try:
+            self._keeps_logits = "logits_to_keep" in inspect.signature(model.forward).parameters
+        except (TypeError, ValueError):
+            self._keeps_logits = False
         self._cache = None
         self._graph = None
         self._tok = self._pos = self._count = self._produced = None
@@ -67,8 +72,11 @@ class GraphedGreedyDecoder:
         dev = self.device
         input_ids = input_ids.to(dev)
         self._prepare()
+        # only the last position's logits are needed: models whose forward can skip the others
+        # (`logits_to_keep`) do not multiply the whole prompt with the output head
+        extra = {"logits_to_keep": 1} if self._keeps_logits else {}
         logits = self.model(input_ids=input_ids, past_key_values=self._cache,
-                            cache_position=torch.arange(n_prompt, device=dev), use_cache=True).logits
+                            cache_position=torch.arange(n_prompt, device=dev), use_cache=True, **extra).logits
         self._tok.copy_(logits[:, -1:].argmax(-1))
         self._pos.fill_(n_prompt)
         self._count.zero_()

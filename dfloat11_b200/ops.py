@@ -15,10 +15,17 @@ import torch
 from . import _lib
 
 
-def _require_cuda(**tensors: torch.Tensor) -> torch.device:
+def _require_cuda(_pinned_ok=(), **tensors: torch.Tensor) -> torch.device:
+    """The CUDA device all the tensors are on.  Names listed in ``_pinned_ok`` may instead be pinned
+    host tensors: page-locked memory has the same address on the device (unified addressing), so a
+    kernel can read the few bytes it needs of them over PCIe without a staging copy."""
     device = None
     for name, t in tensors.items():
         if t is None:
+            continue
+        if not t.is_cuda and name in _pinned_ok and t.is_pinned():
+            if not t.is_contiguous():
+                raise RuntimeError(f"`{name}` must be contiguous")
             continue
         if not t.is_cuda:
             raise RuntimeError(f"df11 decode needs CUDA tensors; `{name}` is on {t.device}")
@@ -68,8 +75,8 @@ def prepare(luts: torch.Tensor, encoded_exponent: torch.Tensor, output_positions
             gaps: torch.Tensor, n_elements: int, aux: Optional[torch.Tensor] = None,
             status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Fill (allocating if needed) the auxiliary buffer that ``decode_prepared`` reads."""
-    device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, output_positions=output_positions,
-                           gaps=gaps, aux=aux, status=status)
+    device = _require_cuda(("encoded_exponent",), luts=luts, encoded_exponent=encoded_exponent,
+                           output_positions=output_positions, gaps=gaps, aux=aux, status=status)
     need = aux_bytes(encoded_exponent.numel(), n_elements)
     if aux is None:
         aux = torch.empty(need, dtype=torch.uint8, device=device)
@@ -144,9 +151,11 @@ def decode_rows_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sig
     """Decompress only the given rows of a unit viewed as ``[n_elements / row_elements, row_elements]``.
 
     ``rows`` is an int64 CUDA tensor; the result has one row per entry, in that order.  Needs the
-    buffer made by ``prepare`` and a row length that is a multiple of ``chunk_elements()``."""
-    device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, sign_mantissa=sign_mantissa,
-                           aux=aux, rows=rows, out=out, status=status)
+    buffer made by ``prepare`` and a row length that is a multiple of ``chunk_elements()``.
+    ``encoded_exponent`` and ``sign_mantissa`` may be pinned host tensors (the kernel then reads
+    just those rows' bytes over PCIe), as may ``encoded_exponent`` in ``prepare``."""
+    device = _require_cuda(("encoded_exponent", "sign_mantissa"), luts=luts, encoded_exponent=encoded_exponent,
+                           sign_mantissa=sign_mantissa, aux=aux, rows=rows, out=out, status=status)
     if rows.dtype != torch.int64:
         raise RuntimeError("`rows` must be an int64 tensor")
     n_rows = rows.numel()

@@ -198,6 +198,53 @@ def encode_py(symbols, code_len, code_val, eof_len, eof_val):
     return encoded.copy(), np.packbits(gap_bits.reshape(-1)), np.asarray(positions, dtype=np.uint32)
 
 
+def encode_stream_py(symbols, code_len, code_val, eof_len, eof_val):
+    """The same bit packer written the way the reference runs it (dfloat11_utils.py:118-170): one
+    Python-level step per symbol, a small bit buffer from which whole bytes are taken as they
+    fill up, so the cost is linear in the number of symbols.  ``encode_py`` above keeps the whole
+    stream in one integer, which is simple to check but quadratic; this form is what the
+    benchmark times as the reference's CPU compression rate.  Same arguments and results."""
+    lens = [int(x) for x in code_len]
+    vals = [int(x) for x in code_val]
+    out = bytearray()
+    gaps, positions = [], []
+    window_bits = 8 * WINDOW_BYTES
+    block_bits = window_bits * WINDOWS_PER_BLOCK
+    held, n_held, total = 0, 0, 0
+    next_window, next_block = 0, 0            # stream bit at which the next window / block starts
+    for i, s in enumerate(symbols):
+        if total >= next_window:              # first code that starts in a new window (windows are
+            gaps.append(total - next_window)  # never skipped: a code is at most 32 bits, a window 64)
+            next_window += window_bits
+        if total >= next_block:
+            positions.append(i)
+            next_block += block_bits
+        n = lens[s]
+        held = (held << n) | vals[s]
+        n_held += n
+        total += n
+        while n_held >= 8:
+            n_held -= 8
+            out.append(held >> n_held)
+            held &= (1 << n_held) - 1
+    n_symbols = len(symbols)
+    if n_held:
+        if total >= next_window:
+            gaps.append(total - next_window)
+        if total >= next_block:
+            positions.append(n_symbols)
+        room = 8 - n_held
+        pad = (eof_val >> (eof_len - room)) if eof_len >= room else (eof_val << (room - eof_len))
+        out.append(((held << room) | pad) & 0xFF)
+    positions.append(n_symbols)
+    encoded = np.frombuffer(bytes(out), dtype=np.uint8).copy()
+    n_blocks = -(-encoded.size // BLOCK_BYTES)
+    g = np.zeros(WINDOWS_PER_BLOCK * n_blocks, dtype=np.uint8)
+    g[:len(gaps)] = gaps
+    gap_bits = ((g[:, None] >> np.arange(4, -1, -1, dtype=np.uint8)) & 1).astype(np.uint8)
+    return encoded, np.packbits(gap_bits.reshape(-1)), np.asarray(positions, dtype=np.uint32)
+
+
 def luts_py(table):
     """LUT builder of dfloat11_utils.py:68-115 for an explicit code table.
 

@@ -164,6 +164,27 @@ def test_tensor_manager_reuses_and_grows():
     assert d.data_ptr() != c.data_ptr() and host.TensorManager.allocate_bfloat16("cpu", 10).data_ptr() == c.data_ptr()
     host.TensorManager.release("cpu")
     assert not host.TensorManager._tensors
+    # the largest unit that is decoded whole sizes slots 0 / 1 at their first allocation
+    host.TensorManager.min_elements = 300
+    e = host.TensorManager.allocate_bfloat16("cpu", 100)
+    assert e.numel() == 100 and host.TensorManager._tensors[(torch.device("cpu"), 0)].numel() == 300
+    assert host.TensorManager.allocate_bfloat16("cpu", 7, slot=2).numel() == 7
+    assert host.TensorManager._tensors[(torch.device("cpu"), 2)].numel() == 7
+    host.TensorManager.release()
+    assert host.TensorManager.min_elements == 0
+
+
+def test_growing_the_scratch_takes_back_the_views_of_the_old_one():
+    host.TensorManager.release()
+    layer = nn.Linear(4, 3, bias=False)
+    del layer._parameters["weight"]
+    layer.split_positions = []
+    small = host.TensorManager.allocate_bfloat16("cpu", 12)
+    host._inject_weights(layer, small)
+    assert layer.weight.shape == (3, 4) and layer.weight.data_ptr() == small.data_ptr()
+    host.TensorManager.allocate_bfloat16("cpu", 1000)           # grows: the old tensor must not stay referenced
+    assert layer.weight is None and layer.__dict__["df11_injected"] is None
+    host.TensorManager.release()
 
 
 def test_environment_switches_are_read_once_per_forward_of_a_marked_model(monkeypatch):
@@ -381,6 +402,89 @@ def test_embedding_unit_decodes_only_looked_up_rows(tmp_path, monkeypatch):
         assert torch.equal(loaded.emb(ids), reference(ids))
         assert loaded.emb.weight.shape == (2000, 512)
     del ref_holder
+
+
+def _wide_llama(seed=0):
+    """Hidden size 1024 (rows that every seek interval can cut), a vocabulary of 16384."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=1024, intermediate_size=2048, num_hidden_layers=2, num_attention_heads=8,
+                      num_key_value_heads=8, vocab_size=16384, max_position_embeddings=256, tie_word_embeddings=False)
+    torch.manual_seed(seed)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 2:
+                p.copy_((torch.randn(p.shape) * (1.0 if "embed" in name else 0.02)).to(torch.bfloat16))
+    return model
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("offload", [False, True])
+def test_large_head_is_multiplied_slab_by_slab(monkeypatch, offload):
+    """A single-Linear unit above SLAB_MIN_ELEMENTS called with up to four activation vectors is
+    decompressed and multiplied in slabs of rows inside the scratch sized for the transformer
+    blocks; logits stay bit-identical to BF16 and the scratch never grows to the size of the head.
+    Under cpu_offload the embedding's rows are read straight from pinned memory (never staged)."""
+    monkeypatch.setattr(host, "SLAB_MIN_ELEMENTS", 1 << 22)              # the 16384 x 1024 head counts as large
+    host.TensorManager.release()
+    host._OffloadStager._by_device.clear()
+    model = _wide_llama().to("cuda:0")
+    ref = copy.deepcopy(model)
+    df11.compress_in_place(model, LLAMA_PATTERNS, cpu_offload=offload)
+    head_elements = 16384 * 1024
+    block_elements = 4 * 1024 * 1024 + 3 * 1024 * 2048
+    assert host.TensorManager.min_elements == block_elements
+    assert model.lm_head.__dict__.get("df11_slabbed") and 0 < host._slab_rows(model.lm_head) < 16384
+    before = df11.stats()["slab_products"]
+    dev = torch.device("cuda:0")
+    with torch.no_grad():
+        for tokens in (1, 3, 4):
+            ids = torch.randint(0, 16384, (1, tokens), generator=torch.Generator().manual_seed(tokens)).to(dev)
+            assert torch.equal(model(input_ids=ids).logits, ref(input_ids=ids).logits)
+        assert df11.stats()["slab_products"] == before + 3
+        assert host.TensorManager._tensors[(dev, 0)].numel() == block_elements < head_elements
+        out_a = model.generate(ids[:, :1], max_new_tokens=6, do_sample=False)
+        assert torch.equal(out_a, ref.generate(ids[:, :1], max_new_tokens=6, do_sample=False))
+        ids = torch.randint(0, 16384, (2, 9), generator=torch.Generator().manual_seed(9)).to(dev)
+        assert torch.equal(model(input_ids=ids).logits, ref(input_ids=ids).logits)      # 18 vectors: whole decode
+        assert host.TensorManager._tensors[(dev, 0)].numel() >= head_elements
+        ids = ids[:1, :2]
+        assert torch.equal(model(input_ids=ids).logits, ref(input_ids=ids).logits)      # and slabs again afterwards
+        monkeypatch.setenv("DF11_SLAB_HEAD", "0")
+        assert torch.equal(model(input_ids=ids).logits, ref(input_ids=ids).logits)
+    df11.check_status()
+    if offload:
+        staged = host._OffloadStager.get(dev).stats["h2d_bytes"]
+        emb = model.model.embed_tokens.offloaded_tensors
+        assert staged > 0 and "df11_next_offloaded" not in model.model.embed_tokens.__dict__
+        assert all(s["owner"] is not model.model.embed_tokens for s in host._OffloadStager.get(dev).slots)
+        assert emb["sign_mantissa"].is_pinned() and model.model.embed_tokens.weight.shape[0] <= 18
+    assert not model.model.layers[0].gaps.is_cuda                        # parked on the host after prepare
+    host.TensorManager.release()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(151936, 4096), (128256, 4096), (12288, 4096), (4096, 14336)])
+def test_row_slabs_of_a_product_have_the_bits_of_the_whole_product(rows, cols):
+    """What the slab-wise head relies on: for a few activation vectors the library computes each
+    output row the same way whether it is given the whole [rows, cols] matrix or a block of its
+    rows -- checked at the baseline configurations' head and MLP shapes, slabs of 47104 rows (a
+    Qwen3-8B block's worth of scratch) and of 8192."""
+    import torch.nn.functional as F
+    g = torch.Generator(device="cuda:0").manual_seed(rows)
+    w = (torch.randn(rows, cols, device="cuda:0", generator=g) * 0.02).to(torch.bfloat16)
+    for m in (1, 2, 3, 4):
+        x = torch.randn(1, m, cols, device="cuda:0", generator=g).to(torch.bfloat16)
+        whole = F.linear(x, w)
+        for slab in (47104, 8192):
+            got = torch.empty_like(whole)
+            for r0 in range(0, rows, slab):
+                r1 = min(rows, r0 + slab)
+                if m == 1:
+                    torch.mm(x.view(1, cols), w[r0:r1].t(), out=got.view(1, rows)[:, r0:r1])
+                else:
+                    got[..., r0:r1] = F.linear(x, w[r0:r1])
+            assert torch.equal(got, whole), (m, slab)
 
 
 @pytest.mark.gpu

@@ -57,6 +57,17 @@ def test_encode_py_matches_reference(golden):
     assert np.array_equal(pos, golden["output_positions"])
 
 
+def test_encode_stream_py_matches_reference(golden):
+    """The linear-time restatement (what the benchmark times as the CPU compression rate)."""
+    e, _ = oracle.split_bf16(golden["w"])
+    code_len, code_val = _tables(golden)
+    enc, gaps, pos = oracle.encode_stream_py(e.tolist(), code_len, code_val,
+                                             int(golden["eof_bits"]), int(golden["eof_val"]))
+    assert np.array_equal(enc, golden["encoded"])
+    assert np.array_equal(gaps, golden["gaps"])
+    assert np.array_equal(pos, golden["output_positions"])
+
+
 def test_luts_py_matches_reference(golden):
     table = list(zip(golden["table_syms"].tolist(), golden["table_bits"].tolist(),
                      golden["table_vals"].tolist()))
