@@ -379,6 +379,11 @@ def main():
                          "separately, the profiler leaves a per-launch cost behind that slows the eager legs after it")
     ap.add_argument("--cpu-offload", action="store_true",
                     help="with --generation: DF11 with cpu_offload=True at --batch sequences against resident BF16")
+    ap.add_argument("--dit-step", action="store_true",
+                    help="only: one denoising step of the FLUX.1-dev-shaped transformer, DF11 against BF16")
+    ap.add_argument("--slab-pipeline", action="store_true",
+                    help="only: one block's batch-1 products with the weights decompressed slab by slab right "
+                         "before each product (L2-resident) against decode-the-whole-block")
     ap.add_argument("--new-tokens", type=int, default=512)
     ap.add_argument("--prompt-tokens", type=int, default=64)
     args = ap.parse_args()
@@ -392,6 +397,12 @@ def main():
         return
     if args.fused_gemv:
         run_fused_gemv(args, cfg)
+        return
+    if args.dit_step:
+        run_dit_step(args)
+        return
+    if args.slab_pipeline:
+        run_slab_pipeline(args, cfg)
         return
 
     if not torch.cuda.is_available():
@@ -1047,6 +1058,286 @@ def tp_block(args, rank, world, device):
         store.set("df11_bench_placement_done", "1")
     barrier(world, device)
     return out
+
+
+def run_dit_step(args):
+    """One denoising step of a FLUX.1-dev-shaped diffusion transformer (19 double-stream + 38
+    single-stream blocks, hidden 3072, 24 heads, MLP ratio 4; 4096 latent + 512 text tokens;
+    random init N(0, 0.02)): the uncompressed BF16 model, then the same model object compressed in
+    place.  Step time by CUDA events, outputs compared bit for bit."""
+    import dfloat11_b200 as df11
+    from dfloat11_b200.dfloat11 import TensorManager
+    dev = torch.device("cuda", 0)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with dev:
+            model = FluxShapedDiT().eval()
+    finally:
+        torch.set_default_dtype(old)
+    with torch.no_grad():
+        g = torch.Generator(device=dev).manual_seed(4)
+        for p in model.parameters():
+            p.normal_(0.0, 0.02, generator=g)
+    x = torch.randn(1, 4096, 3072, device=dev, generator=g).to(torch.bfloat16)
+    ctx = torch.randn(1, 512, 3072, device=dev, generator=g).to(torch.bfloat16)
+    cond = torch.randn(1, 1, 3072, device=dev, generator=g).to(torch.bfloat16)
+    n_weights = sum(p.numel() for p in model.parameters() if p.dim() == 2)
+
+    def timed():
+        with torch.no_grad():
+            for _ in range(max(args.warmup, 1)):
+                out = model(x, ctx, cond)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(args.steps):
+                out = model(x, ctx, cond)
+            b.record()
+            torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps, out
+
+    torch.cuda.reset_peak_memory_stats()
+    ms_bf16, out_bf16 = timed()
+    mem_bf16 = torch.cuda.max_memory_allocated() / 1e9
+    t0 = time.time()
+    df11.compress_in_place(model, {k: list(v) for k, v in FLUX_PATTERNS.items()})
+    torch.cuda.empty_cache()
+    t_compress = time.time() - t0
+    torch.cuda.reset_peak_memory_stats()
+    ms_df11, out_df11 = timed()
+    mem_df11 = torch.cuda.max_memory_allocated() / 1e9
+    print(json.dumps({
+        "metric": "dit_denoising_step_ms", "unit": "ms", "workload": FLUX_DIT["name"], "weights": n_weights,
+        "tokens": {"latent": 4096, "text": 512}, "bf16_ms": round(ms_bf16, 3), "df11_ms": round(ms_df11, 3),
+        "slowdown_vs_bf16": round(ms_df11 / ms_bf16, 4), "identical_output": bool(torch.equal(out_bf16, out_df11)),
+        "peak_mem_GB": {"bf16": round(mem_bf16, 2), "df11": round(mem_df11, 2)}, "compress_s": round(t_compress, 1),
+        "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
+        "df11_stats": {k: v for k, v in df11.stats().items() if isinstance(v, int)},
+    }))
+    TensorManager.release()
+
+
+def run_slab_pipeline(args, cfg):
+    """Decode-in-slabs against decode-the-whole-block, for one transformer block's seven batch-1
+    products: each matrix (or slab of its rows, or run of neighbouring matrices) of at most B MB of
+    BF16 is decompressed into the same scratch addresses right before the library product that
+    reads it, so that the BF16 copy can stay in the L2 cache.  Four distinct blocks are cycled so
+    that compressed data always comes from HBM; each variant is captured in a CUDA graph."""
+    import torch.nn.functional as F
+    from dfloat11_b200 import ops
+    dev = torch.device("cuda", 0)
+    shapes = block_shapes(cfg)
+    n = sum(a * b for a, b in shapes)
+    n_blocks = 4
+    units = [make_unit(n, 0.02, 200 + i, dev, keep_weights=True) for i in range(n_blocks)]
+    auxs = [ops.prepare(u["luts"], u["enc"], u["pos"], u["gaps"], n) for u in units]
+    scratch = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    starts = [0]
+    for a, b in shapes:
+        starts.append(starts[-1] + a * b)
+    xs = {b: torch.randn(1, b, device=dev).to(torch.bfloat16) for _, b in shapes}
+    outs = [torch.empty(1, a, dtype=torch.bfloat16, device=dev) for a, _ in shapes]
+
+    def bf16_block(i):
+        w = units[i]["weights"]
+        for k, (a, b) in enumerate(shapes):
+            torch.mm(xs[b], w[starts[k]:starts[k + 1]].view(a, b).t(), out=outs[k])
+
+    def whole(i):
+        u = units[i]
+        ops.decode_prepared(u["luts"], u["enc"], u["sm"], u["pos"], u["gaps"], auxs[i], out=scratch)
+        for k, (a, b) in enumerate(shapes):
+            torch.mm(xs[b], scratch[starts[k]:starts[k + 1]].view(a, b).t(), out=outs[k])
+
+    def decode_only(i):
+        u = units[i]
+        ops.decode_prepared(u["luts"], u["enc"], u["sm"], u["pos"], u["gaps"], auxs[i], out=scratch)
+
+    def slabbed(budget_mb):
+        budget = (budget_mb << 20) // 2
+        plan, k = [], 0
+        while k < len(shapes):
+            a, b = shapes[k]
+            if a * b <= budget:                       # this matrix and the ones after it, while they fit
+                first, total, parts = starts[k], 0, []
+                while k < len(shapes) and total + shapes[k][0] * shapes[k][1] <= budget:
+                    parts.append((k, 0, shapes[k][0], total))
+                    total += shapes[k][0] * shapes[k][1]
+                    k += 1
+                plan.append((first, total, parts))
+            else:                                     # slabs of rows
+                n_slabs = -(-a // max(1, budget // b))
+                rows = (-(-a // n_slabs) + 7) // 8 * 8
+                for r0 in range(0, a, rows):
+                    r1 = min(a, r0 + rows)
+                    plan.append((starts[k] + r0 * b, (r1 - r0) * b, [(k, r0, r1, 0)]))
+                k += 1
+        slab = scratch[:max(p[1] for p in plan)]
+
+        def run(i):
+            u = units[i]
+            for first, total, parts in plan:
+                ops.decode_range_prepared(u["luts"], u["enc"], u["sm"], auxs[i], first, total, out=slab)
+                for (k, r0, r1, off) in parts:
+                    a, b = shapes[k]
+                    torch.mm(xs[b], slab[off:off + (r1 - r0) * b].view(r1 - r0, b).t(), out=outs[k][:, r0:r1])
+        return run, len(plan), sum(len(p[2]) for p in plan)
+
+    def graph_ms(fn):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(n_blocks):
+                fn(i)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(n_blocks):
+                fn(i)
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps / n_blocks
+
+    bf16_block(0)
+    want = [o.clone() for o in outs]
+    result = {"metric": "batch1_block_products_ms", "unit": "ms per block", "workload": cfg["name"],
+              "elements_per_block": n, "bf16_products": round(graph_ms(bf16_block), 4),
+              "decode_whole_then_products": round(graph_ms(whole), 4), "decode_whole_alone": round(graph_ms(decode_only), 4),
+              "slabs": {}, "steps": args.steps, "data": "synthetic"}
+    for mb in (16, 32, 48, 64, 101):
+        run, n_dec, n_mm = slabbed(mb)
+        for o in outs:
+            o.zero_()
+        run(0)
+        same = all(bool(torch.equal(o, w)) for o, w in zip(outs, want))
+        result["slabs"][f"{mb}MB"] = {"ms": round(graph_ms(run), 4), "decode_launches": n_dec, "products": n_mm,
+                                      "bits_of_the_whole_products": same}
+    print(json.dumps(result))
+
+
+class FluxShapedDiT(torch.nn.Module):
+    """A diffusion-transformer stack with the module names and Linear shapes of the reference's
+    FLUX pattern dictionary (examples/compress_flux1/compress_flux.py:49-74): double-stream blocks
+    with separate image / text projections and a joint attention, single-stream blocks with a
+    fused MLP + attention output.  FLUX.1-dev has hidden 3072, 24 heads, 19 + 38 blocks; the tests
+    build it at toy size.  Own minimal forward (diffusers is not a dependency): what matters for
+    the decompression path are the units, their shapes and that every Linear runs."""
+
+    class _Mod(torch.nn.Module):
+        def __init__(self, h, n):
+            super().__init__()
+            self.linear = torch.nn.Linear(h, n * h)
+            self.n = n
+
+        def forward(self, cond):
+            return self.linear(torch.nn.functional.silu(cond)).chunk(self.n, dim=-1)
+
+    class _Attn(torch.nn.Module):
+        def __init__(self, h, heads, joint):
+            super().__init__()
+            self.heads = heads
+            self.to_q, self.to_k, self.to_v = torch.nn.Linear(h, h), torch.nn.Linear(h, h), torch.nn.Linear(h, h)
+            if joint:
+                self.add_q_proj, self.add_k_proj, self.add_v_proj = torch.nn.Linear(h, h), torch.nn.Linear(h, h), torch.nn.Linear(h, h)
+                self.to_out = torch.nn.ModuleList([torch.nn.Linear(h, h)])
+                self.to_add_out = torch.nn.Linear(h, h)
+
+        def _split(self, t):
+            b, n, h = t.shape
+            return t.view(b, n, self.heads, h // self.heads).transpose(1, 2)
+
+        def forward(self, x, ctx=None):
+            q, k, v = self.to_q(x), self.to_k(x), self.to_v(x)
+            if ctx is not None:
+                q = torch.cat([self.add_q_proj(ctx), q], 1)
+                k = torch.cat([self.add_k_proj(ctx), k], 1)
+                v = torch.cat([self.add_v_proj(ctx), v], 1)
+            o = torch.nn.functional.scaled_dot_product_attention(self._split(q), self._split(k), self._split(v))
+            o = o.transpose(1, 2).reshape(q.shape)
+            if ctx is None:
+                return o
+            n_ctx = ctx.shape[1]
+            return self.to_out[0](o[:, n_ctx:]), self.to_add_out(o[:, :n_ctx])
+
+    class _FF(torch.nn.Module):
+        class _Proj(torch.nn.Module):
+            def __init__(self, h, m):
+                super().__init__()
+                self.proj = torch.nn.Linear(h, m)
+
+            def forward(self, x):
+                return torch.nn.functional.gelu(self.proj(x), approximate="tanh")
+
+        def __init__(self, h, m):
+            super().__init__()
+            self.net = torch.nn.ModuleList([self._Proj(h, m), torch.nn.Identity(), torch.nn.Linear(m, h)])
+
+        def forward(self, x):
+            return self.net[2](self.net[0](x))
+
+    class _Double(torch.nn.Module):
+        def __init__(self, h, heads):
+            super().__init__()
+            self.norm1, self.norm1_context = FluxShapedDiT._Mod(h, 6), FluxShapedDiT._Mod(h, 6)
+            self.attn = FluxShapedDiT._Attn(h, heads, joint=True)
+            self.ff, self.ff_context = FluxShapedDiT._FF(h, 4 * h), FluxShapedDiT._FF(h, 4 * h)
+            self.ln = torch.nn.LayerNorm(h, elementwise_affine=False)
+
+        def forward(self, x, ctx, cond):
+            s1, c1, g1, s2, c2, g2 = self.norm1(cond)
+            t1, d1, h1, t2, d2, h2 = self.norm1_context(cond)
+            a, b = self.attn(self.ln(x) * (1 + c1) + s1, self.ln(ctx) * (1 + d1) + t1)
+            x, ctx = x + g1 * a, ctx + h1 * b
+            x = x + g2 * self.ff(self.ln(x) * (1 + c2) + s2)
+            ctx = ctx + h2 * self.ff_context(self.ln(ctx) * (1 + d2) + t2)
+            return x, ctx
+
+    class _Single(torch.nn.Module):
+        def __init__(self, h, heads):
+            super().__init__()
+            self.norm = FluxShapedDiT._Mod(h, 3)
+            self.proj_mlp = torch.nn.Linear(h, 4 * h)
+            self.proj_out = torch.nn.Linear(5 * h, h)
+            self.attn = FluxShapedDiT._Attn(h, heads, joint=False)
+            self.ln = torch.nn.LayerNorm(h, elementwise_affine=False)
+
+        def forward(self, x, cond):
+            s, c, g = self.norm(cond)
+            y = self.ln(x) * (1 + c) + s
+            m = torch.nn.functional.gelu(self.proj_mlp(y), approximate="tanh")
+            return x + g * self.proj_out(torch.cat([self.attn(y), m], dim=-1))
+
+    def __init__(self, h=3072, heads=24, n_double=19, n_single=38):
+        super().__init__()
+        self.transformer_blocks = torch.nn.ModuleList([self._Double(h, heads) for _ in range(n_double)])
+        self.single_transformer_blocks = torch.nn.ModuleList([self._Single(h, heads) for _ in range(n_single)])
+        self.proj_out = torch.nn.Linear(h, 16)
+
+    def forward(self, x, ctx, cond):
+        for blk in self.transformer_blocks:
+            x, ctx = blk(x, ctx, cond)
+        x = torch.cat([ctx, x], dim=1)
+        for blk in self.single_transformer_blocks:
+            x = blk(x, cond)
+        return self.proj_out(x[:, ctx.shape[1]:])
+
+
+FLUX_PATTERNS = {                                  # tuples, dotted paths: as the reference writes them
+    r"transformer_blocks\.\d+": ("norm1.linear", "norm1_context.linear", "attn.to_q", "attn.to_k", "attn.to_v",
+                                 "attn.add_k_proj", "attn.add_v_proj", "attn.add_q_proj", "attn.to_out.0",
+                                 "attn.to_add_out", "ff.net.0.proj", "ff.net.2", "ff_context.net.0.proj",
+                                 "ff_context.net.2"),
+    r"single_transformer_blocks\.\d+": ("norm.linear", "proj_mlp", "proj_out", "attn.to_q", "attn.to_k", "attn.to_v"),
+}
 
 
 class _Unit(torch.nn.Module):

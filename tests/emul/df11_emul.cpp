@@ -14,6 +14,8 @@
 
 namespace {
 
+bool g_reverse = false;  // order in which the windows of a block run their decode pass
+
 // Memory policy of the window routines for plain host arrays.
 struct HostMem {
     const uint32_t *cnt_t;
@@ -23,8 +25,11 @@ struct HostMem {
     uint32_t cnt(uint32_t i) const { return cnt_t[i]; }
     Df11Entry dec(uint32_t i) const { return dec_t[i]; }
     uint32_t lut(uint32_t i) const { return luts[i]; }
-    template <int OFF>
-    void put(uint32_t slot, uint32_t v) const { stage[slot + OFF] = (uint8_t)v; }
+    void put8(uint32_t addr, uint32_t v) const { stage[addr] = (uint8_t)v; }
+    void put32(uint32_t addr, uint32_t w) const
+    {
+        for (int k = 0; k < 4; ++k) stage[addr + k] = (uint8_t)(w >> (8 * k));
+    }
     // seek-point decoder
     const uint8_t *codes = nullptr;
     int64_t n_bytes = 0;
@@ -166,22 +171,31 @@ int run(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, 
         const uint32_t block_cnt = (uint32_t)c;
         memset(stage.data(), 0xEE, stage.size());  // poison: stale bytes must never reach the output
 
+        // the kernel's 512 threads write their windows in no particular order: first every window's
+        // slots (count pass + scan), then the decode pass front to back or back to front (g_reverse),
+        // so that a window that writes into a neighbour's bytes shows up in one of the two orders
         uint32_t run_sum = 0;
+        struct Win { uint32_t w[3], gap, o, end; bool live; } wins[DF11_WINDOWS_PER_BLOCK];
         for (int tid = 0; tid < DF11_WINDOWS_PER_BLOCK; ++tid) {
+            Win &x = wins[tid];
             const int64_t t = b * DF11_WINDOWS_PER_BLOCK + tid;
-            if (t * 8 >= n_bytes) break;
-            uint32_t w[3];
-            load_window(codes, n_bytes, t, w);
-            uint32_t gap, o, end;
+            x.live = t * 8 < n_bytes;
+            if (!x.live) continue;
+            load_window(codes, n_bytes, t, x.w);
             int tbad = 0;
-            gap = df11_gap(gaps, n_gap_bytes, t);
-            const uint32_t n = df11_count_window<K>(mem, n_luts, w[0], w[1], w[2], gap, &tbad);
-            o = run_sum;
-            end = o + n;
+            x.gap = df11_gap(gaps, n_gap_bytes, t);
+            const uint32_t n = df11_count_window<K>(mem, n_luts, x.w[0], x.w[1], x.w[2], x.gap, &tbad);
+            uint32_t o = run_sum, end = o + n;
             run_sum += n;
-            o = (o < block_cnt ? o : block_cnt) + phase;
-            end = (end < block_cnt ? end : block_cnt) + phase;
-            df11_decode_window<K>(mem, n_luts, w[0], w[1], w[2], gap, o, end, &tbad);
+            x.o = (o < block_cnt ? o : block_cnt) + phase;
+            x.end = (end < block_cnt ? end : block_cnt) + phase;
+            if (tbad) bad |= DF11_STATUS_BAD_TABLE;
+        }
+        for (int k = 0; k < DF11_WINDOWS_PER_BLOCK; ++k) {
+            const Win &x = wins[g_reverse ? DF11_WINDOWS_PER_BLOCK - 1 - k : k];
+            if (!x.live) continue;
+            int tbad = 0;
+            df11_decode_window<K>(mem, n_luts, x.w[0], x.w[1], x.w[2], x.gap, x.o, x.end, &tbad);
             if (tbad) bad |= DF11_STATUS_BAD_TABLE;
         }
 
@@ -209,6 +223,8 @@ int run(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, 
 }
 
 }  // namespace
+
+extern "C" void df11_emul_window_order(int reverse) { g_reverse = reverse != 0; }
 
 // prepared: 0 = the self-contained two-pass flow, 16 / 32 = seek points every 16 / 32 elements
 extern "C" int df11_emul_decode(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes,

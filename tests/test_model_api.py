@@ -576,118 +576,11 @@ def test_graphed_greedy_decoder(saved):
         decoder.generate(ids, 100)
 
 
-class _TinyDiT(nn.Module):
-    """A small diffusion-transformer stack with the module names of the reference's FLUX pattern
-    dictionary (examples/compress_flux1/compress_flux.py:49-74): double-stream blocks with
-    separate image / text projections and a joint attention, single-stream blocks with a fused
-    MLP + attention output.  Own minimal forward; only the names and shapes matter here."""
-
-    class _Mod(nn.Module):
-        def __init__(self, h, n):
-            super().__init__()
-            self.linear = nn.Linear(h, n * h)
-            self.n = n
-
-        def forward(self, cond):
-            return self.linear(torch.nn.functional.silu(cond)).chunk(self.n, dim=-1)
-
-    class _Attn(nn.Module):
-        def __init__(self, h, heads, joint):
-            super().__init__()
-            self.heads = heads
-            self.to_q, self.to_k, self.to_v = nn.Linear(h, h), nn.Linear(h, h), nn.Linear(h, h)
-            if joint:
-                self.add_q_proj, self.add_k_proj, self.add_v_proj = nn.Linear(h, h), nn.Linear(h, h), nn.Linear(h, h)
-                self.to_out = nn.ModuleList([nn.Linear(h, h)])
-                self.to_add_out = nn.Linear(h, h)
-
-        def _split(self, t):
-            b, n, h = t.shape
-            return t.view(b, n, self.heads, h // self.heads).transpose(1, 2)
-
-        def forward(self, x, ctx=None):
-            q, k, v = self.to_q(x), self.to_k(x), self.to_v(x)
-            if ctx is not None:
-                q = torch.cat([self.add_q_proj(ctx), q], 1)
-                k = torch.cat([self.add_k_proj(ctx), k], 1)
-                v = torch.cat([self.add_v_proj(ctx), v], 1)
-            o = torch.nn.functional.scaled_dot_product_attention(self._split(q), self._split(k), self._split(v))
-            o = o.transpose(1, 2).reshape(q.shape)
-            if ctx is None:
-                return o
-            n_ctx = ctx.shape[1]
-            return self.to_out[0](o[:, n_ctx:]), self.to_add_out(o[:, :n_ctx])
-
-    class _FF(nn.Module):
-        class _Proj(nn.Module):
-            def __init__(self, h, m):
-                super().__init__()
-                self.proj = nn.Linear(h, m)
-
-            def forward(self, x):
-                return torch.nn.functional.gelu(self.proj(x), approximate="tanh")
-
-        def __init__(self, h, m):
-            super().__init__()
-            self.net = nn.ModuleList([self._Proj(h, m), nn.Identity(), nn.Linear(m, h)])
-
-        def forward(self, x):
-            return self.net[2](self.net[0](x))
-
-    class _Double(nn.Module):
-        def __init__(self, h, heads):
-            super().__init__()
-            self.norm1, self.norm1_context = _TinyDiT._Mod(h, 6), _TinyDiT._Mod(h, 6)
-            self.attn = _TinyDiT._Attn(h, heads, joint=True)
-            self.ff, self.ff_context = _TinyDiT._FF(h, 4 * h), _TinyDiT._FF(h, 4 * h)
-            self.ln = nn.LayerNorm(h, elementwise_affine=False)
-
-        def forward(self, x, ctx, cond):
-            s1, c1, g1, s2, c2, g2 = self.norm1(cond)
-            t1, d1, h1, t2, d2, h2 = self.norm1_context(cond)
-            a, b = self.attn(self.ln(x) * (1 + c1) + s1, self.ln(ctx) * (1 + d1) + t1)
-            x, ctx = x + g1 * a, ctx + h1 * b
-            x = x + g2 * self.ff(self.ln(x) * (1 + c2) + s2)
-            ctx = ctx + h2 * self.ff_context(self.ln(ctx) * (1 + d2) + t2)
-            return x, ctx
-
-    class _Single(nn.Module):
-        def __init__(self, h, heads):
-            super().__init__()
-            self.norm = _TinyDiT._Mod(h, 3)
-            self.proj_mlp = nn.Linear(h, 4 * h)
-            self.proj_out = nn.Linear(5 * h, h)
-            self.attn = _TinyDiT._Attn(h, heads, joint=False)
-            self.ln = nn.LayerNorm(h, elementwise_affine=False)
-
-        def forward(self, x, cond):
-            s, c, g = self.norm(cond)
-            y = self.ln(x) * (1 + c) + s
-            m = torch.nn.functional.gelu(self.proj_mlp(y), approximate="tanh")
-            return x + g * self.proj_out(torch.cat([self.attn(y), m], dim=-1))
-
-    def __init__(self, h=128, heads=4):
-        super().__init__()
-        self.transformer_blocks = nn.ModuleList([self._Double(h, heads) for _ in range(2)])
-        self.single_transformer_blocks = nn.ModuleList([self._Single(h, heads) for _ in range(2)])
-        self.proj_out = nn.Linear(h, 16)
-
-    def forward(self, x, ctx, cond):
-        for blk in self.transformer_blocks:
-            x, ctx = blk(x, ctx, cond)
-        x = torch.cat([ctx, x], dim=1)
-        for blk in self.single_transformer_blocks:
-            x = blk(x, cond)
-        return self.proj_out(x[:, ctx.shape[1]:])
+from bench import FLUX_PATTERNS, FluxShapedDiT          # the benchmark's FLUX-shaped stack, here at toy size
 
 
-FLUX_PATTERNS = {                                  # tuples, dotted paths: as the reference writes them
-    r"transformer_blocks\.\d+": ("norm1.linear", "norm1_context.linear", "attn.to_q", "attn.to_k", "attn.to_v",
-                                 "attn.add_k_proj", "attn.add_v_proj", "attn.add_q_proj", "attn.to_out.0",
-                                 "attn.to_add_out", "ff.net.0.proj", "ff.net.2", "ff_context.net.0.proj",
-                                 "ff_context.net.2"),
-    r"single_transformer_blocks\.\d+": ("norm.linear", "proj_mlp", "proj_out", "attn.to_q", "attn.to_k", "attn.to_v"),
-}
+def _TinyDiT():
+    return FluxShapedDiT(h=128, heads=4, n_double=2, n_single=2)
 
 
 @pytest.mark.gpu
