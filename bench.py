@@ -384,6 +384,8 @@ def main():
     ap.add_argument("--slab-pipeline", action="store_true",
                     help="only: one block's batch-1 products with the weights decompressed slab by slab right "
                          "before each product (L2-resident) against decode-the-whole-block")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="with --generation on the partitioned workload: transformer layers to build (0 = as many as fit)")
     ap.add_argument("--new-tokens", type=int, default=512)
     ap.add_argument("--prompt-tokens", type=int, default=64)
     args = ap.parse_args()
@@ -391,6 +393,9 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args, cfg)
+        return
+    if args.generation and cfg.get("tp"):
+        run_tp_generation(args, cfg)
         return
     if args.generation:
         run_generation(args, cfg)
@@ -913,7 +918,7 @@ def generation_block(cfg, dev, new_tokens=128, prompt_tokens=64):
         held["everything_else"] = torch.cuda.memory_allocated() - sum(held.values())
         out["df11_memory_GB"] = {k: round(v / 1e9, 3) for k, v in held.items()}
         out["df11_stats"] = {k: v for k, v in df11.stats().items() if k in ("decodes", "prepares", "sparse_lookups",
-                                                                            "fused_products", "l2_slab_products")}
+                                                                            "fused_products", "slab_products")}
     del model
     TensorManager.release()
     torch.cuda.empty_cache()
@@ -1058,6 +1063,82 @@ def tp_block(args, rank, world, device):
         store.set("df11_bench_placement_done", "1")
     barrier(world, device)
     return out
+
+
+def run_tp_generation(args, cfg):
+    """Greedy generation in the partitioned mode on the job's ranks: a Llama-3.1-405B-shaped
+    model (hidden 16384, 128 / 8 heads, intermediate 53248, vocabulary 128256; as many of the 126
+    layers as `--layers` or the memory allow) whose every rank holds only its tensor-parallel
+    shards, random init.  First the BF16 shards, then the same modules compressed in place; both
+    through GraphedGreedyDecoder with the activation all-reduces, the embedding all-reduce and
+    the logits all-gather inside the captured step.  Ids must be identical."""
+    import torch.distributed as dist
+    import dfloat11_b200 as df11
+    from dfloat11_b200 import tp
+    from dfloat11_b200.dfloat11 import TensorManager
+    from transformers import LlamaConfig, LlamaForCausalLM
+    rank, world, local = dist_setup(args.gpus)
+    if world < 2:
+        raise SystemExit("the partitioned generation leg needs 2, 4 or 8 ranks (torchrun)")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    per_layer = 2 * sum(a * b for a, b in block_shapes(cfg)) // world
+    vocab = 128256
+    fixed = 2 * 2 * vocab * cfg["hidden"] // world
+    layers = args.layers or int(min(cfg["layers"], (140e9 - fixed) // per_layer))
+    config = LlamaConfig(hidden_size=cfg["hidden"], intermediate_size=cfg["inter"], num_hidden_layers=layers,
+                         num_attention_heads=cfg["hidden"] // 128, num_key_value_heads=cfg["kv"] // 128,
+                         vocab_size=vocab, tie_word_embeddings=False, max_position_embeddings=4096)
+    with torch.device("meta"):
+        model = LlamaForCausalLM(config).to(torch.bfloat16).eval()
+    tp.apply_tensor_parallel(model, GEN_PATTERNS, world, rank)           # shapes and collectives; no data yet
+    rotary = type(model.model.rotary_emb)
+    model.to_empty(device=dev)
+    model.model.rotary_emb = rotary(config=config, device=dev)           # its tables are computed, not loaded
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 2:
+                p.normal_(0.0, 1.0 if "embed_tokens" in name else 0.02, generator=g)
+            else:
+                p.fill_(1.0)
+    ids = torch.randint(0, vocab, (args.batch, args.prompt_tokens), device=dev,
+                        generator=torch.Generator(device=dev).manual_seed(2))   # the same prompts on every rank
+
+    def generate():
+        torch.cuda.reset_peak_memory_stats()
+        decoder = df11.GraphedGreedyDecoder(model, max_cache_len=args.prompt_tokens + args.new_tokens + 16)
+        decoder.generate(ids, 8)
+        barrier(world, dev)
+        t0 = time.time()
+        out = decoder.generate(ids, args.new_tokens)
+        barrier(world, dev)
+        return out[:, args.prompt_tokens:], time.time() - t0, torch.cuda.max_memory_allocated() / 1e9
+
+    with torch.no_grad():
+        out_bf16, t_bf16, mem_bf16 = generate()
+        t0 = time.time()
+        df11.compress_in_place(model, GEN_PATTERNS)
+        torch.cuda.empty_cache()
+        t_compress = time.time() - t0
+        out_df11, t_df11, mem_df11 = generate()
+    same = torch.tensor([int(torch.equal(out_bf16, out_df11))], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    t_bf16, t_df11 = all_max(t_bf16, world, dev), all_max(t_df11, world, dev)
+    tokens = args.batch * args.new_tokens
+    if rank == 0:
+        print(json.dumps({
+            "metric": "tp_generation_tok_per_s", "unit": "tok/s", "workload": cfg["name"], "parallelism": f"tp{world}",
+            "layers": layers, "layers_of_the_full_model": cfg["layers"], "batch": args.batch,
+            "prompt_tokens": args.prompt_tokens, "new_tokens": args.new_tokens,
+            "harness": "greedy, static KV cache, one CUDA graph per step with the NCCL collectives inside",
+            "bf16_shards_tok_s": round(tokens / t_bf16, 2), "df11_shards_tok_s": round(tokens / t_df11, 2),
+            "slowdown_vs_bf16_shards": round(t_df11 / t_bf16, 3), "ids_identical": bool(same.item()),
+            "peak_mem_GB_per_rank": {"bf16": round(mem_bf16, 1), "df11": round(mem_df11, 1)},
+            "compress_s": round(t_compress, 1), "vocabulary_parallel": True, "data": "synthetic",
+        }))
+    TensorManager.release()
+    dist.destroy_process_group()
 
 
 def run_dit_step(args):
@@ -1402,7 +1483,26 @@ def run_e2e(units, scratch, status, device, world, args):
     if got != units[-1]["checksum"]:
         raise SystemExit("e2e decode mismatch")
     stats = _OffloadStager.get(device).stats
+    # the ceiling of this leg: bare pinned-host -> HBM copies of the same tensors, all ranks at once
+    # (they share the host's memory system and PCIe root ports), nothing decoded
+    copy_stream = torch.cuda.Stream(device=device)
+    sink = torch.empty(max(t.numel() for m in mods for t in m.offloaded_tensors.values()), dtype=torch.uint8,
+                       device=device)
+    barrier(world, device)
+    with torch.cuda.stream(copy_stream):
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for m in mods:
+            for t in m.offloaded_tensors.values():
+                sink[:t.numel()].copy_(t, non_blocking=True)
+        c1.record()
+    copy_stream.synchronize()
+    barrier(world, device)
+    copy_ms = all_max(c0.elapsed_time(c1), world, device)
     return {"value": round(total / ms / 1e6, 1), "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
+            "bare_h2d_copy_ms_per_step": round(copy_ms, 3),
+            "bare_h2d_copy_GBps_per_rank": round(h2d / copy_ms / 1e6, 1),
+            "frac_of_bare_copy_ceiling": round(copy_ms / ms, 3),
             "d2h_bytes_per_step": int(result_host.numel() * 2), "ms_per_step": round(ms, 3),
             "steps": args.e2e_steps, "units": len(units), "prefetch_hits": stats["prefetch_hits"],
             "path": "forward pre-hook of the package with cpu_offload units: pinned host encoded_exponent + "

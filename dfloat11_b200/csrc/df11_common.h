@@ -206,7 +206,7 @@ DF11_HD uint32_t df11_peek(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t pos)
 //   uint32_t  M::cnt(i)        count-table entry i
 //   Df11Entry M::dec(i)        decode-table entry i
 //   uint32_t  M::lut(i)        byte i of the `luts` tensor (for the escape walk)
-//   void      M::put8 / M::put32     stores into the staging area (see df11_decode_window)
+//   void      M::put8(addr, v)       stage byte addr = v & 0xFF
 //
 // df11_walk_m is the exact per-symbol rule of the reference (decode.cu:105-116) applied
 // to the 32 bits `x` (MSB first): row 0 is indexed by the first byte, an entry >= 240
@@ -270,41 +270,37 @@ DF11_HD uint32_t df11_count_window(const M &m, int n_luts, uint32_t w0, uint32_t
 }
 
 // Decoding pass: writes the window's exponents to stage bytes [o, end).  Terminates after at
-// most end - o probes whatever the data is, and writes nothing outside.
-//
-// The exponents of a probe (up to four, packed in one word) are collected in a 64-bit buffer and
-// leave it one aligned 32-bit word at a time; only the bytes a window shares a word with its
-// neighbours -- below `o` in its first word, from `end` on in its last -- are written one by
-// one.  Extra policy members:
+// most end - o probes whatever the data is, and writes nothing outside.  Extra policy member:
 //   void M::put8(addr, v)    stage byte `addr` = v & 0xFF
-//   void M::put32(addr, w)   stage bytes [addr, addr + 4) = w, lowest byte first (addr % 4 == 0)
+// (Collecting the exponents in a 64-bit buffer and storing whole aligned words, single bytes only
+// at a window's two ends, was measured: a tenth slower -- the byte stores' bank conflicts cost
+// less than the extra shifts.)
 template <int K, class M>
 DF11_HD void df11_decode_window(const M &m, int n_luts, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t gap,
                                 uint32_t o, uint32_t end, int *bad)
 {
     uint32_t acc = gap | (o << 8);  // pos | slot << 8
     const uint32_t end_acc = end << 8;
-    uint32_t waddr = o & ~3u;       // stage address of the word being filled
-    uint32_t head = o & 3u;         // bytes of the first word that belong to the window before this one
-    uint32_t fill = head * 8u;      // bits of (hi:lo) in use; always waddr * 8 + fill == slot * 8
-    uint32_t lo = 0, hi = 0;
     for (;;) {
+        // at least four slots left: store all four bytes of an entry; the ones past its
+        // symbol count are rewritten by this thread's next probe
+        while (acc + (3u << 8) < end_acc) {
+            const Df11Entry e = m.dec(df11_peek(w0, w1, w2, acc) >> (32 - K));
+            const uint32_t slot = acc >> 8;
+            m.put8(slot, e.syms);
+            m.put8(slot + 1u, e.syms >> 8);
+            m.put8(slot + 2u, e.syms >> 16);
+            m.put8(slot + 3u, e.syms >> 24);
+            acc += e.meta;
+        }
+        // fewer than four left: bytes past `end` belong to the next window
         while (acc < end_acc) {
             const Df11Entry e = m.dec(df11_peek(w0, w1, w2, acc) >> (32 - K));
-            // (hi:lo) |= symbols << fill; an escape entry has no symbols and a count of 0
-            lo |= e.syms << (fill & 31u);
-            hi |= df11_funnel_l(e.syms, 0u, fill);
-            fill += (e.meta >> 5) & 0x38u;
+            const uint32_t slot = acc >> 8, rem = end - slot;
+            m.put8(slot, e.syms);
+            if (rem > 1u) m.put8(slot + 1u, e.syms >> 8);
+            if (rem > 2u) m.put8(slot + 2u, e.syms >> 16);
             acc += e.meta;
-            if (fill >= 32u && waddr + 4u <= end) {  // a whole word of this window's bytes
-                if (head) {
-                    for (uint32_t k = head; k < 4u; ++k) m.put8(waddr + k, lo >> (8u * k));
-                    head = 0;
-                } else {
-                    m.put32(waddr, lo);
-                }
-                lo = hi, hi = 0, fill -= 32u, waddr += 4u;
-            }
         }
         if (!(acc & DF11_DEC_ESCAPE))
             break;
@@ -312,30 +308,8 @@ DF11_HD void df11_decode_window(const M &m, int n_luts, uint32_t w0, uint32_t w1
         acc -= DF11_DEC_ESCAPE;
         uint32_t len;
         const uint32_t s = df11_walk_m(m, n_luts, df11_peek(w0, w1, w2, acc), &len, bad);
-        if (acc < end_acc) {
-            lo |= s << (fill & 31u);
-            hi |= df11_funnel_l(s, 0u, fill);
-            fill += 8u;
-            if (fill >= 32u && waddr + 4u <= end) {
-                if (head) {
-                    for (uint32_t k = head; k < 4u; ++k) m.put8(waddr + k, lo >> (8u * k));
-                    head = 0;
-                } else {
-                    m.put32(waddr, lo);
-                }
-                lo = hi, hi = 0, fill -= 32u, waddr += 4u;
-            }
-        }
+        if (acc < end_acc) m.put8(acc >> 8, s);
         acc += len + 256u;
-    }
-    // what is left (fewer than eight bytes): the window's last bytes, and symbols the last probe
-    // decoded beyond `end`, which belong to the next window and are dropped
-#ifdef __CUDA_ARCH__
-#pragma unroll
-#endif
-    for (uint32_t k = 0; k < 7u; ++k) {
-        const uint32_t addr = waddr + k;
-        if (k >= head && 8u * k < fill && addr < end) m.put8(addr, k < 4u ? lo >> (8u * k) : hi >> (8u * (k - 4u)));
     }
 }
 

@@ -213,7 +213,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_
 }
 
 // Memory policy of the window routines (df11_common.h) for the kernels: every table probe is
-// one ld.shared, staged exponents leave as whole st.shared.u32 words (single bytes at a window's ends).
+// one ld.shared, every staged exponent one st.shared.u8.
 struct SmemPolicy {
     uint32_t dec_addr, cnt_addr, stage_addr, luts_addr;
     __device__ __forceinline__ uint32_t cnt(uint32_t i) const { return lds32(cnt_addr + i * 4u); }
@@ -227,10 +227,6 @@ struct SmemPolicy {
     }
     __device__ __forceinline__ uint32_t lut(uint32_t i) const { return lds8(luts_addr + i); }
     __device__ __forceinline__ void put8(uint32_t addr, uint32_t v) const { sts8<0>(stage_addr + addr, v); }
-    __device__ __forceinline__ void put32(uint32_t addr, uint32_t w) const
-    {
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(stage_addr + addr), "r"(w) : "memory");
-    }
 };
 
 // Window words read straight from global memory, for blocks at the end of the stream (bytes

@@ -223,8 +223,11 @@ class _OffloadStager:
                 self.stream.wait_event(slot["free"])
             for name, host in module.offloaded_tensors.items():
                 buf = slot["buf"].get(name)
-                if buf is None or buf.numel() < host.numel():
-                    # grown on the compute stream's allocator view; sized once per run in practice
+                if buf is None or buf.numel() < host.numel() or buf.numel() > host.numel() + host.numel() // 4:
+                    # sized for the unit it holds: a slot that took a vocabulary-sized unit gives that
+                    # memory back when a transformer block follows (units of one size reuse the buffer)
+                    slot["buf"].pop(name, None)
+                    buf = None
                     buf = torch.empty(host.numel(), dtype=torch.uint8, device=self.device)
                     buf.record_stream(compute)
                     slot["buf"][name] = buf

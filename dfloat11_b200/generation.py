@@ -9,7 +9,9 @@ kernel, so a replay decompresses (or, with ``DF11_FUSED_GEMV=1``, multiplies str
 compressed weights) exactly as an eager step would.
 
 Works for any ``transformers`` causal LM whose forward accepts ``past_key_values`` /
-``cache_position`` with a ``StaticCache`` -- compressed or not.  Batch size 1.
+``cache_position`` with a ``StaticCache`` -- compressed or not, whole or tensor-parallel (every
+rank runs the same loop; the collectives of the partitioned mode are captured with the rest).
+Prompts of one batch have the same length; the graph is captured per batch size.
 """
 from __future__ import annotations
 
@@ -38,32 +40,36 @@ class GraphedGreedyDecoder:
 
     # -- one single-token step on static tensors -------------------------------------------------
     def _step(self):
-        self._produced.index_copy_(0, self._count, self._tok.view(-1))
+        self._produced.index_copy_(0, self._count, self._tok.view(1, -1))
         logits = self.model(input_ids=self._tok, past_key_values=self._cache, cache_position=self._pos,
                             use_cache=True).logits
         self._tok.copy_(logits[:, -1:].argmax(-1))
         self._pos.add_(1)
         self._count.add_(1)
 
-    def _prepare(self):
+    def _prepare(self, batch: int):
         from transformers import StaticCache
         dev = self.device
-        if self._cache is None:
+        if self._cache is None or self._tok.shape[0] != batch:
+            self._graph = None                            # static tensors change: the old capture is void
             self._cache = StaticCache(config=self.model.config, max_cache_len=self.max_cache_len)
-            self._tok = torch.zeros(1, 1, dtype=torch.int64, device=dev)
+            self._tok = torch.zeros(batch, 1, dtype=torch.int64, device=dev)
             self._pos = torch.zeros(1, dtype=torch.int64, device=dev)
             self._count = torch.zeros(1, dtype=torch.int64, device=dev)
-            self._produced = torch.zeros(self.max_cache_len + 8, dtype=torch.int64, device=dev)
+            self._produced = torch.zeros(self.max_cache_len + 8, batch, dtype=torch.int64, device=dev)
         else:
             self._cache.reset()
 
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int, eos_token_id: Optional[int] = None,
                  eos_check_every: int = 32) -> torch.Tensor:
-        """Prompt ``[1, n]`` -> ``[1, n + new]`` ids, greedy.  Stops early at ``eos_token_id`` (looked
-        for every ``eos_check_every`` tokens, the only host synchronisation in the loop)."""
-        if input_ids.dim() != 2 or input_ids.shape[0] != 1:
-            raise ValueError("one sequence at a time: input_ids must be [1, n]")
+        """Prompts ``[b, n]`` -> ``[b, n + new]`` ids, greedy.  With one sequence, stops early at
+        ``eos_token_id`` (looked for every ``eos_check_every`` tokens, the only host synchronisation
+        in the loop)."""
+        if input_ids.dim() != 2 or input_ids.shape[0] < 1:
+            raise ValueError("input_ids must be [batch, n]")
+        if eos_token_id is not None and input_ids.shape[0] != 1:
+            raise ValueError("early stopping at an end-of-sequence id is for one sequence at a time")
         n_prompt = input_ids.shape[1]
         if n_prompt + max_new_tokens > self.max_cache_len:
             raise ValueError(f"{n_prompt} + {max_new_tokens} tokens exceed max_cache_len = {self.max_cache_len}")
@@ -71,7 +77,7 @@ class GraphedGreedyDecoder:
             return input_ids
         dev = self.device
         input_ids = input_ids.to(dev)
-        self._prepare()
+        self._prepare(input_ids.shape[0])
         # only the last position's logits are needed: models whose forward can skip the others
         # (`logits_to_keep`) do not multiply the whole prompt with the output head
         extra = {"logits_to_keep": 1} if self._keeps_logits else {}
@@ -104,16 +110,16 @@ class GraphedGreedyDecoder:
             self._graph.replay()
             done += 1
             if eos_token_id is not None and done % eos_check_every == 0:
-                if bool((self._produced[:done] == eos_token_id).any()):
+                if bool((self._produced[:done, 0] == eos_token_id).any()):
                     break
         # the token of the last step is still in `tok`
-        self._produced.index_copy_(0, self._count, self._tok.view(-1))
+        self._produced.index_copy_(0, self._count, self._tok.view(1, -1))
         new = self._produced[:done + 1]
         if eos_token_id is not None:
-            hit = (new == eos_token_id).nonzero()
+            hit = (new[:, 0] == eos_token_id).nonzero()
             if hit.numel():
                 new = new[:int(hit[0]) + 1]
-        return torch.cat([input_ids, new.view(1, -1)], dim=1)
+        return torch.cat([input_ids, new.t()], dim=1)
 
     def reset(self) -> None:
         """Forget the captured graph (after changing the model or the DF11 environment switches)."""

@@ -26,10 +26,6 @@ struct HostMem {
     Df11Entry dec(uint32_t i) const { return dec_t[i]; }
     uint32_t lut(uint32_t i) const { return luts[i]; }
     void put8(uint32_t addr, uint32_t v) const { stage[addr] = (uint8_t)v; }
-    void put32(uint32_t addr, uint32_t w) const
-    {
-        for (int k = 0; k < 4; ++k) stage[addr + k] = (uint8_t)(w >> (8 * k));
-    }
     // seek-point decoder
     const uint8_t *codes = nullptr;
     int64_t n_bytes = 0;

@@ -27,7 +27,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REFERENCE = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REFERENCE = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(ROOT), "reference")   # beside the repository
 
 sys.path.insert(0, os.path.join(ROOT, "oracle", "standin"))
 spec = importlib.util.spec_from_file_location(

@@ -131,7 +131,8 @@ def test_llama_block_small_vs_oracle_and_reference():
 
 
 def test_llama_block_full_size_round_trip():
-    """BASELINE config 1: one Llama-3.1-8B block, 218 103 808 elements, N(0, 0.02), seed 0."""
+    """One whole Llama-3.1-8B block (the seven matrices of hidden 4096 / 8 kv heads / intermediate 14336
+    as one unit: 218 103 808 elements, N(0, 0.02), seed 0)."""
     weights = _scaled_llama_block(4096, 14336, 1024, seed=0)
     t, d, widest = _unit_from_weights(weights)
     want = torch.cat([w.reshape(-1) for w in weights]).to(DEV)

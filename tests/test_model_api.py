@@ -330,9 +330,14 @@ def test_logits_identical_to_bf16_model(saved, mode, monkeypatch):
 @pytest.mark.parametrize("offload", [False, True])
 def test_from_pretrained_without_a_skeleton_gives_bf16_logits(saved, offload):
     """Default branch of ``from_pretrained`` (no ``bfloat16_model``) end to end on the GPU."""
+    from transformers import AutoConfig, AutoModelForCausalLM
     path, reference = saved
     model = df11.DFloat11Model.from_pretrained(path, device="cuda:0", cpu_offload=offload)
-    ref = copy.deepcopy(reference).to("cuda:0")
+    # the uncompressed model built the same way (from the saved config, in BF16 from the start: its
+    # rotary tables stay fp32, where `tiny_llama()` rounds them to BF16 with the rest of the model)
+    ref = AutoModelForCausalLM.from_config(AutoConfig.from_pretrained(path), dtype=torch.bfloat16)
+    ref.load_state_dict(reference.state_dict())
+    ref = ref.eval().to("cuda:0")
     ids = torch.randint(0, 1024, (2, 21), generator=torch.Generator().manual_seed(11)).to("cuda:0")
     with torch.no_grad():
         for _ in range(2):
@@ -574,6 +579,12 @@ def test_graphed_greedy_decoder(saved):
         assert torch.equal(got, want[:, :9 + first + 1])
     with pytest.raises(ValueError):
         decoder.generate(ids, 100)
+    # a batch of prompts: the DF11 model and the BF16 model produce the same ids (a new capture per batch size)
+    batch = torch.randint(0, 1024, (3, 9), generator=torch.Generator().manual_seed(10)).to("cuda:0")
+    got = [df11.GraphedGreedyDecoder(m, max_cache_len=64).generate(batch, 12) for m in (model, ref)]
+    assert got[0].shape == (3, 21) and torch.equal(got[0], got[1]) and torch.equal(got[0][:, :9], batch)
+    with pytest.raises(ValueError):
+        decoder.generate(batch, 4, eos_token_id=1)
 
 
 from bench import FLUX_PATTERNS, FluxShapedDiT          # the benchmark's FLUX-shaped stack, here at toy size
