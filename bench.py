@@ -45,6 +45,7 @@ QWEN3_8B = dict(name="qwen3-8b-shape", layers=36, hidden=4096, kv=1024, inter=12
 LLAMA_8B = dict(name="llama3.1-8b-shape", layers=32, hidden=4096, kv=1024, inter=14336, vocab=128256)
 SMALL = dict(name="small-smoke", layers=2, hidden=1024, kv=256, inter=3072, vocab=8192)
 ONE_BLOCK = dict(name="one-llama-block", layers=1, hidden=4096, kv=1024, inter=14336, vocab=0)
+ONE_QWEN_BLOCK = dict(name="one-qwen3-block", layers=1, hidden=4096, kv=1024, inter=12288, vocab=0)
 # Llama-3.1-405B shapes, tensor-parallel over the ranks of the job: every rank holds 1/T of each
 # block's seven matrices as one unit and decodes only that; two activation all-reduces per layer.
 LLAMA_405B_TP = dict(name="llama3.1-405b-shape-tp", layers=126, hidden=16384, kv=1024, inter=53248, vocab=0, tp=True)
@@ -54,7 +55,7 @@ LLAMA_405B_TP = dict(name="llama3.1-405b-shape-tp", layers=126, hidden=16384, kv
 FLUX_DIT = dict(name="flux1-dev-shape", layers=57, hidden=3072, kv=3072, inter=12288, vocab=0,
                 unit_sizes=[2 * 3072 * 18432 + 8 * 3072 * 3072 + 4 * 3072 * 12288] * 19
                 + [3072 * 9216 + 3072 * 12288 + 15360 * 3072 + 3 * 3072 * 3072] * 38)
-WORKLOADS = {"flux-dit": FLUX_DIT, "qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "small": SMALL, "block": ONE_BLOCK,
+WORKLOADS = {"flux-dit": FLUX_DIT, "qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "small": SMALL, "block": ONE_BLOCK, "qwen3-block": ONE_QWEN_BLOCK,
              "llama-405b-tp": LLAMA_405B_TP}
 
 
@@ -1017,6 +1018,21 @@ def tp_block(args, rank, world, device):
     ms_with = timed(lambda: step(True))
     ms_without = timed(lambda: step(False))
     ms_reduce = timed(lambda: [dist.all_reduce(act) for _ in range(2 * layers)])
+    # the same step as one CUDA graph (what a generation loop replays): no host time between the launches
+    ms_graph, graph_error = None, None
+    try:
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            step(True)
+        torch.cuda.current_stream(device).wait_stream(side)
+        barrier(world, device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(True)
+        ms_graph = timed(graph.replay)
+    except Exception as exc:                                # report, do not hide
+        graph_error = f"{type(exc).__name__}: {exc}"[:200]
     ok = int(scratch.view(torch.int16).to(torch.int64).sum().item()) == first["checksum"] and status.item() == 0
     total = all_sum(sum(algorithmic_bytes(u) for u in units), world, device)
     peak, _ = measured_hbm_peak()
@@ -1026,6 +1042,10 @@ def tp_block(args, rank, world, device):
         "ms_per_step": round(ms_with, 3), "aggregate_GBps": round(total / ms_with / 1e6, 1),
         "per_gpu_GBps": round(total / ms_with / 1e6 / world, 1),
         "per_gpu_frac_of_measured_peak": round(total / ms_with / 1e6 / world / peak, 4),
+        "cuda_graph": ({"ms_per_step": round(ms_graph, 3), "per_gpu_GBps": round(total / ms_graph / 1e6 / world, 1),
+                        "per_gpu_frac_of_measured_peak": round(total / ms_graph / 1e6 / world / peak, 4),
+                        "us_per_all_reduce_in_step": round((ms_graph - ms_without) * 1e3 / (2 * layers), 2)}
+                       if ms_graph else {"error": graph_error}),
         "decode_only_ms_per_step": round(ms_without, 3),
         "us_per_all_reduce_back_to_back": round(ms_reduce * 1e3 / (2 * layers), 2),
         "us_per_all_reduce_in_step": round((ms_with - ms_without) * 1e3 / (2 * layers), 2),
