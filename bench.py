@@ -385,8 +385,6 @@ def main():
     ap.add_argument("--slab-pipeline", action="store_true",
                     help="only: one block's batch-1 products with the weights decompressed slab by slab right "
                          "before each product (L2-resident) against decode-the-whole-block")
-    ap.add_argument("--eager", action="store_true",
-                    help="with --slab-pipeline: one untimed pass of each variant without CUDA graphs, for a profiler")
     ap.add_argument("--layers", type=int, default=0,
                     help="with --generation on the partitioned workload: transformer layers to build (0 = as many as fit)")
     ap.add_argument("--new-tokens", type=int, default=512)
@@ -1310,20 +1308,6 @@ def run_slab_pipeline(args, cfg):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / args.steps / n_blocks
 
-    if args.eager:
-        # for a profiler: block 1's products once the plain way, once in 48 MB slabs, launched one by
-        # one (no graph, no timing); blocks 2 and 3 in between push block 1's leftovers out of L2
-        for fn in (whole, slabbed(48)[0]):
-            fn(1)
-            fn(2)
-            fn(3)
-            torch.cuda.synchronize()
-            torch.cuda.nvtx.range_push("measured")
-            fn(1)
-            torch.cuda.synchronize()
-            torch.cuda.nvtx.range_pop()
-        print(json.dumps({"eager": True, "order": ["decode whole + 7 products", "48 MB slabs: 8 decodes + 10 products"]}))
-        return
     bf16_block(0)
     want = [o.clone() for o in outs]
     result = {"metric": "batch1_block_products_ms", "unit": "ms per block", "workload": cfg["name"],

@@ -206,6 +206,7 @@ DF11_HD uint32_t df11_peek(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t pos)
 //   uint32_t  M::cnt(i)        count-table entry i
 //   Df11Entry M::dec(i)        decode-table entry i
 //   uint32_t  M::lut(i)        byte i of the `luts` tensor (for the escape walk)
+//   void      M::put8(addr, v)       stage byte addr = v & 0xFF
 //
 // df11_walk_m is the exact per-symbol rule of the reference (decode.cu:105-116) applied
 // to the 32 bits `x` (MSB first): row 0 is indexed by the first byte, an entry >= 240
@@ -268,37 +269,48 @@ DF11_HD uint32_t df11_count_window(const M &m, int n_luts, uint32_t w0, uint32_t
     return acc >> 8;
 }
 
-// Counting pass that also notes where the window's 16th, 32nd and 48th code start: bit offsets
-// inside the window (0..63), six bits each, packed from bit 0 up (a window of 64 bits holds at
-// most 64 codes).  With the window's gap (the start of its code 0) that gives a place to start
-// decoding at most fifteen codes before any code of the window.
+// Decoding pass: writes the window's exponents to stage bytes [o, end).  Terminates after at
+// most end - o probes whatever the data is, and writes nothing outside.  Extra policy member:
+//   void M::put8(addr, v)    stage byte `addr` = v & 0xFF
+// (Collecting the exponents in a 64-bit buffer and storing whole aligned words, single bytes only
+// at a window's two ends, was measured: a tenth slower -- the byte stores' bank conflicts cost
+// less than the extra shifts.)
 template <int K, class M>
-DF11_HD uint32_t df11_count_window_marks(const M &m, int n_luts, uint32_t w0, uint32_t w1, uint32_t w2,
-                                         uint32_t gap, uint32_t *marks, int *bad)
+DF11_HD void df11_decode_window(const M &m, int n_luts, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t gap,
+                                uint32_t o, uint32_t end, int *bad)
 {
-    uint32_t pos = gap, count = 0, mk = 0;
-    while (pos < 64u) {
-        const uint32_t x = df11_peek(w0, w1, w2, pos);
-        const uint32_t c = m.cnt(x >> (32 - K));
-        uint32_t n, nbits, starts;
-        if (c == DF11_CNT_ESCAPE) {
-            df11_walk_m(m, n_luts, x, &nbits, bad);
-            n = 1u;
-            starts = 0u;
-        } else {
-            const uint32_t lim = 64u - pos;
-            n = lim >= 15u ? ((c >> 8) & 7u) : df11_owned_syms(c, lim);
-            nbits = c & 0xFFu;
-            starts = c >> 16;
+    uint32_t acc = gap | (o << 8);  // pos | slot << 8
+    const uint32_t end_acc = end << 8;
+    for (;;) {
+        // at least four slots left: store all four bytes of an entry; the ones past its
+        // symbol count are rewritten by this thread's next probe
+        while (acc + (3u << 8) < end_acc) {
+            const Df11Entry e = m.dec(df11_peek(w0, w1, w2, acc) >> (32 - K));
+            const uint32_t slot = acc >> 8;
+            m.put8(slot, e.syms);
+            m.put8(slot + 1u, e.syms >> 8);
+            m.put8(slot + 2u, e.syms >> 16);
+            m.put8(slot + 3u, e.syms >> 24);
+            acc += e.meta;
         }
-        const uint32_t k = (0u - count) & 15u;  // codes to go until the count is a multiple of 16
-        if (k < n && count + k != 0u)
-            mk |= (pos + ((starts >> (4u * k)) & 15u)) << (6u * (((count + k) >> 4) - 1u));
-        count += n;
-        pos += nbits;
+        // fewer than four left: bytes past `end` belong to the next window
+        while (acc < end_acc) {
+            const Df11Entry e = m.dec(df11_peek(w0, w1, w2, acc) >> (32 - K));
+            const uint32_t slot = acc >> 8, rem = end - slot;
+            m.put8(slot, e.syms);
+            if (rem > 1u) m.put8(slot + 1u, e.syms >> 8);
+            if (rem > 2u) m.put8(slot + 2u, e.syms >> 16);
+            acc += e.meta;
+        }
+        if (!(acc & DF11_DEC_ESCAPE))
+            break;
+        // an escape entry ended the loop: decode that one symbol with the full walk
+        acc -= DF11_DEC_ESCAPE;
+        uint32_t len;
+        const uint32_t s = df11_walk_m(m, n_luts, df11_peek(w0, w1, w2, acc), &len, bad);
+        if (acc < end_acc) m.put8(acc >> 8, s);
+        acc += len + 256u;
     }
-    *marks = mk;
-    return count;
 }
 
 // ---------------------------------------------------------------------------
@@ -453,14 +465,8 @@ DF11_HD constexpr uint32_t df11_fast_meta(uint32_t meta)
 // group of 16 codes rarely needs more than the 64 positions that gives, so the reload inside
 // the loop is the exception, not the rule.
 template <int K, int EPT, class M>
-DF11_HD void df11_decode_group(const M &m, int n_luts, uint32_t word_index, uint32_t bit, bool active, int *bad,
-                               uint32_t skip = 0)
+DF11_HD void df11_decode_group(const M &m, int n_luts, uint32_t word_index, uint32_t bit, bool active, int *bad)
 {
-    // `skip` (0..15): codes to decode and drop before the group's first one -- for a caller that
-    // only knows a place up to fifteen codes ahead of where it wants to start.  Dropping is free:
-    // the codes pass through the shift register like any others and are not among the sixteen
-    // taken at the end; the count of codes done simply starts at 16 - skip, so that the first run
-    // of the loop below ends when they are through.
     if (!active) return;
     uint32_t w0, w1, w2;
     auto load = [&]() {
@@ -476,9 +482,9 @@ DF11_HD void df11_decode_group(const M &m, int n_luts, uint32_t word_index, uint
         w2 = len ? w2 << len : w2;
     };
     Df11ExpShift X = {0, 0, 0, 0, 0};
-    uint32_t acc = skip ? (16u - skip) << 19 : 0u;
-    for (int part = skip ? -1 : 0; part < EPT / 16; ++part) {
-        if (part > 0 || (part == 0 && skip)) {  // go on where the previous run stopped; codes decoded beyond it are at the top of X
+    uint32_t acc = 0;
+    for (int part = 0; part < EPT / 16; ++part) {
+        if (part > 0) {  // go on where the previous sixteen stopped; codes decoded beyond them are at the top of X
             const uint32_t at = bit + (acc & 0x7Fu);
             word_index += at >> 5;
             bit = at & 31u;
@@ -493,7 +499,7 @@ DF11_HD void df11_decode_group(const M &m, int n_luts, uint32_t word_index, uint
                 shift(meta & 31u);
                 acc += meta;
             }
-            if ((acc & (DF11_FAST_ESCAPE | 64u)) == 0u) break;  // the run is done, nothing special
+            if ((acc & (DF11_FAST_ESCAPE | 64u)) == 0u) break;  // 16 codes done, nothing special
             if (acc & DF11_FAST_ESCAPE) {  // the table could not resolve this code from K bits: full walk
                 acc -= DF11_FAST_ESCAPE;
                 uint32_t len;
@@ -506,7 +512,7 @@ DF11_HD void df11_decode_group(const M &m, int n_luts, uint32_t word_index, uint
                     w0 = w1, w1 = w2, w2 = 0;
                 }
             }
-            if (acc & DF11_FAST_DONE) break;  // the run is done (the position may be past 63)
+            if (acc & DF11_FAST_DONE) break;  // 16 codes done (the position may be past 63)
             if (acc & 64u) {                  // position 64..127: reload the window where the position has got to
                 const uint32_t at = bit + (acc & 0x7Fu);
                 word_index += at >> 5;
@@ -515,7 +521,6 @@ DF11_HD void df11_decode_group(const M &m, int n_luts, uint32_t word_index, uint
                 acc &= ~0xFFu;
             }
         }
-        if (part < 0) continue;  // the dropped codes: nothing to hand over
         uint32_t e0, e1, e2, e3;
         X.take(acc, &e0, &e1, &e2, &e3);
         m.flush(4u * part + 0u, e0);

@@ -101,6 +101,7 @@ struct Params {
     uint32_t chunk_count;      // range decode: chunks to produce; 0 = the whole unit
     int n_luts;
     int ept;          // elements per seek point (16 or 32)
+    int stage_bytes;  // shared staging area (and sign/mantissa tile), multiple of 16
     int codes_aligned;  // bit 0: codes 16-byte aligned, bit 1: gaps 16-byte aligned (bulk copies allowed),
                         // bit 2: codes 4-byte aligned (word loads allowed)
     int sm_aligned;     // bit 0: sign_mantissa 16-byte aligned (bulk copies / 16-byte loads allowed), bit 1: 32-byte
@@ -212,11 +213,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_
 }
 
 // Memory policy of the window routines (df11_common.h) for the kernels: every table probe is
-// one ld.shared.
-struct CountPolicy {
-    uint32_t cnt_addr, luts_addr;
+// one ld.shared, every staged exponent one st.shared.u8.
+struct SmemPolicy {
+    uint32_t dec_addr, cnt_addr, stage_addr, luts_addr;
     __device__ __forceinline__ uint32_t cnt(uint32_t i) const { return lds32(cnt_addr + i * 4u); }
+    __device__ __forceinline__ Df11Entry dec(uint32_t i) const
+    {
+        const uint2 v = lds64(dec_addr + i * 8u);
+        Df11Entry e;
+        e.meta = v.x;
+        e.syms = v.y;
+        return e;
+    }
     __device__ __forceinline__ uint32_t lut(uint32_t i) const { return lds8(luts_addr + i); }
+    __device__ __forceinline__ void put8(uint32_t addr, uint32_t v) const { sts8<0>(stage_addr + addr, v); }
 };
 
 // Window words read straight from global memory, for blocks at the end of the stream (bytes
@@ -297,8 +307,10 @@ __global__ void __launch_bounds__(kThreads, 3) df11_sync_kernel(const Params p)
     uint8_t *luts_s = smem + (4u << K);
     uint8_t *agree = luts_s + p.n_luts * 256;
     uint32_t *wsum = reinterpret_cast<uint32_t *>(agree + 256);
-    CountPolicy mem;
+    SmemPolicy mem;
+    mem.dec_addr = 0;
     mem.cnt_addr = smem_addr;
+    mem.stage_addr = 0;
     mem.luts_addr = smem_addr + (4u << K);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -939,59 +951,44 @@ __global__ void __launch_bounds__(256) df11_gemv_finish_kernel(const GemvArgs g,
 }
 
 // ---------------------------------------------------------------------------------------
-// Self-contained decode kernel (behind df11_decode): needs nothing but the six DF11 tensors.
-//
-// A CTA of 512 threads takes one format block (4096 stream bytes = 512 windows) per pass.
-//   1. Counting pass, one window per thread: how many codes start in the window, and where its
-//      16th, 32nd and 48th code start (df11_count_window_marks).
-//   2. Block scan of the counts: the index, inside the block, of each window's first element.
-//   3. The block's elements are produced in groups of sixteen that are aligned to sixteen in the
-//      OUTPUT (so that a group is one 16-byte load of sign/mantissa bytes and one 32-byte store).
-//      A group is decoded by the thread in whose window its first code starts: the thread starts
-//      at the nearest place it knows (the window's gap or one of its marks), drops the up to
-//      fifteen codes that come before the group, and decodes sixteen -- the same probe loop and
-//      exponent shift register as the fast decoder, reading the stream from the CTA's shared copy
-//      of the block.  Nothing is staged in shared memory and there is no separate merge phase.
-//   4. The elements of the block before its first aligned group (at most fifteen; their group
-//      started in the previous block) are decoded by thread 0; a last group that the block only
-//      partly fills is written element by element.
-//
-// Every global read of the stream is a TMA bulk copy (cp.async.bulk + mbarrier, no multicast,
-// bounded waits): the next block's 4112 stream bytes and 320 gap bytes arrive in a double buffer
-// while the current block is decoded.
+// Self-contained decode kernel (behind df11_decode): count pass + scan + decode pass per block.
 //
 // Shared memory (byte offsets from the dynamic shared base):
-//   [0, 8<<KD)              decode table, fast-decoder entry format
-//   [.., +4<<KC)            count table
+//   [0, 8<<K)               decode table
+//   [.., +4<<K)             count table
 //   2 input buffers         each: 4112 stream bytes, then the block's 320 gap bytes
-//   2 mbarriers, luts, agree, wsum
+//   stage                   exponent bytes of the current block
+//   tile                    sign/mantissa bytes of the current block
+//   3 mbarriers, luts, agree, wsum
 // ---------------------------------------------------------------------------------------
-template <int KD, int KC>
+template <int K>
 struct Layout {
     static constexpr uint32_t dec = 0;
-    static constexpr uint32_t cnt = 8u << KD;
-    static constexpr uint32_t in0 = cnt + (4u << KC);
-    static constexpr uint32_t bars = in0 + 2u * kInBufBytes;
-    static constexpr uint32_t luts = bars + 32;
+    static constexpr uint32_t cnt = 8u << K;
+    static constexpr uint32_t in0 = cnt + (4u << K);
+    static constexpr uint32_t stage = in0 + 2u * kInBufBytes;
 };
 
-template <int KD, int KC>
-__global__ void __launch_bounds__(kThreads, 2) df11_decode_kernel(const Params p)
+template <int K>
+__global__ void __launch_bounds__(kThreads, 3) df11_decode_kernel(const Params p)
 {
     extern __shared__ __align__(16) uint8_t smem[];
-    using L = Layout<KD, KC>;
+    using L = Layout<K>;
     const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
-    uint8_t *luts_s = smem + L::luts;
+    const uint32_t tile_off = L::stage + p.stage_bytes;
+    const uint32_t bars_off = tile_off + p.stage_bytes;
+    uint8_t *luts_s = smem + bars_off + 32;
     uint8_t *agree = luts_s + p.n_luts * 256;
     uint32_t *wsum = reinterpret_cast<uint32_t *>(agree + 256);
 
-    CountPolicy cmem;
-    cmem.cnt_addr = smem_addr + L::cnt;
-    cmem.luts_addr = smem_addr + L::luts;
-    FastTables tab;
-    tab.dec_addr = smem_addr + L::dec;
-    tab.luts_addr = smem_addr + L::luts;
-    const uint32_t bar_in = smem_addr + L::bars;  // two barriers, 8 bytes apart
+    SmemPolicy mem;
+    mem.dec_addr = smem_addr + L::dec;
+    mem.cnt_addr = smem_addr + L::cnt;
+    mem.stage_addr = smem_addr + L::stage;
+    mem.luts_addr = smem_addr + bars_off + 32;
+    const uint32_t tile_addr = smem_addr + tile_off;
+    const uint32_t bar_in = smem_addr + bars_off;       // two barriers, 8 bytes apart
+    const uint32_t bar_sm = smem_addr + bars_off + 16;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     int bad = 0;
@@ -1000,29 +997,13 @@ __global__ void __launch_bounds__(kThreads, 2) df11_decode_kernel(const Params p
     if (tid == 0) {
         mbar_init(bar_in, 1);
         mbar_init(bar_in + 8, 1);
+        mbar_init(bar_sm, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = tid; i < p.n_luts * 256; i += kThreads) luts_s[i] = __ldg(p.luts + i);
     __syncthreads();
-    for (int task = tid; task < 255; task += kThreads) {
-        int u = 1;
-        while (task >= df11_agree_offset(u + 1) && u < 8) ++u;
-        agree[task] = df11_agree_flag(luts_s, u, task - df11_agree_offset(u));
-    }
-    __syncthreads();
-    for (int v = tid; v < (1 << KD); v += kThreads) {
-        Df11Entry e;
-        uint32_t c;
-        df11_build_entry(luts_s, p.n_luts, agree, (uint32_t)v, KD, &e, &c);
-        e.meta = fast_meta(e.meta);
-        reinterpret_cast<Df11Entry *>(smem + L::dec)[v] = e;
-    }
-    for (int v = tid; v < (1 << KC); v += kThreads) {
-        Df11Entry e;
-        uint32_t c;
-        df11_build_entry(luts_s, p.n_luts, agree, (uint32_t)v, KC, &e, &c);
-        reinterpret_cast<uint32_t *>(smem + L::cnt)[v] = c;
-    }
+    build_tables_smem(p, luts_s, agree, reinterpret_cast<Df11Entry *>(smem + L::dec),
+                      reinterpret_cast<uint32_t *>(smem + L::cnt), K, tid);
     __syncthreads();
 
     // A block's stream bytes come by bulk copy when all 4112 of them exist and are aligned.
@@ -1047,9 +1028,7 @@ __global__ void __launch_bounds__(kThreads, 2) df11_decode_kernel(const Params p
             bulk_g2s(dst + kCodesBufBytes, p.gaps + b * DF11_GAP_BYTES_PER_BLOCK, DF11_GAP_BYTES_PER_BLOCK, bar);
     };
     const uint64_t wait_ns = p.wait_ns ? p.wait_ns : kWaitNs;
-    uint32_t n_in[2] = {0, 0};  // copies announced per barrier so far (uniform over the CTA)
-    const bool vec = (p.sm_aligned & 1) && (p.out_aligned & 1);
-    const bool wide = (p.out_aligned & 2) != 0;
+    uint32_t n_in[2] = {0, 0}, n_sm = 0;  // copies announced per barrier so far (uniform over the CTA)
 
     if ((int64_t)blockIdx.x < p.n_blocks) {
         if (tid == 0) issue_inputs(blockIdx.x, 0);
@@ -1081,18 +1060,41 @@ __global__ void __launch_bounds__(kThreads, 2) df11_decode_kernel(const Params p
             c = c < 0 ? 0 : p.n_elements - base;
             if (c < 0) c = 0;
         }
-        if (c > DF11_MAX_BLOCK_ELEMS + 64) {  // more elements than 4096 bytes can start
-            bad |= DF11_STATUS_BAD_POSITIONS;
-            c = DF11_MAX_BLOCK_ELEMS + 64;
+        const uint32_t phase = (uint32_t)(base & 15);
+        if (c + phase > p.stage_bytes - 16) {
+            bad |= DF11_STATUS_TRUNCATED;
+            c = p.stage_bytes - 16 - phase;
         }
         const uint32_t block_cnt = (uint32_t)c;
-        const uint32_t q = (16u - (uint32_t)(base & 15)) & 15u;  // elements before the block's first aligned group
-        const bool in_smem = streamed(b);
+        const uint32_t last = phase + block_cnt;  // one past the last staging byte in use
+        const int64_t gbase = base - phase;       // multiple of 16
+        const uint8_t *sm_blk = p.sm + gbase;
 
-        // ---- my window: words, gap, count, marks ----------------------------------------------
+        // ---- sign/mantissa tile of this block: bulk copy, overlapped with the decode --------
+        // Whole 16-byte pieces that lie inside the tensor come by TMA; a ragged end (only at
+        // the very end of the unit) or an unaligned tensor is fetched with plain loads.
+        uint32_t tma_bytes = 0;
+        if (p.sm_aligned && block_cnt > 0) {  // then base < n_elements, so `avail` is not negative
+            const int64_t avail = (p.n_elements - gbase) & ~(int64_t)15;
+            const uint32_t want = (last + 15u) & ~15u;
+            tma_bytes = (int64_t)want <= avail ? want : (uint32_t)avail;
+        }
+        if (tid == 0) {
+            if (tma_bytes) {
+                mbar_expect_tx(bar_sm, tma_bytes);
+                bulk_g2s(tile_addr, sm_blk, tma_bytes, bar_sm);
+            } else {
+                mbar_arrive(bar_sm);
+            }
+        }
+        ++n_sm;
+        for (uint32_t i = max(tma_bytes, phase) + tid; i < last; i += kThreads)
+            smem[tile_off + i] = __ldg(sm_blk + i);
+
+        // ---- my window ------------------------------------------------------------------------
         uint32_t w0 = 0, w1 = 0, w2 = 0;
         bool live = true;
-        if (in_smem) {
+        if (streamed(b)) {
             const uint2 v = lds64(in_addr + 8u * tid);
             w0 = __byte_perm(v.x, 0, 0x0123);
             w1 = __byte_perm(v.y, 0, 0x0123);
@@ -1105,6 +1107,7 @@ __global__ void __launch_bounds__(kThreads, 2) df11_decode_kernel(const Params p
                 w0 = v.x, w1 = v.y, w2 = v.z;
             }
         }
+
         uint32_t gap;
         if (side_streamed) {
             gap = block_gap([&](uint32_t j) { return lds8(in_addr + kCodesBufBytes + j); }, tid);
@@ -1113,129 +1116,61 @@ __global__ void __launch_bounds__(kThreads, 2) df11_decode_kernel(const Params p
             gap = block_gap([&](uint32_t j) { return (uint32_t)__ldg(g + j); }, tid);
         }
         int cbad = 0;
-        uint32_t marks = 0;
-        const uint32_t cnt = df11_count_window_marks<KC>(cmem, p.n_luts, w0, w1, w2, live ? gap : 64u, &marks, &cbad);
+        const uint32_t cnt = df11_count_window<K>(mem, p.n_luts, w0, w1, w2, live ? gap : 64u, &cbad);
         if (cbad) bad |= DF11_STATUS_BAD_TABLE;
         uint32_t o = block_scan(cnt, wsum, lane, warp);
-        uint32_t end = min(o + cnt, block_cnt);
-        o = min(o, block_cnt);
+        uint32_t end = o + cnt;
 
-        // ---- groups ------------------------------------------------------------------------------
-        // Stream words of this block, by word index inside the block; a group's codes all start
-        // inside the block, so the words it needs lie in the 4112 bytes held here (an index beyond
-        // that can only come from inconsistent tensors and is clamped).
-        const int64_t block_byte = b * DF11_BLOCK_BYTES;
-        auto words_at = [&](uint32_t wi) -> uint4 {
-            if (in_smem) {
-                const uint32_t a = in_addr + 4u * min(wi, (uint32_t)(kCodesBufBytes / 4 - 4));
-                return make_uint4(lds32(a), lds32(a + 4u), lds32(a + 8u), lds32(a + 12u));
-            }
-            return stream_words_slow(p.codes, p.n_bytes, (uint32_t)(block_byte / 4) + wi);  // block_byte / 4 < 2^32
-        };
-        // Sixteen codes after dropping `skip`, starting `bitpos` bits into the block.  The dropped
-        // codes go through the shift register like the others and are simply not among the sixteen
-        // taken at the end: the count of codes done starts at 16 - skip, so the first run of the
-        // loop ends when they are through.
-        auto decode_group = [&](uint32_t bitpos, uint32_t skip, uint32_t &e0, uint32_t &e1, uint32_t &e2, uint32_t &e3) {
-            uint32_t wi = bitpos >> 5, bit = bitpos & 31u, w0g, w1g, w2g;
-            ExpShift X = {0, 0, 0, 0, 0};
-            uint32_t acc = kFastDone;
-            stream_window(words_at(wi), bit, w0g, w1g, w2g);
-            auto reload = [&]() {  // the window again, at the code the position has reached
-                const uint32_t at = bit + (acc & 0x7Fu);
-                wi += at >> 5;
-                bit = at & 31u;
-                stream_window(words_at(wi), bit, w0g, w1g, w2g);
-                acc &= ~0xFFu;
-            };
-            auto run = [&]() {  // probes until sixteen codes are counted
-                for (;;) {
-                    probe_loop<KD>(acc, X, w0g, w1g, w2g, tab.dec_addr);
-                    if (acc & kFastDone) break;
-                    if (acc & kFastEscape) {  // full walk for one symbol
-                        acc -= kFastEscape;
-                        uint32_t len;
-                        int tbad = 0;
-                        const uint32_t sym = df11_walk_m(tab, p.n_luts, w0g, &len, &tbad);
-                        if (tbad) bad |= DF11_STATUS_BAD_TABLE;
-                        X.push(sym, 8u);
-                        acc += len | (8u << 16);
-                        if (len < 32u) {
-                            w0g = __funnelshift_l(w1g, w0g, len);
-                            w1g = __funnelshift_l(w2g, w1g, len);
-                            w2g <<= len;
-                        } else {
-                            w0g = w1g, w1g = w2g, w2g = 0;
-                        }
-                        if (acc & kFastDone) break;
-                    }
-                    if (acc & 64u) reload();
-                }
-            };
-            if (skip != 0u) {
-                acc = (16u - skip) << 19;
-                run();
-                if (acc & 64u) reload();
-            }
-            acc -= kFastDone;  // codes decoded beyond the dropped ones stay counted: they are at the top of X
-            run();
-            X.take(acc, &e0, &e1, &e2, &e3);
-        };
-        // Elements [r, r + valid) of the block from sixteen decoded exponents.
-        auto emit = [&](uint32_t r, uint32_t valid, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3) {
-            const int64_t first = base + r;
-            if (valid == 16u && vec) {
-                const uint4 m = __ldg(reinterpret_cast<const uint4 *>(p.sm + first));
-                uint4 r0, r1;
-                df11_merge4(e0, m.x, &r0.x, &r0.y);
-                df11_merge4(e1, m.y, &r0.z, &r0.w);
-                df11_merge4(e2, m.z, &r1.x, &r1.y);
-                df11_merge4(e3, m.w, &r1.z, &r1.w);
-                uint4 *dst = reinterpret_cast<uint4 *>(p.out + first);
-                if (wide) {
-                    stg256(dst, r0, r1);
-                } else {
-                    dst[0] = r0;
-                    dst[1] = r1;
-                }
-            } else {
-                const uint32_t e[4] = {e0, e1, e2, e3};
-                for (uint32_t k = 0; k < valid; ++k)
-                    p.out[first + k] = df11_merge1((e[k >> 2] >> (8u * (k & 3u))) & 255u, __ldg(p.sm + first + k));
-            }
-        };
-
-        // the groups whose first code starts in my window
-        for (uint32_t r = o + ((q - o) & 15u); r < end; r += 16u) {
-            const uint32_t j = r - o, k = j >> 4;
-            const uint32_t start = k == 0u ? gap : (marks >> (6u * (k - 1u))) & 63u;
-            uint32_t e0, e1, e2, e3;
-            decode_group(tid * 64u + start, j & 15u, e0, e1, e2, e3);
-            emit(r, min(16u, block_cnt - r), e0, e1, e2, e3);
+        // clamp to what this block may write, then shift by the block's alignment phase
+        o = min(o, block_cnt) + phase;
+        end = min(end, block_cnt) + phase;
+        {
+            int tbad = 0;
+            df11_decode_window<K>(mem, p.n_luts, w0, w1, w2, gap, o, end, &tbad);
+            if (tbad) bad |= DF11_STATUS_BAD_TABLE;
         }
-        // the block's first elements, whose group started in the block before
-        if (tid == 0 && q != 0u && block_cnt != 0u) {
-            uint32_t e0, e1, e2, e3;
-            decode_group(gap, 0u, e0, e1, e2, e3);
-            const uint32_t h = min(q, block_cnt);
-            const uint32_t e[4] = {e0, e1, e2, e3};
-            for (uint32_t k = 0; k < h; ++k)
-                p.out[base + k] = df11_merge1((e[k >> 2] >> (8u * (k & 3u))) & 255u, __ldg(p.sm + base + k));
-        }
+        __syncthreads();
+        if (!mbar_wait(bar_sm, it & 1u, (bad & DF11_STATUS_TIMEOUT) ? 0ull : wait_ns)) bad |= DF11_STATUS_TIMEOUT;
 
-        // wsum and this input buffer are reused; and if any thread's wait ran out the CTA stops
-        // here: its remaining blocks stay undecoded, the status word says so
+        // ---- merge with sign/mantissa ------------------------------------------------------------
+        // Groups of eight elements aligned to eight in the output: group g covers staging and tile
+        // bytes [8g, 8g+8).  Complete groups: two 8-byte shared loads, one 16-byte global store.
+        uint16_t *out_blk = p.out + gbase;
+        if (p.out_aligned) {
+            const uint32_t g_lo = (phase + 7u) >> 3, g_hi = last >> 3;
+            for (uint32_t g = g_lo + tid; g < g_hi; g += kThreads) {
+                const uint2 ex = lds64(mem.stage_addr + 8u * g);
+                const uint2 m = lds64(tile_addr + 8u * g);
+                uint4 r;
+                df11_merge4(ex.x, m.x, &r.x, &r.y);
+                df11_merge4(ex.y, m.y, &r.z, &r.w);
+                reinterpret_cast<uint4 *>(out_blk)[g] = r;
+            }
+            // elements of the (at most two) incomplete groups at either end, one per thread
+            if (tid < 16u) {
+                const uint32_t i = tid < 8u ? 8u * (g_lo - 1u) + tid : 8u * g_hi + (tid - 8u);
+                const bool mine = tid < 8u ? ((phase & 7u) != 0u && i >= phase && i < last)
+                                           : (g_hi >= g_lo && i < last);
+                if (mine) out_blk[i] = df11_merge1(lds8(mem.stage_addr + i), lds8(tile_addr + i));
+            }
+        } else {
+            for (uint32_t i = phase + tid; i < last; i += kThreads)
+                out_blk[i] = df11_merge1(lds8(mem.stage_addr + i), lds8(tile_addr + i));
+        }
+        // staging, tile, wsum and this input buffer are reused; and if any thread's wait ran out the
+        // CTA stops here: its remaining blocks stay undecoded, the status word says so
         if (__syncthreads_or(bad & DF11_STATUS_TIMEOUT)) break;
     }
 
     // Never retire with a copy still on its way into this CTA's shared memory: the thread that
     // issued the copies waits (bounded) for the last phase announced on each barrier.  After a
-    // normal run all of them completed long ago and this costs two polls.
+    // normal run all of them completed long ago and this costs three polls.
     if (tid == 0) {
         const uint64_t drain_ns = p.wait_ns ? p.wait_ns : kDrainNs;
         bool drained = true;
         if (n_in[0]) drained &= mbar_wait(bar_in, (n_in[0] - 1u) & 1u, drain_ns);
         if (n_in[1]) drained &= mbar_wait(bar_in + 8, (n_in[1] - 1u) & 1u, drain_ns);
+        if (n_sm) drained &= mbar_wait(bar_sm, (n_sm - 1u) & 1u, drain_ns);
         if (!drained) bad |= DF11_STATUS_TIMEOUT;
     }
     if (bad && p.status != nullptr) atomicOr(p.status, bad);
@@ -1429,12 +1364,10 @@ int launch_gemv(Kernel kernel, int slot, int m_count, size_t smem, int64_t work_
 
 size_t small_tables_bytes(int n_luts) { return (size_t)n_luts * 256 + 256 + 32 * 4; }
 
-constexpr int kSelfDecBits = 12;  // decode table of the self-contained decoder (its count table has kTableBits)
-
 int launch_decode(const Params &p, int device, cudaStream_t stream)
 {
-    const size_t smem = Layout<kSelfDecBits, kTableBits>::luts + small_tables_bytes(p.n_luts);
-    return launch(df11_decode_kernel<kSelfDecBits, kTableBits>, kThreads, 0, smem, p.n_blocks, p, device, stream);
+    const size_t smem = Layout<kTableBits>::stage + 2 * (size_t)p.stage_bytes + 32 + small_tables_bytes(p.n_luts);
+    return launch(df11_decode_kernel<kTableBits>, kThreads, 0, smem, p.n_blocks, p, device, stream);
 }
 
 // Elements per seek point of the prepared form, process-wide: DF11_EPT in the environment (16 or
@@ -1466,6 +1399,15 @@ int check_common(const void *luts, const void *codes, const void *pos, const voi
         return df11_fail(DF11_ERR_BADARG, "n_elements = %lld does not fit the format's 32-bit output positions",
                          (long long)n_elements);
     return DF11_OK;
+}
+
+// Shared staging: alignment phase (<= 15) + elements of the widest block, rounded up to whole
+// 16-byte pieces, plus the 16 bytes the kernel keeps as a margin.
+int stage_bytes_for(int32_t max_block_elems)
+{
+    int64_t m = max_block_elems > 0 ? max_block_elems : DF11_MAX_BLOCK_ELEMS;
+    if (m > DF11_MAX_BLOCK_ELEMS) m = DF11_MAX_BLOCK_ELEMS;
+    return (int)((m + 15 + 15) / 16 * 16) + 16;
 }
 
 constexpr int64_t kAuxTableBytes = (int64_t)sizeof(Df11Entry) << kFastTableBits;
@@ -1504,6 +1446,7 @@ Params base_params(const void *luts, const void *codes, const void *pos, const v
     p.n_elements = n_elements;
     p.n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
     p.n_luts = n_luts;
+    p.stage_bytes = 16;
     p.drop_block = -1;
     p.codes_aligned = (((uintptr_t)codes & 15) == 0 ? 1 : 0) | (((uintptr_t)gaps & 15) == 0 ? 2 : 0) |
                       (((uintptr_t)codes & 3) == 0 ? 4 : 0);
@@ -1524,7 +1467,7 @@ extern "C" int df11_decode(const void *luts, const void *codes, const void *sign
     Params p = base_params(luts, codes, output_positions, gaps, n_luts, n_bytes, n_elements, status);
     p.sm = (const uint8_t *)sign_mantissa;
     p.out = (uint16_t *)out_bf16;
-    (void)max_block_elems;  // sized a staging area in earlier versions of the kernel; kept in the signature
+    p.stage_bytes = stage_bytes_for(max_block_elems);
     p.sm_aligned = (((uintptr_t)sign_mantissa & 15) == 0 ? 1 : 0) | (((uintptr_t)sign_mantissa & 31) == 0 ? 2 : 0);
     p.out_aligned = (((uintptr_t)out_bf16 & 15) == 0 ? 1 : 0) | (((uintptr_t)out_bf16 & 31) == 0 ? 2 : 0);
     return launch_decode(p, device, (cudaStream_t)stream);
@@ -1546,7 +1489,7 @@ extern "C" int df11_selftest_wait_timeout(const void *luts, const void *codes, c
                          (long long)p.n_blocks);
     p.sm = (const uint8_t *)sign_mantissa;
     p.out = (uint16_t *)out_bf16;
-    (void)max_block_elems;  // sized a staging area in earlier versions of the kernel; kept in the signature
+    p.stage_bytes = stage_bytes_for(max_block_elems);
     p.sm_aligned = (((uintptr_t)sign_mantissa & 15) == 0 ? 1 : 0) | (((uintptr_t)sign_mantissa & 31) == 0 ? 2 : 0);
     p.out_aligned = (((uintptr_t)out_bf16 & 15) == 0 ? 1 : 0) | (((uintptr_t)out_bf16 & 31) == 0 ? 2 : 0);
     if (!(p.codes_aligned & 1) && !(p.codes_aligned & 2))

@@ -41,7 +41,7 @@ extern "C" {
 /* Bits a decode kernel ORs into the optional device status word. */
 #define DF11_STATUS_BAD_TABLE 1    /* pointer outside `luts`, or a code length of 0 or > 32 */
 #define DF11_STATUS_BAD_POSITIONS 2 /* output_positions not monotone / beyond n_elements    */
-#define DF11_STATUS_TRUNCATED 4    /* reserved (set by earlier versions whose staging area could be too small) */
+#define DF11_STATUS_TRUNCATED 4    /* a format block holds more elements than max_block_elems */
 #define DF11_STATUS_TIMEOUT 8      /* a bounded wait for an asynchronous copy ran out        */
 
 /* Library version, major*10000 + minor*100 + patch.  (The reference keeps a format
@@ -63,10 +63,10 @@ const char *df11_last_error(void);
  *   output_positions  device, uint32 [ceil(n_bytes/4096) + 1]
  *   gaps              device, uint8  [ceil(n_bytes/4096) * 320]
  *   out_bf16          device, uint16 [n_elements]        receives the BF16 bit patterns
- *   max_block_elems   largest output_positions[b+1] - output_positions[b], the number the
- *                     reference's `shared_mem_size` is computed from (dfloat11.py:299-306).
- *                     Accepted so that a caller can pass what it has; the kernel stages
- *                     nothing in shared memory and does not need it (any value is fine).
+ *   max_block_elems   largest output_positions[b+1] - output_positions[b]; it sizes the
+ *                     kernel's shared-memory staging the way the reference's
+ *                     `shared_mem_size` does (dfloat11.py:299-306).  <= 0: assume the
+ *                     format's worst case (32768).
  *   status            device, int32, optional (may be NULL): DF11_STATUS_* bits are
  *                     ORed in when the kernel meets inconsistent tensors.  The kernel
  *                     never traps, reads out of bounds or loops without bound on bad
@@ -74,9 +74,9 @@ const char *df11_last_error(void);
  *   stream            a cudaStream_t (NULL = the legacy default stream)
  *
  * 64-bit sizes: units above 2^31 elements are fine (the reference's `int`
- * arguments, decode.cu:33, overflow there).  The fast paths (TMA bulk copies, 16-byte loads,
- * 32-byte stores) need `codes`, `gaps` and `sign_mantissa` 16-byte and `out_bf16` 32-byte
- * aligned (any torch allocation is); other alignments work but decode slower.
+ * arguments, decode.cu:33, overflow there).  The fast paths (TMA bulk copies, 16-byte
+ * stores) need `codes`, `gaps`, `sign_mantissa` and `out_bf16` 16-byte aligned (any torch
+ * allocation is); other alignments work but decode slower.
  */
 int df11_decode(const void *luts, const void *codes, const void *sign_mantissa,
                 const void *output_positions, const void *gaps, void *out_bf16,

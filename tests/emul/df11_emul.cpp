@@ -1,9 +1,9 @@
 // Host-side emulation of the CUDA decode kernels' algorithm.  TEST INFRASTRUCTURE ONLY:
 // it is compiled by tests/test_emulation.py, never linked into libdf11 and never used by
-// the product.  It runs the same table builder, window routines, group decoder and merge
-// arithmetic (dfloat11_b200/csrc/df11_common.h) that the kernels run, with the kernels'
-// block-level flow (clamps, output-aligned groups, heads and tails of blocks) restated serially,
-// so that the algorithm can be checked against the CPU oracle on a machine without a GPU.
+// the product.  It runs the same table builder, window routines and merge arithmetic
+// (dfloat11_b200/csrc/df11_common.h) that the kernels run, with the kernels' block-level
+// flow (clamps, alignment phase, 8-element merge groups) restated serially, so that the
+// algorithm can be checked against the CPU oracle on a machine without a GPU.
 #include <stdint.h>
 #include <string.h>
 
@@ -14,14 +14,18 @@
 
 namespace {
 
+bool g_reverse = false;  // order in which the windows of a block run their decode pass
+
 // Memory policy of the window routines for plain host arrays.
 struct HostMem {
     const uint32_t *cnt_t;
     const Df11Entry *dec_t;
     const uint8_t *luts;
+    uint8_t *stage;
     uint32_t cnt(uint32_t i) const { return cnt_t[i]; }
     Df11Entry dec(uint32_t i) const { return dec_t[i]; }
     uint32_t lut(uint32_t i) const { return luts[i]; }
+    void put8(uint32_t addr, uint32_t v) const { stage[addr] = (uint8_t)v; }
     // seek-point decoder
     const uint8_t *codes = nullptr;
     int64_t n_bytes = 0;
@@ -69,7 +73,7 @@ int run_seek(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_by
     std::vector<Df11Entry> dec;
     std::vector<uint32_t> cnt;
     build_tables<K>(luts, n_luts, dec, cnt);
-    HostMem mem{cnt.data(), dec.data(), luts};
+    HostMem mem{cnt.data(), dec.data(), luts, nullptr};
     mem.codes = codes;
     mem.n_bytes = n_bytes;
     int bad = 0;
@@ -128,27 +132,26 @@ int run_seek(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_by
     return 0;
 }
 
-// The self-contained flow: per format block a counting pass (with marks), a scan, then groups of
-// sixteen output-aligned elements, each decoded from the gap or mark of the window in which its
-// first code starts after dropping the codes before it -- df11_decode_kernel's steps, serially.
 template <int K>
 int run(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, const uint8_t *sm,
         int64_t n_elements, const uint32_t *pos, const uint8_t *gaps, uint16_t *out, int max_block_elems,
         int *status)
 {
-    (void)max_block_elems;
     const int64_t n_blocks = (n_bytes + DF11_BLOCK_BYTES - 1) / DF11_BLOCK_BYTES;
     const int64_t n_gap_bytes = n_blocks * DF11_GAP_BYTES_PER_BLOCK;
     std::vector<Df11Entry> dec;
     std::vector<uint32_t> cnt;
     build_tables<K>(luts, n_luts, dec, cnt);
-    HostMem mem{cnt.data(), dec.data(), luts};
-    mem.codes = codes;
-    mem.n_bytes = n_bytes;
+
+    int64_t m = max_block_elems > 0 ? max_block_elems : DF11_MAX_BLOCK_ELEMS;
+    if (m > DF11_MAX_BLOCK_ELEMS) m = DF11_MAX_BLOCK_ELEMS;
+    const int stage_bytes = (int)((m + 15 + 15) / 16 * 16) + 16;
+    std::vector<uint8_t> stage(stage_bytes);
+    HostMem mem{cnt.data(), dec.data(), luts, stage.data()};
     int bad = 0;
 
     for (int64_t b = 0; b < n_blocks; ++b) {
-        const int64_t base = pos[b];
+        int64_t base = pos[b];
         const int64_t next = pos[b + 1];
         int64_t c = next - base;
         if (c < 0 || next > n_elements) {
@@ -156,63 +159,68 @@ int run(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes, 
             c = c < 0 ? 0 : n_elements - base;
             if (c < 0) c = 0;
         }
-        if (c > DF11_MAX_BLOCK_ELEMS + 64) {
-            bad |= DF11_STATUS_BAD_POSITIONS;
-            c = DF11_MAX_BLOCK_ELEMS + 64;
+        const uint32_t phase = (uint32_t)(base & 15);
+        if (c + phase > stage_bytes - 16) {
+            bad |= DF11_STATUS_TRUNCATED;
+            c = stage_bytes - 16 - phase;
         }
         const uint32_t block_cnt = (uint32_t)c;
-        const uint32_t q = (16u - (uint32_t)(base & 15)) & 15u;
+        memset(stage.data(), 0xEE, stage.size());  // poison: stale bytes must never reach the output
 
-        auto group = [&](uint64_t bitpos, uint32_t skip, uint32_t r, uint32_t valid) {
-            uint32_t row[4] = {0xEEEEEEEEu, 0xEEEEEEEEu, 0xEEEEEEEEu, 0xEEEEEEEEu};
-            mem.row = row;
-            int tbad = 0;
-            df11_decode_group<K, 16>(mem, n_luts, (uint32_t)(bitpos >> 5), (uint32_t)bitpos & 31u, true, &tbad, skip);
-            if (tbad) bad |= DF11_STATUS_BAD_TABLE;
-            const int64_t first = base + r;
-            if (valid == 16u) {
-                for (int k = 0; k < 4; ++k) {
-                    uint32_t m4, o2[2];
-                    memcpy(&m4, sm + first + 4 * k, 4);
-                    df11_merge4(row[k], m4, &o2[0], &o2[1]);
-                    memcpy(out + first + 4 * k, o2, 8);
-                }
-            } else {
-                const uint8_t *bytes = reinterpret_cast<const uint8_t *>(row);
-                for (uint32_t k = 0; k < valid; ++k) out[first + k] = df11_merge1(bytes[k], sm[first + k]);
-            }
-        };
-
-        uint32_t run_sum = 0, gap0 = 0;
+        // the kernel's 512 threads write their windows in no particular order: first every window's
+        // slots (count pass + scan), then the decode pass front to back or back to front (g_reverse),
+        // so that a window that writes into a neighbour's bytes shows up in one of the two orders
+        uint32_t run_sum = 0;
+        struct Win { uint32_t w[3], gap, o, end; bool live; } wins[DF11_WINDOWS_PER_BLOCK];
         for (int tid = 0; tid < DF11_WINDOWS_PER_BLOCK; ++tid) {
+            Win &x = wins[tid];
             const int64_t t = b * DF11_WINDOWS_PER_BLOCK + tid;
-            if (t * 8 >= n_bytes) break;
-            uint32_t w[3], marks = 0;
-            load_window(codes, n_bytes, t, w);
+            x.live = t * 8 < n_bytes;
+            if (!x.live) continue;
+            load_window(codes, n_bytes, t, x.w);
             int tbad = 0;
-            const uint32_t gap = df11_gap(gaps, n_gap_bytes, t);
-            if (tid == 0) gap0 = gap;
-            const uint32_t n = df11_count_window_marks<K>(mem, n_luts, w[0], w[1], w[2], gap, &marks, &tbad);
-            if (tbad) bad |= DF11_STATUS_BAD_TABLE;
-            if (n != df11_count_window<K>(mem, n_luts, w[0], w[1], w[2], gap, &tbad)) return -2;  // the two counting passes agree
+            x.gap = df11_gap(gaps, n_gap_bytes, t);
+            const uint32_t n = df11_count_window<K>(mem, n_luts, x.w[0], x.w[1], x.w[2], x.gap, &tbad);
             uint32_t o = run_sum, end = o + n;
             run_sum += n;
-            o = o < block_cnt ? o : block_cnt;
-            end = end < block_cnt ? end : block_cnt;
-            for (uint32_t r = o + ((q - o) & 15u); r < end; r += 16u) {
-                const uint32_t j = r - o, k = j >> 4;
-                const uint32_t start = k == 0u ? gap : (marks >> (6u * (k - 1u))) & 63u;
-                group((uint64_t)t * 64 + start, j & 15u, r, block_cnt - r < 16u ? block_cnt - r : 16u);
-            }
+            x.o = (o < block_cnt ? o : block_cnt) + phase;
+            x.end = (end < block_cnt ? end : block_cnt) + phase;
+            if (tbad) bad |= DF11_STATUS_BAD_TABLE;
         }
-        if (q != 0u && block_cnt != 0u)
-            group((uint64_t)b * DF11_WINDOWS_PER_BLOCK * 64 + gap0, 0u, 0u, q < block_cnt ? q : block_cnt);
+        for (int k = 0; k < DF11_WINDOWS_PER_BLOCK; ++k) {
+            const Win &x = wins[g_reverse ? DF11_WINDOWS_PER_BLOCK - 1 - k : k];
+            if (!x.live) continue;
+            int tbad = 0;
+            df11_decode_window<K>(mem, n_luts, x.w[0], x.w[1], x.w[2], x.gap, x.o, x.end, &tbad);
+            if (tbad) bad |= DF11_STATUS_BAD_TABLE;
+        }
+
+        const int64_t gbase = base - phase;
+        const uint8_t *sm_blk = sm + gbase;
+        uint16_t *out_blk = out + gbase;
+        const uint32_t last = phase + block_cnt;
+        const uint32_t g_lo = (phase + 7u) >> 3, g_hi = last >> 3;
+        for (uint32_t g = g_lo; g < g_hi; ++g) {
+            uint32_t ex[2], mm[2], r[4];
+            memcpy(ex, stage.data() + 8 * g, 8);
+            memcpy(mm, sm_blk + 8 * g, 8);
+            df11_merge4(ex[0], mm[0], &r[0], &r[1]);
+            df11_merge4(ex[1], mm[1], &r[2], &r[3]);
+            memcpy(out_blk + 8 * g, r, 16);
+        }
+        for (uint32_t tid = 0; tid < 16; ++tid) {
+            const uint32_t i = tid < 8u ? 8u * (g_lo - 1u) + tid : 8u * g_hi + (tid - 8u);
+            const bool mine = tid < 8u ? ((phase & 7u) != 0u && i >= phase && i < last) : (g_hi >= g_lo && i < last);
+            if (mine) out_blk[i] = df11_merge1(stage[i], sm_blk[i]);
+        }
     }
     if (status) *status = bad;
     return 0;
 }
 
 }  // namespace
+
+extern "C" void df11_emul_window_order(int reverse) { g_reverse = reverse != 0; }
 
 // prepared: 0 = the self-contained two-pass flow, 16 / 32 = seek points every 16 / 32 elements
 extern "C" int df11_emul_decode(const uint8_t *luts, int n_luts, const uint8_t *codes, int64_t n_bytes,

@@ -42,9 +42,24 @@ def _run(lib, g, K, prepared, cap):
 @pytest.mark.parametrize("K", [9, 11, 12, 14])
 @pytest.mark.parametrize("prepared", [0, 16, 32])
 def test_kernel_algorithm_matches_golden(emul, golden, K, prepared):
-    rc, status, out = _run(emul, golden, K, prepared, 0)
-    assert rc == 0 and status == 0
-    assert np.array_equal(out, golden["w"])
+    widest = int(np.diff(golden["output_positions"].astype(np.int64)).max())
+    for reverse in ((0, 1) if prepared == 0 else (0,)):
+        # the windows of a block write their staged exponents word by word next to each other: run the
+        # decode pass front to back and back to front, a window that touches a neighbour's bytes shows
+        emul.df11_emul_window_order(reverse)
+        for cap in (0, widest):
+            rc, status, out = _run(emul, golden, K, prepared, cap)
+            assert rc == 0 and status == 0
+            assert np.array_equal(out, golden["w"]), (reverse, cap)
+    emul.df11_emul_window_order(0)
+
+
+def test_small_staging_is_flagged_not_overrun(emul, golden):
+    widest = int(np.diff(golden["output_positions"].astype(np.int64)).max())
+    if widest < 64:
+        pytest.skip("tiny case")
+    rc, status, _ = _run(emul, golden, 11, 0, widest // 2)
+    assert rc == 0 and status & 4          # DF11_STATUS_TRUNCATED
 
 
 def test_table_entries_are_consistent(emul, golden):

@@ -218,12 +218,12 @@ def test_corrupt_units_set_status_and_return():
     ops.decode(luts, d["enc"], d["sm"], d["pos"], d["gaps"], status=st)
     torch.cuda.synchronize()
     assert st.item() & _lib.STATUS_BAD_TABLE
-    # 2. a cap below the widest block (it sized a staging area once; now ignored): still bit-exact
+    # 2. staging smaller than a block: flagged, no out-of-bounds write
     st = _status()
     buf = torch.full((n + 64,), 7.0, dtype=torch.bfloat16, device=DEV)
     ops.decode(d["luts"], d["enc"], d["sm"], d["pos"], d["gaps"], out=buf[:n], max_block_elems=1000, status=st)
     torch.cuda.synchronize()
-    assert st.item() == 0 and np.array_equal(_bits(buf[:n]), g["w"])
+    assert st.item() & _lib.STATUS_TRUNCATED
     assert torch.all(buf[n:] == 7.0)
     # 3. output positions running backwards / past the end
     pos = g["output_positions"].copy()
