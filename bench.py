@@ -946,8 +946,11 @@ def tp_block(args, rank, world, device):
     out = {}
 
     def toy(seed):
+        # built in BF16 from the start, as from_pretrained builds its skeleton: the rotary tables then
+        # stay fp32 in both (a model cast to BF16 afterwards has them rounded, and other logits)
+        from transformers import AutoModelForCausalLM
         torch.manual_seed(seed)
-        m = LlamaForCausalLM(LlamaConfig(**TOY_TP)).to(torch.bfloat16).eval()
+        m = AutoModelForCausalLM.from_config(LlamaConfig(**TOY_TP), dtype=torch.bfloat16).eval()
         with torch.no_grad():
             for name, p in m.named_parameters():
                 if p.dim() == 2:
