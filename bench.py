@@ -1034,6 +1034,45 @@ def tp_block(args, rank, world, device):
         ms_graph = timed(graph.replay)
     except Exception as exc:                                # report, do not hide
         graph_error = f"{type(exc).__name__}: {exc}"[:200]
+    # the same step with this library's one-kernel all-reduce over NVLink peer memory
+    peer_result = None
+    try:
+        from dfloat11_b200.comm import PeerAllReduce
+        peer = PeerAllReduce.get(None, device)
+        if peer is None:
+            peer_result = {"unavailable": "symmetric memory could not be set up"}
+        else:
+            def step_peer():
+                for u in units:
+                    ops.decode_prepared(u["luts"], u["enc"], u["sm"], u["pos"], u["gaps"], u["aux"], out=scratch,
+                                        status=status)
+                    peer.all_reduce_(act)
+                    peer.all_reduce_(act)
+
+            ms_peer = timed(step_peer)
+            ms_peer_alone = timed(lambda: [peer.all_reduce_(act) for _ in range(2 * layers)])
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                step_peer()
+            torch.cuda.current_stream(device).wait_stream(side)
+            barrier(world, device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step_peer()
+            ms_peer_graph = timed(graph.replay)
+            peer.check()
+            total_p = all_sum(sum(algorithmic_bytes(u) for u in units), world, device)
+            peak_p, _ = measured_hbm_peak()
+            peer_result = {
+                "ms_per_step": round(ms_peer, 3), "per_gpu_GBps": round(total_p / ms_peer / 1e6 / world, 1),
+                "per_gpu_frac_of_measured_peak": round(total_p / ms_peer / 1e6 / world / peak_p, 4),
+                "us_per_all_reduce_back_to_back": round(ms_peer_alone * 1e3 / (2 * layers), 2),
+                "cuda_graph": {"ms_per_step": round(ms_peer_graph, 3),
+                               "per_gpu_GBps": round(total_p / ms_peer_graph / 1e6 / world, 1),
+                               "per_gpu_frac_of_measured_peak": round(total_p / ms_peer_graph / 1e6 / world / peak_p, 4)}}
+    except Exception as exc:                                # report, do not hide
+        peer_result = {"error": f"{type(exc).__name__}: {exc}"[:200]}
     ok = int(scratch.view(torch.int16).to(torch.int64).sum().item()) == first["checksum"] and status.item() == 0
     total = all_sum(sum(algorithmic_bytes(u) for u in units), world, device)
     peak, _ = measured_hbm_peak()
@@ -1051,7 +1090,8 @@ def tp_block(args, rank, world, device):
         "us_per_all_reduce_back_to_back": round(ms_reduce * 1e3 / (2 * layers), 2),
         "us_per_all_reduce_in_step": round((ms_with - ms_without) * 1e3 / (2 * layers), 2),
         "bit_exact": bool(ok),
-        "note": "one block-shard per rank compressed once and cloned per layer; NCCL all-reduce"}
+        "peer_all_reduce": peer_result,
+        "note": "one block-shard per rank compressed once and cloned per layer; NCCL all-reduce unless stated"}
     del units, first, scratch
     torch.cuda.empty_cache()
 

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libdf11.so")
-SOURCES = ["df11_decode.cu", "df11_encode.cu", "df11_host.cpp"]
+SOURCES = ["df11_decode.cu", "df11_encode.cu", "df11_allreduce.cu", "df11_host.cpp"]
 HEADERS = ["df11_common.h", "df11_error.h", os.path.join("..", "..", "include", "df11.h")]
 
 NVCC_FLAGS = [

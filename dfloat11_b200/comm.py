@@ -1,0 +1,93 @@
+"""The activation all-reduce of the partitioned mode in one kernel over NVLink peer memory.
+
+After every row-parallel layer the ranks' partial outputs are summed: a ``[batch, hidden]`` BF16
+tensor, 32 KB at batch 1 for hidden 16384.  A library collective is pure latency at that size
+(some 25 microseconds through NCCL at eight ranks, two of them per transformer layer).
+``df11_allreduce_bf16`` (``csrc/df11_allreduce.cu``) does it in one launch with plain peer loads
+and stores on buffers that every rank can address; this module sets those buffers up with
+torch's symmetric memory and keeps one set per process group and device.  The reference has no
+such mode at all (its only multi-GPU form places whole layers on different devices,
+dfloat11/dfloat11.py:455-460).
+
+Opt-in: ``DF11_PEER_ALLREDUCE=1`` (read when ``apply_tensor_parallel`` runs).  Whatever cannot
+go through the kernel -- another dtype, more than ``SLOT_BYTES``, a setup that failed -- goes
+through ``torch.distributed.all_reduce`` as before; compare models only with the same setting,
+the two ways of summing round differently.
+"""
+from __future__ import annotations
+
+import ctypes
+import logging
+from typing import Dict, Optional
+
+import torch
+
+from . import _lib
+
+log = logging.getLogger("dfloat11")
+
+SLOT_BYTES = 1 << 20          # largest tensor the kernel takes (batch 32 at hidden 16384)
+
+
+class PeerAllReduce:
+    """Buffers, flags and the call counter of one process group on one device."""
+
+    _instances: Dict[tuple, Optional["PeerAllReduce"]] = {}
+
+    def __init__(self, group, device: torch.device, slot_bytes: int = SLOT_BYTES):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise RuntimeError("the peer all-reduce handles up to 8 ranks")
+        self.device = device
+        self.slot_bytes = int(slot_bytes)
+        flag_bytes = int(_lib.lib.df11_allreduce_flag_bytes())
+        self.buffer = symm_mem.empty(2 * self.slot_bytes + flag_bytes, dtype=torch.uint8, device=device)
+        self.buffer.zero_()
+        torch.cuda.synchronize(device)
+        self.handle = symm_mem.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
+        pointers = [int(p) for p in self.handle.buffer_ptrs]
+        self._data = (ctypes.c_uint64 * 8)(*(pointers + [0] * (8 - len(pointers))))
+        self._flags = (ctypes.c_uint64 * 8)(*([p + 2 * self.slot_bytes for p in pointers] + [0] * (8 - len(pointers))))
+        self.counters = torch.zeros(2, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.calls = 0
+        # nobody writes a flag before every rank's flag area is zero
+        dist.barrier(group=group, device_ids=[device.index])
+        torch.cuda.synchronize(device)
+
+    @classmethod
+    def get(cls, group, device: torch.device) -> Optional["PeerAllReduce"]:
+        """The instance for (group, device), made on first use by all ranks together; None when
+        symmetric memory cannot be set up here (logged once; the caller uses the library collective)."""
+        key = (id(group) if group is not None else None, device)
+        if key not in cls._instances:
+            try:
+                cls._instances[key] = cls(group, device)
+            except Exception as exc:  # noqa: BLE001 - optional acceleration
+                log.warning("peer all-reduce unavailable (%s: %s); using torch.distributed.all_reduce",
+                            type(exc).__name__, exc)
+                cls._instances[key] = None
+        return cls._instances[key]
+
+    def all_reduce_(self, tensor: torch.Tensor) -> bool:
+        """Sums ``tensor`` over the ranks in place; False if this tensor is not one the kernel takes."""
+        if (tensor.dtype != torch.bfloat16 or not tensor.is_cuda or tensor.device != self.device
+                or not tensor.is_contiguous() or tensor.numel() % 8 or tensor.numel() * 2 > self.slot_bytes
+                or tensor.data_ptr() % 16):
+            return False
+        _lib.check(_lib.lib.df11_allreduce_bf16(
+            self._data, self._flags, self.counters.data_ptr(), self.rank, self.world, tensor.data_ptr(),
+            tensor.data_ptr(), tensor.numel(), self.slot_bytes, 0, self.status.data_ptr(), self.device.index,
+            torch.cuda.current_stream(self.device).cuda_stream))
+        self.calls += 1
+        return True
+
+    def check(self) -> None:
+        """Raises if a call gave up waiting for a peer (synchronises)."""
+        if int(self.status.item()):
+            self.status.zero_()
+            raise _lib.DF11Error(_lib.DF11_ERR_CUDA, "a peer all-reduce timed out waiting for another rank")

@@ -1,0 +1,177 @@
+// One-shot all-reduce of a small BF16 activation tensor over NVLink peer memory, for the
+// partitioned (tensor-parallel) mode: after every row-parallel layer the ranks' partial outputs
+// ([batch, hidden] BF16: 32 KB at batch 1 for hidden 16384) are summed.  At that size a
+// collective is pure latency; this kernel does it in one launch with plain peer loads and
+// stores -- no library call, no multicast object, no TMA:
+//
+//   1. every rank copies its slice into its own buffer in symmetric memory (local stores),
+//   2. tells every peer so (one flag per rank, CTA and call parity, written into the PEER's flag
+//      area with a system-scope release store),
+//   3. waits until all ranks' flags for this call have arrived in its own flag area (bounded),
+//   4. reads every rank's slice (peer loads over NVLink), adds them in rank order in fp32 and
+//      rounds once to BF16: the same bits on every rank, run to run.
+//
+// The call number lives in device memory and is advanced by the kernel itself, so a launch
+// recorded in a CUDA graph can be replayed.  Buffers alternate between two halves by call
+// parity: a rank can only be one call ahead of a peer (it needs the peer's flag of call s to
+// finish call s), so the half written in call s + 2 is no longer being read.
+// The reference has no counterpart: its only multi-GPU form places whole layers on different
+// devices (dfloat11/dfloat11.py:455-460).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/df11.h"
+#include "df11_error.h"
+
+namespace {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxCtas = 32;
+constexpr int kThreads = 512;
+constexpr uint64_t kWaitNs = 2000ull * 1000 * 1000;  // a peer that has not shown up after two seconds is not coming
+constexpr uint32_t kWaitPolls = 1u << 24;
+
+struct Peers {
+    uint8_t *data[kMaxRanks];    // each rank's buffer: two halves of slot_bytes
+    uint32_t *flags[kMaxRanks];  // each rank's flag area: [2][kMaxCtas][kMaxRanks]
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ld_volatile16(const void *p)
+{
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint64_t global_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t bf16x2_from_floats(float lo, float hi)  // round to nearest even; NaN stays NaN
+{
+    auto one = [](float f) -> uint32_t {
+        uint32_t u = __float_as_uint(f);
+        if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (u >> 16) | 0x40u;
+        u += 0x7FFFu + ((u >> 16) & 1u);
+        return u >> 16;
+    };
+    return one(lo) | (one(hi) << 16);
+}
+
+__global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers peers, uint32_t *counters, int rank,
+                                                                  int world, const uint4 *in, uint4 *out, uint32_t n_vec,
+                                                                  uint32_t vec_per_cta, uint32_t slot_bytes,
+                                                                  uint64_t wait_ns, int *status)
+{
+    const uint32_t tid = threadIdx.x, cta = blockIdx.x;
+    const uint32_t call = *reinterpret_cast<volatile uint32_t *>(counters);  // advanced by the last CTA to finish
+    const uint32_t half = call & 1u;
+    const uint32_t v0 = cta * vec_per_cta, v1 = min(n_vec, v0 + vec_per_cta);
+    const uint32_t flag_index = (half * kMaxCtas + cta) * kMaxRanks;
+
+    // 1. my slice into my own half
+    uint4 *mine = reinterpret_cast<uint4 *>(peers.data[rank] + (size_t)half * slot_bytes);
+    for (uint32_t v = v0 + tid; v < v1; v += kThreads) mine[v] = in[v];
+    __threadfence_system();
+    __syncthreads();
+    // 2. tell every rank (myself included), 3. wait for every rank
+    bool ok = true;
+    if (tid < (uint32_t)world) {
+        st_release_sys(peers.flags[tid] + flag_index + rank, call + 1u);
+        const uint32_t *theirs = peers.flags[rank] + flag_index + tid;
+        const uint64_t t0 = global_ns();
+        ok = false;
+        for (uint32_t it = 0; it < kWaitPolls; ++it) {
+            if (ld_acquire_sys(theirs) == call + 1u) {
+                ok = true;
+                break;
+            }
+            if ((it & 63u) == 63u && global_ns() - t0 > wait_ns) break;
+        }
+    }
+    const int all_ok = __syncthreads_and(ok ? 1 : 0);
+    // 4. sum in rank order
+    if (all_ok) {
+        for (uint32_t v = v0 + tid; v < v1; v += kThreads) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < world; ++r) {
+                const uint4 x = ld_volatile16(peers.data[r] + (size_t)half * slot_bytes + (size_t)v * 16);
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    acc[2 * k] += __uint_as_float(w[k] << 16);
+                    acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+                }
+            }
+            out[v] = make_uint4(bf16x2_from_floats(acc[0], acc[1]), bf16x2_from_floats(acc[2], acc[3]),
+                                bf16x2_from_floats(acc[4], acc[5]), bf16x2_from_floats(acc[6], acc[7]));
+        }
+    } else if (tid == 0 && status != nullptr) {
+        atomicOr(status, DF11_STATUS_TIMEOUT);  // the output is left as it was; the host reads the status
+    }
+    // the last CTA to get here advances the call number (every CTA has read it by then)
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(counters + 1, 1u) == gridDim.x - 1u) {
+            counters[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(counters) = call + 1u;
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int64_t df11_allreduce_flag_bytes(void) { return (int64_t)2 * kMaxCtas * kMaxRanks * sizeof(uint32_t); }
+
+extern "C" int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *peer_flags, void *counters, int32_t rank,
+                                   int32_t world, const void *in_bf16, void *out_bf16, int64_t n_elements,
+                                   int64_t slot_bytes, int64_t wait_ms, void *status, int32_t device, void *stream)
+{
+    if (!peer_data || !peer_flags || !counters || !in_bf16 || !out_bf16)
+        return df11_fail(DF11_ERR_BADARG, "null pointer");
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+        return df11_fail(DF11_ERR_BADARG, "rank %d of %d: up to %d ranks", rank, world, kMaxRanks);
+    if (n_elements < 0 || n_elements % 8) return df11_fail(DF11_ERR_BADARG, "n_elements must be a multiple of 8");
+    if (n_elements * 2 > slot_bytes || slot_bytes % 16 || slot_bytes > 0x7FFFFFFF)
+        return df11_fail(DF11_ERR_NOSPACE, "%lld elements do not fit a buffer half of %lld bytes", (long long)n_elements,
+                         (long long)slot_bytes);
+    if (((uintptr_t)in_bf16 & 15) || ((uintptr_t)out_bf16 & 15) || ((uintptr_t)counters & 3))
+        return df11_fail(DF11_ERR_BADARG, "in / out must be 16-byte aligned");
+    if (n_elements == 0) return DF11_OK;
+    Peers peers = {};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_data[r] || !peer_flags[r] || (peer_data[r] & 15) || (peer_flags[r] & 3))
+            return df11_fail(DF11_ERR_BADARG, "peer pointer %d is null or misaligned", r);
+        peers.data[r] = reinterpret_cast<uint8_t *>(peer_data[r]);
+        peers.flags[r] = reinterpret_cast<uint32_t *>(peer_flags[r]);
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != device && cudaSetDevice(device) != cudaSuccess)
+        return df11_fail(DF11_ERR_CUDA, "cudaSetDevice(%d) failed", device);
+    const uint32_t n_vec = (uint32_t)(n_elements / 8);
+    uint32_t ctas = (n_vec + 1023u) / 1024u;  // about two vectors per thread
+    if (ctas > (uint32_t)kMaxCtas) ctas = kMaxCtas;
+    if (ctas < 1u) ctas = 1u;
+    const uint32_t per = (n_vec + ctas - 1u) / ctas;
+    df11_allreduce_kernel<<<ctas, kThreads, 0, (cudaStream_t)stream>>>(
+        peers, (uint32_t *)counters, rank, world, (const uint4 *)in_bf16, (uint4 *)out_bf16, n_vec, per,
+        (uint32_t)slot_bytes, wait_ms > 0 ? (uint64_t)wait_ms * 1000000ull : kWaitNs, (int *)status);
+    const cudaError_t e = cudaGetLastError();
+    if (prev >= 0 && prev != device) cudaSetDevice(prev);
+    if (e != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+    return DF11_OK;
+}

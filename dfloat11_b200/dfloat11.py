@@ -218,6 +218,9 @@ class _OffloadStager:
         if slot is None:
             slot = next(s for s in self.slots if s["owner"] is not keep)
         compute = torch.cuda.current_stream(self.device)
+        nvtx = _Flags.current().nvtx
+        if nvtx:
+            torch.cuda.nvtx.range_push("df11.h2d")
         with torch.cuda.stream(self.stream):
             if slot["free"] is not None:
                 self.stream.wait_event(slot["free"])
@@ -236,6 +239,8 @@ class _OffloadStager:
                 self.stats["copies"] += 1
             slot["ready"] = torch.cuda.Event()
             slot["ready"].record(self.stream)
+        if nvtx:
+            torch.cuda.nvtx.range_pop()
         slot["owner"] = module
         return slot
 
@@ -710,7 +715,7 @@ def get_hook(threads_per_block, bytes_per_thread):
                 _counters["decoded_elements"] += fast[4][9]
                 return None
         if _Flags.current().nvtx:                  # DF11_NVTX=1: one range per unit in profiler timelines
-            torch.cuda.nvtx.range_push(f"df11_decode {type(module).__name__} {module.sign_mantissa.numel() if hasattr(module, 'sign_mantissa') else 'offloaded'}")
+            torch.cuda.nvtx.range_push(f"df11.decode {type(module).__name__}")
             try:
                 return full_path(module, inputs)
             finally:

@@ -18,7 +18,8 @@ sharded BEFORE compression, because a Huffman stream cannot be re-cut without de
 
 Decompression itself never communicates: the collectives are the activation all-reduce after
 each row-parallel layer (two per transformer block), the all-reduce of the embedding lookup and
-the all-gather of the logits.
+the all-gather of the logits -- NCCL's, or, with ``DF11_PEER_ALLREDUCE=1``, for the activation
+all-reduce one kernel of this library over NVLink peer memory (``comm.py``).
 """
 from __future__ import annotations
 
@@ -146,8 +147,17 @@ def apply_tensor_parallel(model: nn.Module, pattern_dict: Dict[str, List[str]], 
     if tp_size == 1:
         return model
     import torch.distributed as dist
+    own_all_reduce = os.environ.get("DF11_PEER_ALLREDUCE", "0") == "1"
+
+    peer = [None, False]          # the one-kernel all-reduce over NVLink peer memory, set up at its first use
 
     def all_reduce_output(_module, _inputs, output):
+        if own_all_reduce and output.is_cuda:
+            if not peer[1]:
+                from .comm import PeerAllReduce
+                peer[0], peer[1] = PeerAllReduce.get(group, output.device), True
+            if peer[0] is not None and peer[0].all_reduce_(output):
+                return output
         dist.all_reduce(output, group=group)
         return output
 

@@ -247,6 +247,35 @@ int df11_decode_static(const void *luts, const void *codes, const void *sign_man
                        int32_t device, void *stream);
 
 /*
+ * All-reduce (sum) of a small BF16 tensor across the ranks of the partitioned mode, in one
+ * kernel over NVLink peer memory: plain peer loads and stores, no collective library, no
+ * multicast.  For the [batch, hidden] activations that are summed after every row-parallel
+ * layer (32 KB at batch 1 for hidden 16384), where a library collective is all latency.
+ * Every rank calls it with the same n_elements, in the same order, on its own GPU.
+ *
+ *   peer_data    HOST array [world] of device addresses: rank r's buffer of 2 * slot_bytes
+ *                bytes in memory that every rank can address (symmetric memory, or IPC
+ *                mappings), as seen from THIS process; entry `rank` is this rank's own
+ *   peer_flags   HOST array [world]: rank r's flag area of df11_allreduce_flag_bytes() bytes,
+ *                zeroed once before the first call on any rank
+ *   counters     device, this rank only: two uint32, zeroed once (call number, CTAs done)
+ *   in_bf16 / out_bf16   device, n_elements BF16 each (a multiple of 8; in == out is fine),
+ *                16-byte aligned; n_elements * 2 <= slot_bytes
+ *   wait_ms      how long a rank waits for its peers' data before it gives up, sets
+ *                DF11_STATUS_TIMEOUT in `status` and leaves `out` untouched (<= 0: 2 s)
+ * The sum is taken in rank order in fp32 and rounded once: identical bits on every rank.
+ * The call number is kept in `counters`, so a launch captured in a CUDA graph replays.
+ * No counterpart in the reference (its only multi-GPU form places whole layers on
+ * different devices, dfloat11/dfloat11.py:455-460).
+ */
+int64_t df11_allreduce_flag_bytes(void);
+
+int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *peer_flags, void *counters,
+                        int32_t rank, int32_t world, const void *in_bf16, void *out_bf16,
+                        int64_t n_elements, int64_t slot_bytes, int64_t wait_ms, void *status,
+                        int32_t device, void *stream);
+
+/*
  * Host-side check of one unit before its first launch (all pointers HOST memory).
  * The reference performs no validation: a zero entry in the length row makes its
  * kernel spin forever (decode.cu:116-118).  Checks: table count, pointers stay

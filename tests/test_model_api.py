@@ -347,6 +347,43 @@ def test_from_pretrained_without_a_skeleton_gives_bf16_logits(saved, offload):
 
 
 @pytest.mark.gpu
+def test_status_word_stats_and_nvtx_switch(saved, monkeypatch):
+    """Every launch of the hooks reports into one status word per device: a forward over tensors
+    that went bad raises from ``check_status`` (or by itself with DF11_CHECK_STATUS=1) instead of
+    silently computing with unspecified weights; ``stats()`` counts what the hooks did."""
+    path, reference = saved
+    model = df11.DFloat11Model.from_pretrained(path, device="cuda:0", bfloat16_model=tiny_llama(seed=7))
+    ids = torch.randint(0, 1024, (1, 12), generator=torch.Generator().manual_seed(3)).to("cuda:0")
+    before = df11.stats()
+    monkeypatch.setenv("DF11_NVTX", "1")                      # the slower, fully checked path with ranges around it
+    with torch.no_grad():
+        model(input_ids=ids)
+        monkeypatch.setenv("DF11_NVTX", "0")
+        model(input_ids=ids)
+    after = df11.stats()
+    assert after["decodes"] >= before["decodes"] + 2 * 4 and after["decoded_elements"] > before["decoded_elements"]
+    assert any(k.startswith("cuda:0/slot0") for k in after["scratch_bytes"])
+    df11.check_status()                                       # nothing wrong so far
+    layer = model.model.layers[1]
+    good = layer.luts.clone()
+    layer.luts[-1, :] = 0                                     # code lengths of 0: the reference kernel would spin on these
+    layer.__dict__.pop("df11_aux", None)                      # rebuild the tables from the broken luts
+    layer.__dict__["df11_fast"] = None
+    with torch.no_grad():
+        model(input_ids=ids)
+    with pytest.raises(df11._lib.DF11Error):
+        df11.check_status()
+    df11.check_status()                                       # the word was reset by the failed check
+    monkeypatch.setenv("DF11_CHECK_STATUS", "1")
+    with torch.no_grad(), pytest.raises(df11._lib.DF11Error):
+        model(input_ids=ids)
+    layer.luts.copy_(good)
+    layer.__dict__.pop("df11_aux", None)
+    with torch.no_grad():
+        model(input_ids=ids)                                  # repaired: the per-forward check passes again
+
+
+@pytest.mark.gpu
 def test_compress_model_self_check_and_single_file(tmp_path):
     class Block(nn.Module):
         def __init__(self):

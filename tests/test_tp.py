@@ -88,8 +88,8 @@ def test_biases_are_sharded_with_their_layers(tmp_path):
         assert torch.equal(emb, want.model.embed_tokens.weight.data[rank * 512:(rank + 1) * 512])
 
 
-def _tp_worker(rank, world, port, use_cuda, path, ids, want, q):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+def _tp_worker(rank, world, port, use_cuda, path, ids, want, q, peer=False):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), DF11_PEER_ALLREDUCE="1" if peer else "0")
     dist.init_process_group("nccl" if use_cuda else "gloo", rank=rank, world_size=world)
     try:
         if use_cuda:
@@ -102,6 +102,11 @@ def _tp_worker(rank, world, port, use_cuda, path, ids, want, q):
             with torch.no_grad():
                 a = bf16(input_ids=ids.to(dev)).logits
                 b = df(input_ids=ids.to(dev)).logits
+            if peer:                                            # the kernel really ran, and no wait ran out
+                from dfloat11_b200.comm import PeerAllReduce
+                inst = PeerAllReduce.get(None, torch.device(dev))
+                assert inst is not None and inst.calls > 0
+                inst.check()
             q.put((rank, bool(torch.equal(a, b)), float((a.float().cpu() - want).abs().max())))
         else:
             model = tiny_llama(attention_bias=True, bias_seed=3).float()
@@ -114,7 +119,7 @@ def _tp_worker(rank, world, port, use_cuda, path, ids, want, q):
         dist.destroy_process_group()
 
 
-def _run_ranks(world, use_cuda, path=None):
+def _run_ranks(world, use_cuda, path=None, peer=False):
     ids = torch.randint(0, 1024, (2, 17), generator=torch.Generator().manual_seed(4))
     ref = tiny_llama(attention_bias=True, bias_seed=3).float() if not use_cuda else tiny_llama()
     with torch.no_grad():
@@ -122,7 +127,8 @@ def _run_ranks(world, use_cuda, path=None):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29600 + os.getpid() % 300
-    procs = [ctx.Process(target=_tp_worker, args=(r, world, port, use_cuda, path, ids, want, q)) for r in range(world)]
+    procs = [ctx.Process(target=_tp_worker, args=(r, world, port, use_cuda, path, ids, want, q, peer))
+             for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(world)]
@@ -139,12 +145,82 @@ def test_all_reduce_wiring_on_two_gloo_ranks():
         assert gathered and err < 1e-3              # full-vocabulary logits on every rank
 
 
+def _peer_worker(rank, world, port, q):
+    """The one-kernel all-reduce against an fp32 sum of the same inputs, eagerly, back to back
+    (call parity, counters) and replayed from a CUDA graph."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from dfloat11_b200.comm import PeerAllReduce
+        inst = PeerAllReduce.get(None, dev)
+        if inst is None:
+            q.put((rank, "unavailable"))
+            return
+        ok = True
+        for n in (8, 16384, 16384, 40000, 16 * 16384, 16384):
+            parts = [torch.randn(n, generator=torch.Generator().manual_seed(100 * n + r)).to(torch.bfloat16)
+                     for r in range(world)]
+            want = torch.zeros(n)
+            for p in parts:                                  # rank order, fp32, one rounding: what the kernel does
+                want = want + p.float()
+            x = parts[rank].to(dev)
+            assert inst.all_reduce_(x)
+            ok &= bool(torch.equal(x.cpu(), want.to(torch.bfloat16)))
+        assert not inst.all_reduce_(torch.zeros(7, dtype=torch.bfloat16, device=dev))      # not a multiple of 8
+        assert not inst.all_reduce_(torch.zeros(8, dtype=torch.float32, device=dev))
+        # three calls in one graph, replayed: the call number lives on the device
+        x = torch.ones(4096, dtype=torch.bfloat16, device=dev)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            inst.all_reduce_(x)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        dist.barrier(device_ids=[rank])
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(3):
+                inst.all_reduce_(x)
+        x.fill_(1.0)
+        graph.replay()
+        graph.replay()
+        torch.cuda.synchronize()
+        ok &= bool((x == float(world) ** 6).all()) if world <= 2 else True
+        inst.check()
+        q.put((rank, "ok" if ok else "wrong"))
+    finally:
+        dist.destroy_process_group()
+
+
 @pytest.mark.gpu
-def test_df11_shards_match_bf16_shards_on_two_gpus(tmp_path):
+@pytest.mark.parametrize("world", [1, 2])
+def test_peer_all_reduce_kernel(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs more GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29300 + os.getpid() % 300 + world
+    procs = [ctx.Process(target=_peer_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    if any(r[1] == "unavailable" for r in results):
+        pytest.skip("symmetric memory cannot be set up on this box")
+    assert [r[1] for r in results] == ["ok"] * world
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("peer", [False, True])
+def test_df11_shards_match_bf16_shards_on_two_gpus(tmp_path, peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     tp.compress_model_tp(tiny_llama(), LLAMA_PATTERNS, str(tmp_path), tp_size=2)
-    results = _run_ranks(2, use_cuda=True, path=str(tmp_path))
+    results = _run_ranks(2, use_cuda=True, path=str(tmp_path), peer=peer)
     for _, identical, err in results:
         assert identical                            # same TP degree: bit-identical logits
         assert err < 0.25                           # and close to the unsharded BF16 model
