@@ -50,7 +50,7 @@ constexpr int kWarps = kThreads / 32;
 #define DF11_FAST_TABLE_BITS 12
 #endif
 #ifndef DF11_FAST_MIN_CTAS
-#define DF11_FAST_MIN_CTAS 4
+#define DF11_FAST_MIN_CTAS 2
 #endif
 #ifndef DF11_GEMV_THREADS
 #define DF11_GEMV_THREADS 1024
@@ -70,8 +70,11 @@ constexpr int kInBufBytes = kCodesBufBytes + DF11_GAP_BYTES_PER_BLOCK;  // strea
 constexpr uint32_t kWaitPolls = 1u << 20;
 constexpr uint64_t kWaitNs = 50ull * 1000 * 1000;
 constexpr uint64_t kDrainNs = 200ull * 1000 * 1000;
+// Two CTAs of 512 threads per SM: with 32-byte stores, two copies of the decode table per SM beat
+// four (measured on one Llama-8B block: 256 x 4 5 388 GB/s, 512 x 2 5 491, 1024 x 1 with a 2^14-entry
+// table 5 487, 512 x 2 with 2^13 entries 5 451).
 #ifndef DF11_FAST_THREADS
-#define DF11_FAST_THREADS 256
+#define DF11_FAST_THREADS 512
 #endif
 constexpr int kFastThreads = DF11_FAST_THREADS;
 // The fused product runs one CTA of 1024 threads per SM: its launches are short, and one copy of

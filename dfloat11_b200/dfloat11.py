@@ -59,6 +59,7 @@ class _Flags:
     check_status = False
     slab_head = True
     side_on_host = True
+    offload_prepared = False
 
     @classmethod
     def read(cls) -> None:
@@ -71,6 +72,7 @@ class _Flags:
         cls.check_status = env("DF11_CHECK_STATUS", "0") == "1"
         cls.slab_head = env("DF11_SLAB_HEAD", "1") != "0"
         cls.side_on_host = env("DF11_SIDE_TENSORS_ON_HOST", "1") != "0"
+        cls.offload_prepared = env("DF11_OFFLOAD_PREPARED", "0") == "1"
 
     @classmethod
     def current(cls):
@@ -367,7 +369,7 @@ class _DecodeAhead:
             return
         n_next = nxt.sign_mantissa.numel()
         n_this = module.sign_mantissa.numel() if not hasattr(module, "offloaded_tensors") else n_next
-        ctas = int(os.environ.get("DF11_AHEAD_CTAS", "2"))
+        ctas = int(os.environ.get("DF11_AHEAD_CTAS", "1"))
         if light or n_next > 2 * n_this:
             ctas = 0                                   # nothing to share the GPU with: full speed
         slot = self.slot ^ 1
@@ -764,7 +766,13 @@ def get_hook(threads_per_block, bytes_per_thread):
         n_elements = sign_mantissa.numel()
         widest = getattr(module, "max_block_elems", 0)
 
-        if flags.prepared:
+        # An offloaded unit is bound by its host -> device copy (some 55 GB/s against 2 000 for the
+        # slowest decoder), so it takes the self-contained kernel and keeps no auxiliary buffer on
+        # the device: that is what offloading is for.  Units whose partial decode needs seek points
+        # (a slab-wise head, a lookup table) keep theirs; DF11_OFFLOAD_PREPARED=1 gives every unit one.
+        prepared = flags.prepared and (stager is None or flags.offload_prepared or d.get("df11_slabbed")
+                                       or isinstance(module, nn.Embedding) or d.get("df11_aux") is not None)
+        if prepared:
             aux = d.get("df11_aux")
             if aux is None or aux.device != device:
                 # once per unit and device: decode table + seek points (derived data, never saved)

@@ -206,8 +206,8 @@ int df11_gemv_prepared(const void *luts, const void *codes, const void *sign_man
 /*
  * df11_decode_prepared for a launch that is meant to run BESIDE other kernels: the decode
  * of the next transformer block on a second stream while the current block computes.  The
- * fast decoder is a persistent kernel that otherwise fills every SM (4 CTAs of 256 threads),
- * so kernels of other streams would wait for it to end; `ctas_per_sm` (1..4, 0 = all) caps
+ * fast decoder is a persistent kernel that otherwise fills every SM (2 CTAs of 512 threads),
+ * so kernels of other streams would wait for it to end; `ctas_per_sm` (1, or 0 = all) caps
  * the CTAs it places per SM and leaves the rest of each SM to them.  Same arguments, result
  * and bits as df11_decode_prepared.  No counterpart in the reference, which decodes in the
  * stream of the forward pass and overwrites one buffer (dfloat11.py:119-151).

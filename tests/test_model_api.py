@@ -501,7 +501,12 @@ def test_large_head_is_multiplied_slab_by_slab(monkeypatch, offload):
         assert staged > 0 and "df11_next_offloaded" not in model.model.embed_tokens.__dict__
         assert all(s["owner"] is not model.model.embed_tokens for s in host._OffloadStager.get(dev).slots)
         assert emb["sign_mantissa"].is_pinned() and model.model.embed_tokens.weight.shape[0] <= 18
-    assert not model.model.layers[0].gaps.is_cuda                        # parked on the host after prepare
+    block = model.model.layers[0]
+    if offload:          # bound by its host -> device copy: self-contained kernel, no auxiliary buffer on the device
+        assert block.__dict__.get("df11_aux") is None and block.gaps.is_cuda
+        assert model.lm_head.__dict__.get("df11_aux") is not None        # the slab-wise head keeps its seek points
+    else:                # side tensors parked on the host once the auxiliary buffer exists
+        assert block.__dict__.get("df11_aux") is not None and not block.gaps.is_cuda
     host.TensorManager.release()
 
 
