@@ -61,7 +61,7 @@ WORKLOADS = {"flux-dit": FLUX_DIT, "qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "
 
 # DRAM bytes per element of one df11_fast_kernel launch on a 192.9 M-element Qwen3-8B block unit,
 # from the ncu capture summarised in profiles/df11_fast_kernel_one_qwen3_block.md, by seek interval.
-DRAM_BYTES_PER_ELEMENT = {16: None, 32: None}
+DRAM_BYTES_PER_ELEMENT = {16: 3.190, 32: None}
 
 
 def block_shapes(cfg):
@@ -385,6 +385,8 @@ def main():
     ap.add_argument("--slab-pipeline", action="store_true",
                     help="only: one block's batch-1 products with the weights decompressed slab by slab right "
                          "before each product (L2-resident) against decode-the-whole-block")
+    ap.add_argument("--eager", action="store_true",
+                    help="with --slab-pipeline: one untimed pass of each variant without CUDA graphs, for a profiler")
     ap.add_argument("--layers", type=int, default=0,
                     help="with --generation on the partitioned workload: transformer layers to build (0 = as many as fit)")
     ap.add_argument("--new-tokens", type=int, default=512)
@@ -560,30 +562,36 @@ def main():
         if e2e is not None:
             result["e2e"] = e2e
         if not args.skip_extras:
+            def extra(key, fn):                             # an extra leg that fails is reported, the line still prints
+                try:
+                    result[key] = fn()
+                except Exception as exc:  # noqa: BLE001
+                    result[key] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
             block = next(u for u, (name, _, _) in zip(units, plan) if name == "layers.0")
-            result["reference_gpu_kernel"] = time_reference_gpu_kernel(block, scratch)
-            from oracle import df11_oracle as oracle
-            oracle.build()
-            cores = oracle.max_threads()
-            mean, checksum = cpu_decode_sample(block["host"], cores, repeats=5, warmup=1)
-            one, _ = cpu_decode_sample(block["host"], 1, repeats=1)
-            ok = checksum == block["checksum"]
-            result["cpu_baseline"] = {
-                "value": round(algorithmic_bytes(block) / mean / 1e9, 3), "unit": "GB/s", "cores": cores,
-                "kind": "port", "single_core_GBps": round(algorithmic_bytes(block) / one / 1e9, 3),
-                "bit_exact": ok,
-                "sample": f"one transformer-block unit ({block['n_elements']} elements), mean of 5 decodes after "
-                          f"1 untimed, {cores} threads; CPU restatement of the reference decode rule "
-                          "(the reference has no CPU decoder)",
-                "compress": cpu_compress_sample(),
-            }
+            extra("reference_gpu_kernel", lambda: time_reference_gpu_kernel(block, scratch))
+
+            def cpu_legs():
+                from oracle import df11_oracle as oracle
+                oracle.build()
+                cores = oracle.max_threads()
+                mean, checksum = cpu_decode_sample(block["host"], cores, repeats=5, warmup=1)
+                one, _ = cpu_decode_sample(block["host"], 1, repeats=1)
+                return {
+                    "value": round(algorithmic_bytes(block) / mean / 1e9, 3), "unit": "GB/s", "cores": cores,
+                    "kind": "port", "single_core_GBps": round(algorithmic_bytes(block) / one / 1e9, 3),
+                    "bit_exact": checksum == block["checksum"],
+                    "sample": f"one transformer-block unit ({block['n_elements']} elements), mean of 5 decodes after "
+                              f"1 untimed, {cores} threads; CPU restatement of the reference decode rule "
+                              "(the reference has no CPU decoder)",
+                    "compress": cpu_compress_sample(),
+                }
+
+            extra("cpu_baseline", cpu_legs)
             if world == 1 and cfg.get("vocab"):
                 del units, u, block
                 scratch = None
-                try:
-                    result["generation"] = generation_block(cfg, device)
-                except Exception as exc:                    # report, do not hide
-                    result["generation"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+                extra("generation", lambda: generation_block(cfg, device))
         print(json.dumps(result))
     if world > 1:
         import torch.distributed as dist
@@ -1351,6 +1359,20 @@ def run_slab_pipeline(args, cfg):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / args.steps / n_blocks
 
+    if args.eager:
+        # for a profiler: block 1's products once the plain way, once in 48 MB slabs, launched one by
+        # one (no graph, no timing); blocks 2 and 3 in between push block 1's leftovers out of L2
+        for fn in (whole, slabbed(48)[0]):
+            fn(1)
+            fn(2)
+            fn(3)
+            torch.cuda.synchronize()
+            torch.cuda.nvtx.range_push("measured")
+            fn(1)
+            torch.cuda.synchronize()
+            torch.cuda.nvtx.range_pop()
+        print(json.dumps({"eager": True, "order": ["decode whole + 7 products", "48 MB slabs: 8 decodes + 10 products"]}))
+        return
     bf16_block(0)
     want = [o.clone() for o in outs]
     result = {"metric": "batch1_block_products_ms", "unit": "ms per block", "workload": cfg["name"],
