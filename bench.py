@@ -771,7 +771,15 @@ def run_generation(args, cfg):
         torch.cuda.reset_peak_memory_stats()
         out_df11, t_df11 = timed_generate()
         mem_df11 = torch.cuda.max_memory_allocated() / 1e9
-        stats = _OffloadStager.get(dev).stats
+        stager = _OffloadStager.get(dev)
+        stats = stager.stats
+        held = {"staging_slots": sum(b.numel() for slot in stager.slots for b in slot["buf"].values()),
+                "scratch": sum(t.numel() * 2 for t in df11.TensorManager._tensors.values()),
+                "seek_points_and_tables": sum(m.__dict__["df11_aux"].numel() for m in model.modules()
+                                              if m.__dict__.get("df11_aux") is not None),
+                "gaps_positions_luts": sum(getattr(m, k).numel() for m in model.modules() if hasattr(m, "luts")
+                                           for k in ("gaps", "output_positions", "luts") if getattr(m, k).is_cuda)}
+        held["everything_else"] = torch.cuda.memory_allocated() - sum(held.values())
         tokens = args.batch * args.new_tokens
         print(json.dumps({
             "metric": "offload_generation_tok_per_s", "unit": "tok/s", "workload": cfg["name"], "batch": args.batch,
@@ -781,6 +789,7 @@ def run_generation(args, cfg):
             "df11_offload_s_per_step": round(t_df11 / args.new_tokens, 4),
             "identical_tokens": bool(torch.equal(out_bf16, out_df11)),
             "peak_mem_GB": {"bf16_resident": round(mem_bf16, 2), "df11_offload": round(mem_df11, 2)},
+            "df11_device_memory_after_GB": {k: round(v / 1e9, 3) for k, v in held.items()},
             "h2d_GB": round(stats["h2d_bytes"] / 1e9, 2), "prefetch_hits": stats["prefetch_hits"], "data": "synthetic",
         }))
         return
