@@ -422,7 +422,7 @@ def _mark_root(model: nn.Module) -> None:
     # offloaded units in definition (= forward) order; a lookup table that can be read row by row out
     # of pinned memory is never staged, so it is not part of the ring
     ring = [m for m in units if hasattr(m, "offloaded_tensors")
-            and not (isinstance(m, nn.Embedding) and m.max_norm is None and m.embedding_dim % 1024 == 0)]
+            and not (isinstance(m, nn.Embedding) and m.max_norm is None and m.embedding_dim % ops.chunk_elements() == 0)]
     for a, b in zip(ring, ring[1:] + ring[:1]):
         a.__dict__["df11_next_offloaded"] = b          # a plain reference, not a registered submodule
     if not model.__dict__.get("df11_root_hooked"):
@@ -487,11 +487,12 @@ FUSED_MAX_ROWS = 4          # activation vectors one fused product takes (df11_g
 def _fused_layers(module: nn.Module):
     """(layer, first element of its weight inside the unit) for every Linear of a unit, or None
     when the unit cannot take the fused product (a lookup table, rows that are not multiples
-    of 512 elements, tensors kept on the host)."""
+    of a chunk -- 512 or 1024 elements, tensors kept on the host)."""
     if hasattr(module, "offloaded_tensors") or isinstance(module, nn.Embedding):
         return None
     layers = [module] if isinstance(module, nn.Linear) else list(getattr(module, "weight_injection_modules", []))
-    if not layers or not all(isinstance(l, nn.Linear) and l.in_features % 512 == 0 for l in layers):
+    chunk = ops.chunk_elements()
+    if not layers or not all(isinstance(l, nn.Linear) and l.in_features % chunk == 0 for l in layers):
         return None
     starts = [0] + list(module.split_positions)
     if len(starts) != len(layers):

@@ -34,7 +34,16 @@ def test_version_and_sizes():
     small = _lib.lib.df11_aux_bytes(1000, 4000)
     big = _lib.lib.df11_aux_bytes(10 ** 8, 4 * 10 ** 8)
     assert 0 < small < big
-    assert abs(big - 4 * 10 ** 8 * 68 / 512) < 10 ** 6          # ~0.133 bytes per element
+    interval = _lib.lib.df11_seek_interval(0)
+    assert interval in (16, 32)
+    assert abs(big - 4 * 10 ** 8 * 68 / (32 * interval)) < 10 ** 6   # 0.133 bytes per element at 16, 0.066 at 32
+    assert _lib.lib.df11_seek_interval(16) == 16
+    at16 = _lib.lib.df11_aux_bytes(10 ** 8, 4 * 10 ** 8)
+    assert _lib.lib.df11_seek_interval(32) == 32
+    at32 = _lib.lib.df11_aux_bytes(10 ** 8, 4 * 10 ** 8)
+    assert at32 < 0.51 * at16                                   # half the seek points (the table stays)
+    assert _lib.lib.df11_seek_interval(24) == _lib.DF11_ERR_BADARG
+    _lib.lib.df11_seek_interval(interval)
     assert _lib.lib.df11_aux_bytes(-1, 0) == _lib.DF11_ERR_BADARG
 
 

@@ -46,6 +46,15 @@ def tiny_llama(seed=0, attention_bias=False, bias_seed=None):
     return model
 
 
+@pytest.fixture
+def seek16():
+    """Rows of 512 elements are whole chunks only with a seek point every 16 elements."""
+    before = df11.seek_interval()
+    df11.seek_interval(16)
+    yield
+    df11.seek_interval(before)
+
+
 @pytest.fixture(scope="module")
 def saved(tmp_path_factory):
     model = tiny_llama()
@@ -230,7 +239,7 @@ def test_placement_moves_structured_outputs_and_keeps_their_type():
     assert _first_tensor_device((1, "x"), {}) is None
 
 
-def test_fused_product_groups_follow_the_layer_families():
+def test_fused_product_groups_follow_the_layer_families(seek16):
     """q/k/v and gate/up of a block are served by one stacked product each; o and down stand alone;
     a unit whose rows are not multiples of 512 elements, a lookup table or an offloaded unit take no
     fused product at all."""
@@ -419,7 +428,7 @@ def test_compress_model_self_check_and_single_file(tmp_path):
 
 
 @pytest.mark.gpu
-def test_embedding_unit_decodes_only_looked_up_rows(tmp_path, monkeypatch):
+def test_embedding_unit_decodes_only_looked_up_rows(tmp_path, monkeypatch, seek16):
     torch.manual_seed(5)
     emb = nn.Embedding(2000, 512).to(torch.bfloat16)
     reference = copy.deepcopy(emb).to("cuda:0")
@@ -535,7 +544,7 @@ def test_row_slabs_of_a_product_have_the_bits_of_the_whole_product(rows, cols):
 
 
 @pytest.mark.gpu
-def test_fused_products_for_single_token_steps(monkeypatch):
+def test_fused_products_for_single_token_steps(monkeypatch, seek16):
     """DF11_FUSED_GEMV=1: a forward over a few tokens multiplies straight from the compressed
     weights (same exact products, fp32 sums in another order than the library GEMV: logits
     agree to BF16 rounding, not bit for bit); a longer forward decompresses as usual and stays
