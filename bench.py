@@ -61,7 +61,7 @@ WORKLOADS = {"flux-dit": FLUX_DIT, "qwen3-8b": QWEN3_8B, "llama-8b": LLAMA_8B, "
 
 # DRAM bytes per element of one df11_fast_kernel launch on a 192.9 M-element Qwen3-8B block unit,
 # from the ncu capture summarised in profiles/df11_fast_kernel_one_qwen3_block.md, by seek interval.
-DRAM_BYTES_PER_ELEMENT = {16: 3.190, 32: None}
+DRAM_BYTES_PER_ELEMENT = {16: 3.190, 32: 3.144}
 
 
 def block_shapes(cfg):
