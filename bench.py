@@ -382,6 +382,9 @@ def main():
                     help="with --generation: DF11 with cpu_offload=True at --batch sequences against resident BF16")
     ap.add_argument("--dit-step", action="store_true",
                     help="only: one denoising step of the FLUX.1-dev-shaped transformer, DF11 against BF16")
+    ap.add_argument("--loader", action="store_true",
+                    help="only: seconds to load a saved DF11 model (--layers blocks of the workload's shape) with this "
+                         "package's loader and the reference's way")
     ap.add_argument("--slab-pipeline", action="store_true",
                     help="only: one block's batch-1 products with the weights decompressed slab by slab right "
                          "before each product (L2-resident) against decode-the-whole-block")
@@ -408,6 +411,9 @@ def main():
         return
     if args.dit_step:
         run_dit_step(args)
+        return
+    if args.loader:
+        run_loader(args, cfg)
         return
     if args.slab_pipeline:
         run_slab_pipeline(args, cfg)
@@ -1219,6 +1225,74 @@ def run_tp_generation(args, cfg):
         }))
     TensorManager.release()
     dist.destroy_process_group()
+
+
+def run_loader(args, cfg):
+    """Load time of a DF11 model directory: this package's loader (files memory-mapped, every large
+    tensor copied once -- through pinned staging and a copy stream to the GPU, or straight into
+    pinned memory of its own under cpu_offload) against the reference's way (dfloat11.py:215-219,
+    256-263: `safetensors.torch.load_file` of every file, then `pin_memory()` or a pageable
+    host -> device copy per tensor).  The model has the workload's shapes with `--layers` blocks
+    (default 8) plus embedding and head; files come from the page cache in both cases (each way is
+    run twice, the second run counts)."""
+    import copy
+    import dfloat11_b200 as df11
+    from safetensors.torch import load_file
+    dev = torch.device("cuda", 0)
+    layers = args.layers or 8
+    model, vocab = _random_init_model(cfg, dev, layers=layers)
+    tmp = tempfile.mkdtemp(prefix="df11_load_")
+    try:
+        t0 = time.time()
+        df11.compress_model(model, GEN_PATTERNS, tmp, save_single_file=False, check_correctness=False)
+        t_save = time.time() - t0
+        del model
+        torch.cuda.empty_cache()
+        files = sorted(f for f in os.listdir(tmp) if f.endswith(".safetensors"))
+        total = sum(os.path.getsize(os.path.join(tmp, f)) for f in files)
+
+        def ours(offload):
+            torch.cuda.synchronize()
+            t0 = time.time()
+            m = df11.DFloat11Model.from_pretrained(tmp, device="cuda:0", cpu_offload=offload)
+            torch.cuda.synchronize()
+            dt = time.time() - t0
+            del m
+            df11.TensorManager.release()
+            torch.cuda.empty_cache()
+            return dt
+
+        def reference_way(offload):
+            torch.cuda.synchronize()
+            t0 = time.time()
+            kept = []
+            for f in files:
+                for name, value in load_file(os.path.join(tmp, f)).items():
+                    leaf = name.rsplit(".", 1)[-1]
+                    if offload and leaf in ("encoded_exponent", "sign_mantissa"):
+                        kept.append(value.pin_memory())
+                    else:
+                        kept.append(value.to(dev))
+            torch.cuda.synchronize()
+            dt = time.time() - t0
+            del kept
+            torch.cuda.empty_cache()
+            return dt
+
+        out = {"metric": "df11_model_load_s", "unit": "s", "workload": cfg["name"], "layers": layers,
+               "files": len(files), "bytes": total, "save_s": round(t_save, 1), "data": "synthetic"}
+        for offload in (False, True):
+            ours(offload), reference_way(offload)
+            a, b = ours(offload), reference_way(offload)
+            key = "cpu_offload" if offload else "resident"
+            out[key] = {"this_loader_s": round(a, 3), "this_loader_GBps": round(total / a / 1e9, 2),
+                        "load_file_then_copy_s": round(b, 3), "load_file_then_copy_GBps": round(total / b / 1e9, 2),
+                        "note": "the first includes building the model skeleton and validating every unit; the second "
+                                "only reads and copies the tensors"}
+        print(json.dumps(out))
+    finally:
+        import shutil
+        shutil.rmtree(tmp, ignore_errors=True)
 
 
 def run_dit_step(args):
