@@ -595,7 +595,7 @@ def main():
 
             extra("cpu_baseline", cpu_legs)
             if world == 1 and cfg.get("vocab"):
-                del units, u, block
+                del units, u, block, out                    # `out` is a view of the scratch: it would keep it alive
                 scratch = None
                 extra("generation", lambda: generation_block(cfg, device))
         print(json.dumps(result))
@@ -1262,6 +1262,27 @@ def run_loader(args, cfg):
             torch.cuda.empty_cache()
             return dt
 
+        def ours_tensors_only(offload):
+            # the loader proper, on a skeleton built beforehand (what from_pretrained does first)
+            from transformers import AutoConfig, AutoModelForCausalLM
+            try:
+                from transformers.initialization import no_init_weights
+            except ImportError:
+                from transformers.modeling_utils import no_init_weights
+            config = AutoConfig.from_pretrained(tmp)
+            with no_init_weights():
+                skeleton = AutoModelForCausalLM.from_config(config, dtype=torch.bfloat16).eval()
+            torch.cuda.synchronize()
+            t0 = time.time()
+            df11.load_and_replace_tensors(skeleton, tmp, config.dfloat11_config, cpu_offload=offload, device="cuda:0")
+            skeleton.to("cuda:0")
+            torch.cuda.synchronize()
+            dt = time.time() - t0
+            del skeleton
+            df11.TensorManager.release()
+            torch.cuda.empty_cache()
+            return dt
+
         def reference_way(offload):
             torch.cuda.synchronize()
             t0 = time.time()
@@ -1282,13 +1303,14 @@ def run_loader(args, cfg):
         out = {"metric": "df11_model_load_s", "unit": "s", "workload": cfg["name"], "layers": layers,
                "files": len(files), "bytes": total, "save_s": round(t_save, 1), "data": "synthetic"}
         for offload in (False, True):
-            ours(offload), reference_way(offload)
-            a, b = ours(offload), reference_way(offload)
+            ours(offload), reference_way(offload), ours_tensors_only(offload)
+            a, b, c = ours(offload), reference_way(offload), ours_tensors_only(offload)
             key = "cpu_offload" if offload else "resident"
-            out[key] = {"this_loader_s": round(a, 3), "this_loader_GBps": round(total / a / 1e9, 2),
+            out[key] = {"from_pretrained_s": round(a, 3),
+                        "load_and_replace_tensors_s": round(c, 3), "load_and_replace_tensors_GBps": round(total / c / 1e9, 2),
                         "load_file_then_copy_s": round(b, 3), "load_file_then_copy_GBps": round(total / b / 1e9, 2),
-                        "note": "the first includes building the model skeleton and validating every unit; the second "
-                                "only reads and copies the tensors"}
+                        "note": "from_pretrained also builds the skeleton; load_and_replace_tensors reads, copies, "
+                                "validates and arms every unit; the last only reads and copies the tensors"}
         print(json.dumps(out))
     finally:
         import shutil

@@ -82,7 +82,7 @@ class MappedFile:
         raw = self.raw(name)
         out = torch.empty(raw.size, dtype=torch.uint8, pin_memory=pin and torch.cuda.is_available())
         if raw.size:
-            out.numpy()[:] = raw
+            out.copy_(torch.from_numpy(raw))              # torch's host copy runs on several threads
         return out.view(self.torch_dtype(name)).reshape(self.shape(name))
 
     def close(self) -> None:
@@ -129,7 +129,7 @@ class DeviceUploader:
             if self._busy[k] is not None:
                 self._busy[k].synchronize()                   # the copy that last read this buffer is over
             piece = min(n - done, self._staging[k].numel())
-            self._staging[k].numpy()[:piece] = raw[done:done + piece]
+            self._staging[k][:piece].copy_(torch.from_numpy(raw[done:done + piece]))
             with torch.cuda.stream(self.stream):
                 out[done:done + piece].copy_(self._staging[k][:piece], non_blocking=True)
                 self._busy[k] = torch.cuda.Event()
