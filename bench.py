@@ -786,6 +786,8 @@ def run_generation(args, cfg):
                 "gaps_positions_luts": sum(getattr(m, k).numel() for m in model.modules() if hasattr(m, "luts")
                                            for k in ("gaps", "output_positions", "luts") if getattr(m, k).is_cuda)}
         held["everything_else"] = torch.cuda.memory_allocated() - sum(held.values())
+        largest = sorted((b["size"] for seg in torch.cuda.memory_snapshot() for b in seg["blocks"]
+                          if b["state"] == "active_allocated" and b["size"] >= 64 << 20), reverse=True)
         tokens = args.batch * args.new_tokens
         print(json.dumps({
             "metric": "offload_generation_tok_per_s", "unit": "tok/s", "workload": cfg["name"], "batch": args.batch,
@@ -796,6 +798,7 @@ def run_generation(args, cfg):
             "identical_tokens": bool(torch.equal(out_bf16, out_df11)),
             "peak_mem_GB": {"bf16_resident": round(mem_bf16, 2), "df11_offload": round(mem_df11, 2)},
             "df11_device_memory_after_GB": {k: round(v / 1e9, 3) for k, v in held.items()},
+            "allocator_blocks_over_64MB_after": [round(x / 2 ** 20) for x in largest[:8]],
             "h2d_GB": round(stats["h2d_bytes"] / 1e9, 2), "prefetch_hits": stats["prefetch_hits"], "data": "synthetic",
         }))
         return
