@@ -671,3 +671,38 @@ def test_diffusion_transformer_with_the_flux_pattern_dictionary(tmp_path, offloa
             assert torch.equal(model(x, ctx, cond), reference(x, ctx, cond))
     assert len(model.transformer_blocks[0].weight_injection_modules) == 14
     assert not isinstance(model.transformer_blocks[1].attn.to_out[0].weight, nn.Parameter)   # an injected view
+
+
+def test_mapped_safetensors_reader_round_trips_every_dtype(tmp_path):
+    """`safetensors_io.MappedFile` against `safetensors.torch.save_file` / `load_file`: names in
+    file order, shapes, dtypes (BF16 included, which numpy does not know) and bytes; a tensor
+    taken out owns its memory; malformed files are refused."""
+    from safetensors.torch import load_file, save_file
+    from dfloat11_b200.safetensors_io import MappedFile
+    g = torch.Generator().manual_seed(0)
+    tensors = {
+        "a.bf16": torch.randn(33, 7, generator=g).to(torch.bfloat16),
+        "b.u8": torch.randint(0, 256, (1000,), generator=g, dtype=torch.uint8),
+        "c.f32": torch.randn(5, generator=g),
+        "d.i64": torch.arange(12).view(3, 4),
+        "e.f16": torch.randn(2, 2, 2, generator=g).to(torch.float16),
+        "f.empty": torch.zeros(0, dtype=torch.uint8),
+    }
+    path = str(tmp_path / "t.safetensors")
+    save_file(tensors, path)
+    want = load_file(path)
+    with MappedFile(path) as mapped:
+        assert set(mapped.names()) == set(tensors)
+        for name in mapped.names():
+            got = mapped.tensor(name)
+            assert got.dtype == want[name].dtype and got.shape == want[name].shape
+            assert torch.equal(got.view(torch.uint8), want[name].view(torch.uint8) if want[name].numel() else got.view(torch.uint8))
+            assert mapped.nbytes(name) == want[name].numel() * want[name].element_size()
+        kept = mapped.tensor("a.bf16")
+    assert torch.equal(kept, tensors["a.bf16"])                  # still valid after the mapping is closed
+    for bad in (b"", b"\x10\x00\x00\x00\x00\x00\x00\x00{}", (10 ** 6).to_bytes(8, "little") + b"{}"):
+        broken = str(tmp_path / "broken.safetensors")
+        with open(broken, "wb") as f:
+            f.write(bad)
+        with pytest.raises((ValueError, OSError)):
+            MappedFile(broken)
