@@ -35,7 +35,13 @@ class PeerAllReduce:
     _instances: Dict[tuple, Optional["PeerAllReduce"]] = {}
 
     def __init__(self, group, device: torch.device, slot_bytes: int = SLOT_BYTES):
+        import os
         import torch.distributed as dist
+        # The kernel uses plain peer loads and stores only.  Binding the buffers to an NVLink
+        # multicast object as well (what the symmetric-memory rendezvous does when the hardware
+        # offers it) would buy nothing here and ties the ranks' memory together beyond the life
+        # of a single rank, so it is switched off unless the caller has decided otherwise.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group
         self.world = dist.get_world_size(group)
