@@ -1105,6 +1105,7 @@ def tp_block(args, rank, world, device):
                 "ms_per_step": round(ms_peer, 3), "per_gpu_GBps": round(total_p / ms_peer / 1e6 / world, 1),
                 "per_gpu_frac_of_measured_peak": round(total_p / ms_peer / 1e6 / world / peak_p, 4),
                 "us_per_all_reduce_back_to_back": round(ms_peer_alone * 1e3 / (2 * layers), 2),
+                "buffers_bound_to_a_multicast_object": peer.multicast_bound,
                 "cuda_graph": {"ms_per_step": round(ms_peer_graph, 3),
                                "per_gpu_GBps": round(total_p / ms_peer_graph / 1e6 / world, 1),
                                "per_gpu_frac_of_measured_peak": round(total_p / ms_peer_graph / 1e6 / world / peak_p, 4)}}

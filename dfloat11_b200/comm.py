@@ -55,6 +55,10 @@ class PeerAllReduce:
         self.buffer.zero_()
         torch.cuda.synchronize(device)
         self.handle = symm_mem.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
+        try:
+            self.multicast_bound = bool(self.handle.multicast_ptr)      # 0 when no multicast object was made
+        except Exception:  # noqa: BLE001 - informational only
+            self.multicast_bound = None
         pointers = [int(p) for p in self.handle.buffer_ptrs]
         self._data = (ctypes.c_uint64 * 8)(*(pointers + [0] * (8 - len(pointers))))
         self._flags = (ctypes.c_uint64 * 8)(*([p + 2 * self.slot_bytes for p in pointers] + [0] * (8 - len(pointers))))
