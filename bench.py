@@ -540,7 +540,10 @@ def main():
     }
     tp_result = None
     if world > 1 and not args.skip_extras and not cfg.get("tp"):
-        tp_result = tp_block(args, rank, world, device)
+        try:
+            tp_result = tp_block(args, rank, world, device)
+        except Exception as exc:                            # report, do not lose the line
+            tp_result = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     if rank == 0:
         peak, how = measured_hbm_peak()
         per_gpu = step_bytes / ms / 1e6
@@ -1076,8 +1079,10 @@ def tp_block(args, rank, world, device):
     try:
         from dfloat11_b200.comm import PeerAllReduce
         peer = PeerAllReduce.get(None, device)
-        if peer is None:
-            peer_result = {"unavailable": "symmetric memory could not be set up"}
+        agreed = torch.tensor([int(peer is not None)], device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)       # every rank takes the same branch below
+        if not int(agreed.item()):
+            peer_result = {"unavailable": "symmetric memory could not be set up on every rank"}
         else:
             def step_peer():
                 for u in units:
