@@ -75,12 +75,18 @@ class PeerAllReduce:
         symmetric memory cannot be set up here (logged once; the caller uses the library collective)."""
         key = (id(group) if group is not None else None, device)
         if key not in cls._instances:
+            import torch.distributed as dist
             try:
-                cls._instances[key] = cls(group, device)
+                instance = cls(group, device)
             except Exception as exc:  # noqa: BLE001 - optional acceleration
                 log.warning("peer all-reduce unavailable (%s: %s); using torch.distributed.all_reduce",
                             type(exc).__name__, exc)
-                cls._instances[key] = None
+                instance = None
+            # all ranks or none: a rank that summed through the library while its peers wait in the
+            # kernel would leave them waiting
+            agreed = torch.tensor([int(instance is not None)], device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+            cls._instances[key] = instance if int(agreed.item()) else None
         return cls._instances[key]
 
     def all_reduce_(self, tensor: torch.Tensor) -> bool:
