@@ -1330,4 +1330,9 @@ def compress_in_place(model, pattern_dict: Dict[str, List[str]], cpu_offload: bo
             _finish_unit(sub_module, full_name)
             sub_module.register_forward_pre_hook(hook)
     _mark_root(model)
+    # A BF16 weight that is only kept alive by a reference cycle (module bookkeeping of the host
+    # framework) would otherwise stay allocated until the collector happens to run: a vocabulary-sized
+    # matrix, 1 GB and more, held beside the compressed model.
+    import gc
+    gc.collect()
     return model
