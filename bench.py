@@ -691,27 +691,11 @@ def run_generation(args, cfg):
     model object with its weights compressed in place.  Same harness, same attention
     implementation, same inputs; the generated ids must be identical."""
     import dfloat11_b200 as df11
-    from transformers import Qwen3Config, Qwen3ForCausalLM, LlamaConfig, LlamaForCausalLM
     dev = torch.device("cuda", 0)
-    common = dict(hidden_size=cfg["hidden"], intermediate_size=cfg["inter"], num_hidden_layers=cfg["layers"],
-                  num_attention_heads=cfg["hidden"] // 128, num_key_value_heads=cfg["kv"] // 128,
-                  vocab_size=max(cfg["vocab"], 1024), tie_word_embeddings=False, max_position_embeddings=4096)
-    torch.manual_seed(1)
-    old = torch.get_default_dtype()
-    torch.set_default_dtype(torch.bfloat16)
-    try:
-        with dev:
-            if "qwen" in cfg["name"]:
-                model = Qwen3ForCausalLM(Qwen3Config(head_dim=128, **common))
-            else:
-                model = LlamaForCausalLM(LlamaConfig(**common))
-    finally:
-        torch.set_default_dtype(old)
-    model.eval()
-    with torch.no_grad():
-        for name, p in model.named_parameters():
-            if p.dim() == 2:
-                p.normal_(0.0, 1.0 if "embed_tokens" in name else 0.02)
+    # built inside a helper: a loop variable left over from initialising the weights would keep the
+    # last parameter (the vocabulary-sized head) alive after the model has been compressed
+    model, vocab_size = _random_init_model(cfg, dev)
+    common = {"vocab_size": vocab_size}
     ids = torch.randint(0, common["vocab_size"], (args.batch if args.cpu_offload else 1, args.prompt_tokens), device=dev,
                         generator=torch.Generator(device=dev).manual_seed(2))
 
@@ -1208,6 +1192,7 @@ def run_tp_generation(args, cfg):
                 p.normal_(0.0, 1.0 if "embed_tokens" in name else 0.02, generator=g)
             else:
                 p.fill_(1.0)
+        del name, p                                          # or the last parameter (the head) outlives its compression
     ids = torch.randint(0, vocab, (args.batch, args.prompt_tokens), device=dev,
                         generator=torch.Generator(device=dev).manual_seed(2))   # the same prompts on every rank
 
