@@ -69,11 +69,15 @@ __device__ __forceinline__ uint32_t bf16x2_from_floats(float lo, float hi)  // r
     return one(lo) | (one(hi) << 16);
 }
 
+// WORLD > 0: the number of ranks is known at compile time, the loads of all ranks' vectors are
+// issued together (one NVLink round trip instead of one per rank); WORLD = 0: any number up to 8.
+template <int WORLD>
 __global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers peers, uint32_t *counters, int rank,
-                                                                  int world, const uint4 *in, uint4 *out, uint32_t n_vec,
-                                                                  uint32_t vec_per_cta, uint32_t slot_bytes,
-                                                                  uint64_t wait_ns, int *status)
+                                                                  int world_arg, const uint4 *in, uint4 *out,
+                                                                  uint32_t n_vec, uint32_t vec_per_cta,
+                                                                  uint32_t slot_bytes, uint64_t wait_ns, int *status)
 {
+    const int world = WORLD > 0 ? WORLD : world_arg;
     const uint32_t tid = threadIdx.x, cta = blockIdx.x;
     const uint32_t call = *reinterpret_cast<volatile uint32_t *>(counters);  // advanced by the last CTA to finish
     const uint32_t half = call & 1u;
@@ -103,16 +107,25 @@ __global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers pe
     const int all_ok = __syncthreads_and(ok ? 1 : 0);
     // 4. sum in rank order
     if (all_ok) {
+        auto add = [](float *acc, const uint4 &x) {
+            const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc[2 * k] += __uint_as_float(w[k] << 16);
+                acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+            }
+        };
         for (uint32_t v = v0 + tid; v < v1; v += kThreads) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int r = 0; r < world; ++r) {
-                const uint4 x = ld_volatile16(peers.data[r] + (size_t)half * slot_bytes + (size_t)v * 16);
-                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+            const size_t offset = (size_t)half * slot_bytes + (size_t)v * 16;
+            if (WORLD > 0) {
+                uint4 x[WORLD > 0 ? WORLD : 1];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    acc[2 * k] += __uint_as_float(w[k] << 16);
-                    acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
-                }
+                for (int r = 0; r < WORLD; ++r) x[r] = ld_volatile16(peers.data[r] + offset);  // all in flight together
+#pragma unroll
+                for (int r = 0; r < WORLD; ++r) add(acc, x[r]);
+            } else {
+                for (int r = 0; r < world; ++r) add(acc, ld_volatile16(peers.data[r] + offset));
             }
             out[v] = make_uint4(bf16x2_from_floats(acc[0], acc[1]), bf16x2_from_floats(acc[2], acc[3]),
                                 bf16x2_from_floats(acc[4], acc[5]), bf16x2_from_floats(acc[6], acc[7]));
@@ -163,13 +176,16 @@ extern "C" int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *pe
     if (prev != device && cudaSetDevice(device) != cudaSuccess)
         return df11_fail(DF11_ERR_CUDA, "cudaSetDevice(%d) failed", device);
     const uint32_t n_vec = (uint32_t)(n_elements / 8);
-    uint32_t ctas = (n_vec + 1023u) / 1024u;  // about two vectors per thread
+    uint32_t ctas = (n_vec + (uint32_t)kThreads - 1u) / (uint32_t)kThreads;  // one vector per thread
     if (ctas > (uint32_t)kMaxCtas) ctas = kMaxCtas;
     if (ctas < 1u) ctas = 1u;
     const uint32_t per = (n_vec + ctas - 1u) / ctas;
-    df11_allreduce_kernel<<<ctas, kThreads, 0, (cudaStream_t)stream>>>(
-        peers, (uint32_t *)counters, rank, world, (const uint4 *)in_bf16, (uint4 *)out_bf16, n_vec, per,
-        (uint32_t)slot_bytes, wait_ms > 0 ? (uint64_t)wait_ms * 1000000ull : kWaitNs, (int *)status);
+    const uint64_t wait_ns = wait_ms > 0 ? (uint64_t)wait_ms * 1000000ull : kWaitNs;
+    auto kernel = world == 2 ? df11_allreduce_kernel<2> : world == 4 ? df11_allreduce_kernel<4>
+                : world == 8 ? df11_allreduce_kernel<8> : df11_allreduce_kernel<0>;
+    kernel<<<ctas, kThreads, 0, (cudaStream_t)stream>>>(peers, (uint32_t *)counters, rank, world,
+                                                        (const uint4 *)in_bf16, (uint4 *)out_bf16, n_vec, per,
+                                                        (uint32_t)slot_bytes, wait_ns, (int *)status);
     const cudaError_t e = cudaGetLastError();
     if (prev >= 0 && prev != device) cudaSetDevice(prev);
     if (e != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
