@@ -4,7 +4,8 @@ After every row-parallel layer the ranks' partial outputs are summed: a ``[batch
 tensor, 32 KB at batch 1 for hidden 16384.  A library collective is pure latency at that size
 (some 25 microseconds through NCCL at eight ranks, two of them per transformer layer).
 ``df11_allreduce_bf16`` (``csrc/df11_allreduce.cu``) does it in one launch with plain peer loads
-and stores on buffers that every rank can address; this module sets those buffers up with
+and stores on buffers that every rank can address (up to 64 KB: every rank pushes its slice to
+all ranks as tagged 8-byte pairs, one NVLink crossing); this module sets those buffers up with
 torch's symmetric memory and keeps one set per process group and device.  The reference has no
 such mode at all (its only multi-GPU form places whole layers on different devices,
 dfloat11/dfloat11.py:455-460).

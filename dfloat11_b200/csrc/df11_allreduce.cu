@@ -15,6 +15,15 @@
 // recorded in a CUDA graph can be replayed.  Buffers alternate between two halves by call
 // parity: a rank can only be one call ahead of a peer (it needs the peer's flag of call s to
 // finish call s), so the half written in call s + 2 is no longer being read.
+//
+// Tensors of up to 64 KB on 1, 2, 4 or 8 ranks take a second, faster form with no flags, fences
+// or barriers at all (`df11_allreduce_ll_kernel`): every rank PUSHES its slice into every rank's
+// buffer as 8-byte pairs {4 bytes of data, call tag}; an 8-byte store arrives whole, so a pair
+// whose tag is this call's tag is this call's data.  A thread writes the pairs of its own 16
+// bytes to all ranks, polls the pairs of all ranks for the same 16 bytes in its own buffer
+// (bounded), sums them in rank order and writes the result: one NVLink crossing instead of
+// fence + flag round trip + data round trip.  (The same idea as the low-latency protocol of
+// collective libraries; written here from its published description.)
 // The reference has no counterpart: its only multi-GPU form places whole layers on different
 // devices (dfloat11/dfloat11.py:455-460).
 #include <cuda_runtime.h>
@@ -30,6 +39,12 @@ constexpr int kMaxCtas = 32;
 constexpr int kThreads = 512;
 constexpr uint64_t kWaitNs = 2000ull * 1000 * 1000;  // a peer that has not shown up after two seconds is not coming
 constexpr uint32_t kWaitPolls = 1u << 24;
+constexpr size_t kFlagBytes = (size_t)2 * kMaxCtas * kMaxRanks * sizeof(uint32_t);
+// pushed form: after the flags, two halves (call parity) of [rank][vector] cells of 32 bytes
+// (16 bytes of data as four {data, tag} pairs)
+constexpr int kLlThreads = 128;
+constexpr uint32_t kLlSlotVecs = 4096;                                   // 64 KB of data per rank and call
+constexpr size_t kLlHalfBytes = (size_t)kMaxRanks * kLlSlotVecs * 32;    // 1 MiB
 
 struct Peers {
     uint8_t *data[kMaxRanks];    // each rank's buffer: two halves of slot_bytes
@@ -51,6 +66,10 @@ __device__ __forceinline__ uint4 ld_volatile16(const void *p)
     uint4 v;
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
+}
+__device__ __forceinline__ void st_volatile16(void *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ uint64_t global_ns()
 {
@@ -145,9 +164,75 @@ __global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers pe
     }
 }
 
+// The pushed form: one 16-byte vector per thread, no shared state between threads.
+template <int WORLD>
+__global__ void __launch_bounds__(kLlThreads) df11_allreduce_ll_kernel(const Peers peers, const uint8_t *own,
+                                                                       uint32_t *counters, int rank, const uint4 *in, uint4 *out, uint32_t n_vec,
+                                                                       uint64_t wait_ns, int *status)
+{
+    const uint32_t call = *reinterpret_cast<volatile uint32_t *>(counters);
+    uint32_t tag = call + 1u;  // never 0: the buffers start zeroed
+    if (tag == 0u) tag = 1u;   // (the neighbouring calls' tags in the same half are 0xFFFFFFFF and 2)
+    const uint32_t v = blockIdx.x * kLlThreads + threadIdx.x;
+    const size_t half = kFlagBytes + (size_t)(call & 1u) * kLlHalfBytes;
+    bool ok = true;
+    if (v < n_vec) {
+        const uint4 x = in[v];
+        const size_t mine = half + ((size_t)rank * kLlSlotVecs + v) * 32;
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) {
+            uint8_t *cell = reinterpret_cast<uint8_t *>(peers.flags[r]) + mine;
+            st_volatile16(cell, x.x, tag, x.y, tag);
+            st_volatile16(cell + 16, x.z, tag, x.w, tag);
+        }
+        const uint8_t *cells = own + half + (size_t)v * 32;  // this rank's own area (= peers.flags[rank])
+        uint4 a[WORLD], b[WORLD];
+        const uint64_t t0 = global_ns();
+        ok = false;
+        for (uint32_t it = 0; it < kWaitPolls; ++it) {
+            bool all = true;
+#pragma unroll
+            for (int r = 0; r < WORLD; ++r) {
+                a[r] = ld_volatile16(cells + (size_t)r * kLlSlotVecs * 32);
+                b[r] = ld_volatile16(cells + (size_t)r * kLlSlotVecs * 32 + 16);
+                all &= a[r].y == tag && a[r].w == tag && b[r].y == tag && b[r].w == tag;
+            }
+            if (all) {
+                ok = true;
+                break;
+            }
+            if ((it & 63u) == 63u && global_ns() - t0 > wait_ns) break;
+        }
+        if (ok) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < WORLD; ++r) {  // rank order, fp32
+                const uint32_t w[4] = {a[r].x, a[r].z, b[r].x, b[r].z};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    acc[2 * k] += __uint_as_float(w[k] << 16);
+                    acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+                }
+            }
+            out[v] = make_uint4(bf16x2_from_floats(acc[0], acc[1]), bf16x2_from_floats(acc[2], acc[3]),
+                                bf16x2_from_floats(acc[4], acc[5]), bf16x2_from_floats(acc[6], acc[7]));
+        }
+    }
+    const int all_ok = __syncthreads_and(ok ? 1 : 0);
+    if (threadIdx.x == 0) {
+        if (!all_ok && status != nullptr) atomicOr(status, DF11_STATUS_TIMEOUT);
+        __threadfence();
+        if (atomicAdd(counters + 1, 1u) == gridDim.x - 1u) {  // the last CTA advances the call number
+            counters[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(counters) = call + 1u;
+        }
+    }
+}
+
 }  // namespace
 
-extern "C" int64_t df11_allreduce_flag_bytes(void) { return (int64_t)2 * kMaxCtas * kMaxRanks * sizeof(uint32_t); }
+extern "C" int64_t df11_allreduce_flag_bytes(void) { return (int64_t)(kFlagBytes + 2 * kLlHalfBytes); }
 
 extern "C" int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *peer_flags, void *counters, int32_t rank,
                                    int32_t world, const void *in_bf16, void *out_bf16, int64_t n_elements,
@@ -176,11 +261,22 @@ extern "C" int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *pe
     if (prev != device && cudaSetDevice(device) != cudaSuccess)
         return df11_fail(DF11_ERR_CUDA, "cudaSetDevice(%d) failed", device);
     const uint32_t n_vec = (uint32_t)(n_elements / 8);
+    const uint64_t wait_ns = wait_ms > 0 ? (uint64_t)wait_ms * 1000000ull : kWaitNs;
+    if (n_vec <= kLlSlotVecs && (world == 1 || world == 2 || world == 4 || world == 8)) {
+        auto kernel = world == 1 ? df11_allreduce_ll_kernel<1> : world == 2 ? df11_allreduce_ll_kernel<2>
+                    : world == 4 ? df11_allreduce_ll_kernel<4> : df11_allreduce_ll_kernel<8>;
+        kernel<<<(n_vec + kLlThreads - 1) / kLlThreads, kLlThreads, 0, (cudaStream_t)stream>>>(
+            peers, reinterpret_cast<const uint8_t *>(peers.flags[rank]), (uint32_t *)counters, rank, (const uint4 *)in_bf16,
+            (uint4 *)out_bf16, n_vec, wait_ns, (int *)status);
+        const cudaError_t e = cudaGetLastError();
+        if (prev >= 0 && prev != device) cudaSetDevice(prev);
+        if (e != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+        return DF11_OK;
+    }
     uint32_t ctas = (n_vec + (uint32_t)kThreads - 1u) / (uint32_t)kThreads;  // one vector per thread
     if (ctas > (uint32_t)kMaxCtas) ctas = kMaxCtas;
     if (ctas < 1u) ctas = 1u;
     const uint32_t per = (n_vec + ctas - 1u) / ctas;
-    const uint64_t wait_ns = wait_ms > 0 ? (uint64_t)wait_ms * 1000000ull : kWaitNs;
     auto kernel = world == 2 ? df11_allreduce_kernel<2> : world == 4 ? df11_allreduce_kernel<4>
                 : world == 8 ? df11_allreduce_kernel<8> : df11_allreduce_kernel<0>;
     kernel<<<ctas, kThreads, 0, (cudaStream_t)stream>>>(peers, (uint32_t *)counters, rank, world,

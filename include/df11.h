@@ -256,13 +256,19 @@ int df11_decode_static(const void *luts, const void *codes, const void *sign_man
  *   peer_data    HOST array [world] of device addresses: rank r's buffer of 2 * slot_bytes
  *                bytes in memory that every rank can address (symmetric memory, or IPC
  *                mappings), as seen from THIS process; entry `rank` is this rank's own
- *   peer_flags   HOST array [world]: rank r's flag area of df11_allreduce_flag_bytes() bytes,
- *                zeroed once before the first call on any rank
+ *   peer_flags   HOST array [world]: rank r's flag area of df11_allreduce_flag_bytes() bytes
+ *                (about 2 MiB: the flags, and the cells of the pushed form below), in the
+ *                same kind of memory, zeroed once before the first call on any rank
  *   counters     device, this rank only: two uint32, zeroed once (call number, CTAs done)
  *   in_bf16 / out_bf16   device, n_elements BF16 each (a multiple of 8; in == out is fine),
  *                16-byte aligned; n_elements * 2 <= slot_bytes
- *   wait_ms      how long a rank waits for its peers' data before it gives up, sets
- *                DF11_STATUS_TIMEOUT in `status` and leaves `out` untouched (<= 0: 2 s)
+ *   wait_ms      how long a rank waits for its peers' data before it gives up and sets
+ *                DF11_STATUS_TIMEOUT in `status`; `out` is then undefined (<= 0: 2 s)
+ * Two forms, chosen by size alone (so every rank chooses alike).  Up to 64 KB on 1, 2, 4 or 8
+ * ranks: every rank pushes its slice into every rank's flag area as 8-byte {data, call tag}
+ * pairs and sums what has arrived with this call's tag -- one NVLink crossing, no fence, flag
+ * or barrier.  Anything else: slices into the own data buffer, one flag per rank and CTA,
+ * peer loads.
  * The sum is taken in rank order in fp32 and rounded once: identical bits on every rank.
  * The call number is kept in `counters`, so a launch captured in a CUDA graph replays.
  * No counterpart in the reference (its only multi-GPU form places whole layers on
