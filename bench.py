@@ -1065,8 +1065,18 @@ def tp_block(args, rank, world, device):
         peer = PeerAllReduce.get(None, device)
         agreed = torch.tensor([int(peer is not None)], device=device)
         dist.all_reduce(agreed, op=dist.ReduceOp.MIN)       # every rank takes the same branch below
+        if int(agreed.item()):
+            # one call first: a rank whose peers do not answer gives up after two seconds, and then
+            # the timed loops (hundreds of calls) are not run at all
+            probe = torch.ones(args.batch * cfg["hidden"], dtype=torch.bfloat16, device=device)
+            fine = peer.all_reduce_(probe)
+            torch.cuda.synchronize(device)
+            fine = fine and int(peer.status.item()) == 0 and bool((probe == float(world)).all())
+            agreed = torch.tensor([int(fine)], device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            peer.status.zero_()
         if not int(agreed.item()):
-            peer_result = {"unavailable": "symmetric memory could not be set up on every rank"}
+            peer_result = {"unavailable": "symmetric memory could not be set up on every rank, or the first call failed"}
         else:
             def step_peer():
                 for u in units:
@@ -1097,7 +1107,8 @@ def tp_block(args, rank, world, device):
                 "buffers_bound_to_a_multicast_object": peer.multicast_bound,
                 "cuda_graph": {"ms_per_step": round(ms_peer_graph, 3),
                                "per_gpu_GBps": round(total_p / ms_peer_graph / 1e6 / world, 1),
-                               "per_gpu_frac_of_measured_peak": round(total_p / ms_peer_graph / 1e6 / world / peak_p, 4)}}
+                               "per_gpu_frac_of_measured_peak": round(total_p / ms_peer_graph / 1e6 / world / peak_p, 4),
+                               "us_per_all_reduce_in_step": round((ms_peer_graph - ms_without) * 1e3 / (2 * layers), 2)}}
     except Exception as exc:                                # report, do not hide
         peer_result = {"error": f"{type(exc).__name__}: {exc}"[:200]}
     ok = int(scratch.view(torch.int16).to(torch.int64).sum().item()) == first["checksum"] and status.item() == 0

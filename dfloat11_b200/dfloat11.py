@@ -25,6 +25,7 @@ import json
 import logging
 import os
 import re
+import sys
 import weakref
 from sys import stderr
 from typing import Dict, List, Optional, Union
@@ -166,8 +167,9 @@ def _status_word(device: torch.device) -> torch.Tensor:
 def check_status(reset: bool = True) -> None:
     """Raises ``DF11Error`` if a decode launched by the hooks since the last check met
     inconsistent tensors (bad table, bad positions, truncated block, timed-out copy) or an
-    embedding index outside its table.  Synchronises with the devices, so it is not called per
-    forward unless ``DF11_CHECK_STATUS=1`` is set."""
+    embedding index outside its table, or if a one-kernel all-reduce of the partitioned mode gave
+    up waiting for a peer.  Synchronises with the devices, so it is not called per forward unless
+    ``DF11_CHECK_STATUS=1`` is set."""
     names = {_lib.STATUS_BAD_TABLE: "bad table", _lib.STATUS_BAD_POSITIONS: "bad positions or index",
              _lib.STATUS_TRUNCATED: "truncated block", _lib.STATUS_TIMEOUT: "copy timed out"}
     for device, word in _status_words.items():
@@ -177,6 +179,11 @@ def check_status(reset: bool = True) -> None:
                 word.zero_()
             what = ", ".join(n for b, n in names.items() if bits & b) or "unknown"
             raise _lib.DF11Error(_lib.DF11_ERR_CORRUPT, f"decode on {device} reported status {bits} ({what})")
+    comm = sys.modules.get(__package__ + ".comm")       # only if the partitioned mode set it up
+    if comm is not None:
+        for instance in comm.PeerAllReduce._instances.values():
+            if instance is not None:
+                instance.check()
 
 
 def stats() -> dict:
