@@ -776,10 +776,14 @@ def run_generation(args, cfg):
         held["everything_else"] = torch.cuda.memory_allocated() - sum(held.values())
         largest = sorted((b["size"] for seg in torch.cuda.memory_snapshot() for b in seg["blocks"]
                           if b["state"] == "active_allocated" and b["size"] >= 64 << 20), reverse=True)
-        del model
+        stats = dict(stats)
+        del model, stager                                       # nothing of the DF11 run stays on the device
         df11.TensorManager.release()
         _OffloadStager._by_device.clear()
+        import gc
+        gc.collect()
         torch.cuda.empty_cache()
+        left_behind = torch.cuda.memory_allocated() / 1e9
         model, _ = _random_init_model(cfg, dev)
         model.load_state_dict(bf16_state)
         del bf16_state
@@ -797,6 +801,7 @@ def run_generation(args, cfg):
             "peak_mem_GB": {"bf16_resident": round(mem_bf16, 2), "df11_offload": round(mem_df11, 2)},
             "df11_device_memory_after_GB": {k: round(v / 1e9, 3) for k, v in held.items()},
             "allocator_blocks_over_64MB_after": [round(x / 2 ** 20) for x in largest[:8]],
+            "device_memory_left_before_bf16_GB": round(left_behind, 3),
             "h2d_GB": round(stats["h2d_bytes"] / 1e9, 2), "prefetch_hits": stats["prefetch_hits"], "data": "synthetic",
         }))
         return
