@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers pe
     const int world = WORLD > 0 ? WORLD : world_arg;
     const uint32_t tid = threadIdx.x, cta = blockIdx.x;
     const uint32_t call = *reinterpret_cast<volatile uint32_t *>(counters);  // advanced by the last CTA to finish
+    const uint32_t tag = call + 1u != 0u ? call + 1u : 1u;  // never 0: the flag areas start zeroed
     const uint32_t half = call & 1u;
     const uint32_t v0 = cta * vec_per_cta, v1 = min(n_vec, v0 + vec_per_cta);
     const uint32_t flag_index = (half * kMaxCtas + cta) * kMaxRanks;
@@ -111,12 +112,12 @@ __global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers pe
     // 2. tell every rank (myself included), 3. wait for every rank
     bool ok = true;
     if (tid < (uint32_t)world) {
-        st_release_sys(peers.flags[tid] + flag_index + rank, call + 1u);
+        st_release_sys(peers.flags[tid] + flag_index + rank, tag);
         const uint32_t *theirs = peers.flags[rank] + flag_index + tid;
         const uint64_t t0 = global_ns();
         ok = false;
         for (uint32_t it = 0; it < kWaitPolls; ++it) {
-            if (ld_acquire_sys(theirs) == call + 1u) {
+            if (ld_acquire_sys(theirs) == tag) {
                 ok = true;
                 break;
             }

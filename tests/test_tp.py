@@ -189,6 +189,18 @@ def _peer_worker(rank, world, port, q):
         torch.cuda.synchronize()
         ok &= bool((x == float(world) ** 6).all()) if world <= 2 else True
         inst.check()
+        # the call number wraps: the tag of the pushed form skips 0, the buffer halves keep alternating
+        torch.cuda.synchronize()
+        dist.barrier(device_ids=[rank])
+        inst.counters[0] = -3                                  # 0xFFFFFFFD, on every rank, nothing in flight
+        torch.cuda.synchronize()
+        dist.barrier(device_ids=[rank])
+        for k in range(6):
+            x = torch.full((40000 if k % 2 else 16384,), float(rank + 1 + k), dtype=torch.bfloat16, device=dev)  # both forms
+            assert inst.all_reduce_(x)
+            ok &= bool((x == float(sum(r + 1 + k for r in range(world)))).all())
+        ok &= int(inst.counters[0].item()) == 3
+        inst.check()
         q.put((rank, "ok" if ok else "wrong"))
     finally:
         dist.destroy_process_group()
