@@ -18,8 +18,8 @@ sharded BEFORE compression, because a Huffman stream cannot be re-cut without de
 
 Decompression itself never communicates: the collectives are the activation all-reduce after
 each row-parallel layer (two per transformer block), the all-reduce of the embedding lookup and
-the all-gather of the logits -- NCCL's, or, with ``DF11_PEER_ALLREDUCE=1``, for the activation
-all-reduce one kernel of this library over NVLink peer memory (``comm.py``).
+the all-gather of the logits -- NCCL's, or, with ``DF11_PEER_ALLREDUCE=1``, for the two
+all-reduces one kernel of this library over NVLink peer memory (``comm.py``).
 """
 from __future__ import annotations
 
@@ -151,7 +151,7 @@ def apply_tensor_parallel(model: nn.Module, pattern_dict: Dict[str, List[str]], 
 
     peer = [None, False]          # the one-kernel all-reduce over NVLink peer memory, set up at its first use
 
-    def all_reduce_output(_module, _inputs, output):
+    def sum_over_ranks(output):
         if own_all_reduce and output.is_cuda:
             if not peer[1]:
                 from .comm import PeerAllReduce
@@ -160,6 +160,9 @@ def apply_tensor_parallel(model: nn.Module, pattern_dict: Dict[str, List[str]], 
                 return output
         dist.all_reduce(output, group=group)
         return output
+
+    def all_reduce_output(_module, _inputs, output):
+        return sum_over_ranks(output)
 
     def local_ids(module, args):
         # ids of other ranks' rows look up row 0 here and are zeroed afterwards
@@ -172,8 +175,7 @@ def apply_tensor_parallel(model: nn.Module, pattern_dict: Dict[str, List[str]], 
 
     def sum_lookups(module, _inputs, output):
         output = output * module.__dict__.pop("df11_tp_mine").unsqueeze(-1).to(output.dtype)
-        dist.all_reduce(output, group=group)
-        return output
+        return sum_over_ranks(output)
 
     def gather_output(_module, _inputs, output):
         parts = [torch.empty_like(output) for _ in range(tp_size)]
