@@ -90,14 +90,16 @@ __device__ __forceinline__ uint32_t bf16x2_from_floats(float lo, float hi)  // r
 
 // WORLD > 0: the number of ranks is known at compile time, the loads of all ranks' vectors are
 // issued together (one NVLink round trip instead of one per rank); WORLD = 0: any number up to 8.
+// `cta` of `n_ctas`: this CTA's place among the CTAs that work for `rank` (the whole grid in the
+// real launch; one row of the grid when one launch plays all ranks, see the self-test below).
 template <int WORLD>
-__global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers peers, uint32_t *counters, int rank,
-                                                                  int world_arg, const uint4 *in, uint4 *out,
-                                                                  uint32_t n_vec, uint32_t vec_per_cta,
-                                                                  uint32_t slot_bytes, uint64_t wait_ns, int *status)
+__device__ __forceinline__ void flag_form(const Peers &peers, uint32_t *counters, int rank, int world_arg,
+                                          const uint4 *in, uint4 *out, uint32_t n_vec, uint32_t vec_per_cta,
+                                          uint32_t slot_bytes, uint64_t wait_ns, int *status, uint32_t cta,
+                                          uint32_t n_ctas)
 {
     const int world = WORLD > 0 ? WORLD : world_arg;
-    const uint32_t tid = threadIdx.x, cta = blockIdx.x;
+    const uint32_t tid = threadIdx.x;
     const uint32_t call = *reinterpret_cast<volatile uint32_t *>(counters);  // advanced by the last CTA to finish
     const uint32_t tag = call + 1u != 0u ? call + 1u : 1u;  // never 0: the flag areas start zeroed
     const uint32_t half = call & 1u;
@@ -157,7 +159,7 @@ __global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers pe
     __syncthreads();
     if (tid == 0) {
         __threadfence();
-        if (atomicAdd(counters + 1, 1u) == gridDim.x - 1u) {
+        if (atomicAdd(counters + 1, 1u) == n_ctas - 1u) {
             counters[1] = 0u;
             __threadfence();
             *reinterpret_cast<volatile uint32_t *>(counters) = call + 1u;
@@ -165,16 +167,26 @@ __global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers pe
     }
 }
 
+template <int WORLD>
+__global__ void __launch_bounds__(kThreads) df11_allreduce_kernel(const Peers peers, uint32_t *counters, int rank,
+                                                                  int world_arg, const uint4 *in, uint4 *out,
+                                                                  uint32_t n_vec, uint32_t vec_per_cta,
+                                                                  uint32_t slot_bytes, uint64_t wait_ns, int *status)
+{
+    flag_form<WORLD>(peers, counters, rank, world_arg, in, out, n_vec, vec_per_cta, slot_bytes, wait_ns, status,
+                     blockIdx.x, gridDim.x);
+}
+
 // The pushed form: one 16-byte vector per thread, no shared state between threads.
 template <int WORLD>
-__global__ void __launch_bounds__(kLlThreads) df11_allreduce_ll_kernel(const Peers peers, const uint8_t *own,
-                                                                       uint32_t *counters, int rank, const uint4 *in, uint4 *out, uint32_t n_vec,
-                                                                       uint64_t wait_ns, int *status)
+__device__ __forceinline__ void pushed_form(const Peers &peers, const uint8_t *own, uint32_t *counters, int rank,
+                                            const uint4 *in, uint4 *out, uint32_t n_vec, uint64_t wait_ns,
+                                            int *status, uint32_t cta, uint32_t n_ctas)
 {
     const uint32_t call = *reinterpret_cast<volatile uint32_t *>(counters);
     uint32_t tag = call + 1u;  // never 0: the buffers start zeroed
     if (tag == 0u) tag = 1u;   // (the neighbouring calls' tags in the same half are 0xFFFFFFFF and 2)
-    const uint32_t v = blockIdx.x * kLlThreads + threadIdx.x;
+    const uint32_t v = cta * kLlThreads + threadIdx.x;
     const size_t half = kFlagBytes + (size_t)(call & 1u) * kLlHalfBytes;
     bool ok = true;
     if (v < n_vec) {
@@ -223,7 +235,7 @@ __global__ void __launch_bounds__(kLlThreads) df11_allreduce_ll_kernel(const Pee
     if (threadIdx.x == 0) {
         if (!all_ok && status != nullptr) atomicOr(status, DF11_STATUS_TIMEOUT);
         __threadfence();
-        if (atomicAdd(counters + 1, 1u) == gridDim.x - 1u) {  // the last CTA advances the call number
+        if (atomicAdd(counters + 1, 1u) == n_ctas - 1u) {  // the last CTA advances the call number
             counters[1] = 0u;
             __threadfence();
             *reinterpret_cast<volatile uint32_t *>(counters) = call + 1u;
@@ -231,7 +243,99 @@ __global__ void __launch_bounds__(kLlThreads) df11_allreduce_ll_kernel(const Pee
     }
 }
 
+template <int WORLD>
+__global__ void __launch_bounds__(kLlThreads) df11_allreduce_ll_kernel(const Peers peers, const uint8_t *own,
+                                                                       uint32_t *counters, int rank, const uint4 *in,
+                                                                       uint4 *out, uint32_t n_vec,
+                                                                       uint64_t wait_ns, int *status)
+{
+    pushed_form<WORLD>(peers, own, counters, rank, in, out, n_vec, wait_ns, status, blockIdx.x, gridDim.x);
+}
+
+// All ranks played by ONE launch on one GPU (row y of the grid is rank y; a cooperative launch, so
+// that every CTA is resident while the rows wait for one another): the same code as above on
+// `world` buffers, flag areas, counters, inputs and outputs laid out one after another.
+struct Emulated {
+    uint8_t *data, *flags;       // [world] buffers of 2 * slot_bytes, [world] flag areas
+    uint32_t *counters;          // [world][2]
+    const uint4 *in;             // [world][n_vec]
+    uint4 *out;                  // [world][n_vec]
+};
+
+template <int WORLD, bool PUSHED>
+__global__ void __launch_bounds__(PUSHED ? kLlThreads : kThreads) df11_allreduce_emulated_kernel(
+    const Emulated e, uint32_t n_vec, uint32_t vec_per_cta, uint32_t slot_bytes, uint64_t wait_ns, int *status)
+{
+    const int rank = blockIdx.y;
+    Peers peers = {};
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+        peers.data[r] = e.data + (size_t)r * 2 * slot_bytes;
+        peers.flags[r] = reinterpret_cast<uint32_t *>(e.flags + (size_t)r * (kFlagBytes + 2 * kLlHalfBytes));
+    }
+    uint32_t *counters = e.counters + 2 * rank;
+    const uint4 *in = e.in + (size_t)rank * n_vec;
+    uint4 *out = e.out + (size_t)rank * n_vec;
+    if (PUSHED)
+        pushed_form<WORLD>(peers, e.flags + (size_t)rank * (kFlagBytes + 2 * kLlHalfBytes), counters, rank, in, out,
+                           n_vec, wait_ns, status, blockIdx.x, gridDim.x);
+    else
+        flag_form<WORLD>(peers, counters, rank, WORLD, in, out, n_vec, vec_per_cta, slot_bytes, wait_ns, status,
+                         blockIdx.x, gridDim.x);
+}
+
+template <int WORLD>
+cudaError_t launch_emulated(const Emulated &e, uint32_t n_vec, uint32_t slot_bytes, uint64_t wait_ns, int *status,
+                            cudaStream_t stream)
+{
+    const bool pushed = n_vec <= kLlSlotVecs;
+    uint32_t ctas, per = 0;
+    if (pushed) {
+        ctas = (n_vec + kLlThreads - 1) / kLlThreads;
+    } else {
+        ctas = (n_vec + (uint32_t)kThreads - 1u) / (uint32_t)kThreads;
+        if (ctas > (uint32_t)kMaxCtas) ctas = kMaxCtas;
+        per = (n_vec + ctas - 1u) / ctas;
+    }
+    Emulated ee = e;
+    void *args[] = {&ee, &n_vec, &per, &slot_bytes, &wait_ns, &status};
+    const void *fn = pushed ? (const void *)df11_allreduce_emulated_kernel<WORLD, true>
+                            : (const void *)df11_allreduce_emulated_kernel<WORLD, false>;
+    return cudaLaunchCooperativeKernel(fn, dim3(ctas, WORLD), dim3(pushed ? kLlThreads : kThreads), args, 0, stream);
+}
+
 }  // namespace
+
+extern "C" int df11_selftest_allreduce_one_gpu(int32_t world, void *data, void *flags, void *counters,
+                                               const void *in_bf16, void *out_bf16, int64_t n_elements,
+                                               int64_t slot_bytes, int64_t wait_ms, void *status, int32_t device,
+                                               void *stream)
+{
+    if (!data || !flags || !counters || !in_bf16 || !out_bf16) return df11_fail(DF11_ERR_BADARG, "null pointer");
+    if (world != 2 && world != 4 && world != 8) return df11_fail(DF11_ERR_BADARG, "world must be 2, 4 or 8");
+    if (n_elements <= 0 || n_elements % 8 || n_elements * 2 > slot_bytes || slot_bytes % 16 || slot_bytes > 0x7FFFFFFF)
+        return df11_fail(DF11_ERR_BADARG, "n_elements must be a positive multiple of 8 that fits slot_bytes");
+    if (((uintptr_t)data | (uintptr_t)flags | (uintptr_t)in_bf16 | (uintptr_t)out_bf16) & 15)
+        return df11_fail(DF11_ERR_BADARG, "buffers must be 16-byte aligned");
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != device && cudaSetDevice(device) != cudaSuccess)
+        return df11_fail(DF11_ERR_CUDA, "cudaSetDevice(%d) failed", device);
+    int cooperative = 0;
+    cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, device);
+    cudaError_t err = cudaErrorNotSupported;
+    if (cooperative) {
+        Emulated e = {(uint8_t *)data, (uint8_t *)flags, (uint32_t *)counters, (const uint4 *)in_bf16, (uint4 *)out_bf16};
+        const uint32_t n_vec = (uint32_t)(n_elements / 8);
+        const uint64_t wait_ns = wait_ms > 0 ? (uint64_t)wait_ms * 1000000ull : 200ull * 1000 * 1000;
+        err = world == 2 ? launch_emulated<2>(e, n_vec, (uint32_t)slot_bytes, wait_ns, (int *)status, (cudaStream_t)stream)
+            : world == 4 ? launch_emulated<4>(e, n_vec, (uint32_t)slot_bytes, wait_ns, (int *)status, (cudaStream_t)stream)
+                         : launch_emulated<8>(e, n_vec, (uint32_t)slot_bytes, wait_ns, (int *)status, (cudaStream_t)stream);
+    }
+    if (prev >= 0 && prev != device) cudaSetDevice(prev);
+    if (err != cudaSuccess) return df11_fail(DF11_ERR_CUDA, "cooperative launch failed: %s", cudaGetErrorString(err));
+    return DF11_OK;
+}
 
 extern "C" int64_t df11_allreduce_flag_bytes(void) { return (int64_t)(kFlagBytes + 2 * kLlHalfBytes); }
 

@@ -282,6 +282,24 @@ int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *peer_flags, v
                         int32_t device, void *stream);
 
 /*
+ * Self-test of df11_allreduce_bf16's kernels on ONE GPU: a single cooperative launch plays all
+ * `world` ranks (2, 4 or 8) -- row r of the grid runs rank r's code on rank r's buffers -- so
+ * the exchange between ranks, the call tags and the alternating buffer halves are exercised
+ * where only one GPU is at hand.  (Separate launches that wait for one another must never share
+ * a GPU; one cooperative launch may.)
+ *   data      device, world buffers of 2 * slot_bytes bytes one after another
+ *   flags     device, world flag areas of df11_allreduce_flag_bytes() bytes, zeroed once
+ *   counters  device, world pairs of uint32, zeroed once
+ *   in_bf16 / out_bf16   device, [world][n_elements] BF16: rank r's input and result
+ * Size limits, forms, summation order and time-out as for df11_allreduce_bf16 (wait_ms <= 0:
+ * 200 ms).  No counterpart in the reference.
+ */
+int df11_selftest_allreduce_one_gpu(int32_t world, void *data, void *flags, void *counters,
+                                    const void *in_bf16, void *out_bf16, int64_t n_elements,
+                                    int64_t slot_bytes, int64_t wait_ms, void *status, int32_t device,
+                                    void *stream);
+
+/*
  * Host-side check of one unit before its first launch (all pointers HOST memory).
  * The reference performs no validation: a zero entry in the length row makes its
  * kernel spin forever (decode.cu:116-118).  Checks: table count, pointers stay

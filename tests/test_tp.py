@@ -207,6 +207,50 @@ def _peer_worker(rank, world, port, q):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_all_reduce_kernels_with_all_ranks_on_one_gpu(world):
+    """Both forms of the all-reduce kernel with 2, 4 and 8 ranks played by one cooperative launch
+    on one GPU: results against an fp32 sum in rank order, the call numbers, the alternating
+    buffer halves, and the wrap of the call number."""
+    from dfloat11_b200 import _lib
+    lib, dev, slot = _lib.lib, torch.device("cuda", 0), 1 << 20
+    flag_bytes = int(lib.df11_allreduce_flag_bytes())
+    data = torch.zeros(world * 2 * slot, dtype=torch.uint8, device=dev)
+    flags = torch.zeros(world * flag_bytes, dtype=torch.uint8, device=dev)
+    counters = torch.zeros(world, 2, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def one_call(n, seed):
+        parts = torch.randn(world, n, generator=torch.Generator().manual_seed(seed)).to(torch.bfloat16)
+        want = torch.zeros(n)
+        for r in range(world):                                # rank order, fp32, one rounding
+            want = want + parts[r].float()
+        x, out = parts.to(dev), torch.empty(world, n, dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.df11_selftest_allreduce_one_gpu(world, data.data_ptr(), flags.data_ptr(), counters.data_ptr(),
+                                                       x.data_ptr(), out.data_ptr(), n, slot, 0, status.data_ptr(),
+                                                       0, stream))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for r in range(world):
+            assert torch.equal(out[r].cpu(), want.to(torch.bfloat16)), (n, r)
+
+    sizes = (8, 16384, 16384, 40000, 32768, 16 * 16384, 40000, 16384, 1000 * 8)   # pushed form up to 32768 elements
+    for k, n in enumerate(sizes):
+        one_call(n, 17 * k + world)
+        assert counters.cpu().tolist() == [[k + 1, 0]] * world
+    counters[:, 0] = -3                                       # 0xFFFFFFFD: the tags pass 0xFFFFFFFF, skip 0
+    torch.cuda.synchronize()
+    for k in range(6):
+        one_call(40000 if k % 2 else 16384, 900 + k)
+    assert counters.cpu().tolist() == [[3, 0]] * world
+    with pytest.raises(_lib.DF11Error):
+        _lib.check(lib.df11_selftest_allreduce_one_gpu(3, data.data_ptr(), flags.data_ptr(), counters.data_ptr(),
+                                                       data.data_ptr(), data.data_ptr(), 8, slot, 0, status.data_ptr(),
+                                                       0, stream))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("world", [1, 2])
 def test_peer_all_reduce_kernel(world):
     if torch.cuda.device_count() < world:
