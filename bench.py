@@ -1045,22 +1045,28 @@ def tp_block(args, rank, world, device):
         barrier(world, device)
         return all_max(a.elapsed_time(b) / steps, world, device)
 
-    ms_with = timed(lambda: step(True))
-    ms_without = timed(lambda: step(False))
-    ms_reduce = timed(lambda: [dist.all_reduce(act) for _ in range(2 * layers)])
-    # the same step as one CUDA graph (what a generation loop replays): no host time between the launches
-    ms_graph, graph_error = None, None
-    try:
+    def graphed(fn):
+        """fn captured into one CUDA graph after a run on a side stream; returns the replay."""
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(side):
-            step(True)
+            fn()
         torch.cuda.current_stream(device).wait_stream(side)
         barrier(world, device)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            step(True)
-        ms_graph = timed(graph.replay)
+            fn()
+        return graph.replay
+
+    ms_with = timed(lambda: step(True))
+    ms_without = timed(lambda: step(False))
+    ms_reduce = timed(lambda: [dist.all_reduce(act) for _ in range(2 * layers)])
+    # the same step as one CUDA graph (what a generation loop replays): no host time between the launches
+    ms_graph, ms_reduce_graph, graph_error = None, None, None
+    try:
+        ms_graph = timed(graphed(lambda: step(True)))
+        # the all-reduces alone as one graph: their cost on the device, no host time and no decode between them
+        ms_reduce_graph = timed(graphed(lambda: [dist.all_reduce(act) for _ in range(2 * layers)]), steps=50)
     except Exception as exc:                                # report, do not hide
         graph_error = f"{type(exc).__name__}: {exc}"[:200]
     # the same step with this library's one-kernel all-reduce over NVLink peer memory
@@ -1092,16 +1098,8 @@ def tp_block(args, rank, world, device):
 
             ms_peer = timed(step_peer)
             ms_peer_alone = timed(lambda: [peer.all_reduce_(act) for _ in range(2 * layers)])
-            side = torch.cuda.Stream(device=device)
-            side.wait_stream(torch.cuda.current_stream(device))
-            with torch.cuda.stream(side):
-                step_peer()
-            torch.cuda.current_stream(device).wait_stream(side)
-            barrier(world, device)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                step_peer()
-            ms_peer_graph = timed(graph.replay)
+            ms_peer_graph = timed(graphed(step_peer))
+            ms_peer_alone_graph = timed(graphed(lambda: [peer.all_reduce_(act) for _ in range(2 * layers)]), steps=50)
             peer.check()
             total_p = all_sum(sum(algorithmic_bytes(u) for u in units), world, device)
             peak_p, _ = measured_hbm_peak()
@@ -1109,6 +1107,7 @@ def tp_block(args, rank, world, device):
                 "ms_per_step": round(ms_peer, 3), "per_gpu_GBps": round(total_p / ms_peer / 1e6 / world, 1),
                 "per_gpu_frac_of_measured_peak": round(total_p / ms_peer / 1e6 / world / peak_p, 4),
                 "us_per_all_reduce_back_to_back": round(ms_peer_alone * 1e3 / (2 * layers), 2),
+                "us_per_all_reduce_in_a_graph_of_all_reduces": round(ms_peer_alone_graph * 1e3 / (2 * layers), 2),
                 "buffers_bound_to_a_multicast_object": peer.multicast_bound,
                 "cuda_graph": {"ms_per_step": round(ms_peer_graph, 3),
                                "per_gpu_GBps": round(total_p / ms_peer_graph / 1e6 / world, 1),
@@ -1131,6 +1130,8 @@ def tp_block(args, rank, world, device):
                        if ms_graph else {"error": graph_error}),
         "decode_only_ms_per_step": round(ms_without, 3),
         "us_per_all_reduce_back_to_back": round(ms_reduce * 1e3 / (2 * layers), 2),
+        "us_per_all_reduce_in_a_graph_of_all_reduces": (round(ms_reduce_graph * 1e3 / (2 * layers), 2)
+                                                        if ms_reduce_graph else None),
         "us_per_all_reduce_in_step": round((ms_with - ms_without) * 1e3 / (2 * layers), 2),
         "bit_exact": bool(ok),
         "peer_all_reduce": peer_result,
