@@ -33,6 +33,8 @@ SIGNATURES = {
     "df11_seek_interval": (c_int32, [c_int32]),
     "df11_decode_range_prepared": (c_int32, [c_void_p] * 4 + [c_int64, c_int64, c_void_p, c_int32, c_int64, c_int64,
                                              c_void_p, c_int32, c_void_p]),
+    "df11_decode_range_prepared_shared": (c_int32, [c_void_p] * 4 + [c_int64, c_int64, c_void_p, c_int32, c_int64,
+                                                    c_int64, c_int32, c_void_p, c_int32, c_void_p]),
     "df11_prepare": (c_int32, [c_void_p] * 5 + [c_int64, c_int32, c_int64, c_int64, c_void_p, c_int32, c_void_p]),
     "df11_decode_prepared": (c_int32, [c_void_p] * 7 + [c_int32, c_int64, c_int64, c_int32, c_void_p, c_int32, c_void_p]),
     "df11_decode_prepared_shared": (c_int32, [c_void_p] * 7 + [c_int32, c_int64, c_int64, c_int32, c_void_p, c_int32,

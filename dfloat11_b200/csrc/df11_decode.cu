@@ -1652,6 +1652,17 @@ extern "C" int df11_decode_range_prepared(const void *luts, const void *codes, c
                            device, stream, 0, first_element, range_elements);
 }
 
+extern "C" int df11_decode_range_prepared_shared(const void *luts, const void *codes, const void *sign_mantissa,
+                                                 const void *aux, int64_t first_element, int64_t range_elements,
+                                                 void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                                                 int32_t ctas_per_sm, void *status, int32_t device, void *stream)
+{
+    if (range_elements < 0) return df11_fail(DF11_ERR_BADARG, "negative range length");
+    if (ctas_per_sm < 0) return df11_fail(DF11_ERR_BADARG, "ctas_per_sm = %d", ctas_per_sm);
+    return decode_prepared(luts, codes, sign_mantissa, luts, luts, aux, out_bf16, n_luts, n_bytes, n_elements, status,
+                           device, stream, ctas_per_sm, first_element, range_elements);
+}
+
 extern "C" int df11_decode_rows_prepared(const void *luts, const void *codes, const void *sign_mantissa,
                                          const void *aux, const void *rows, int64_t n_rows, int64_t row_elements,
                                          void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,

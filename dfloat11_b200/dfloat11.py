@@ -54,6 +54,7 @@ class _Flags:
     in_forward = False
     prepared = True
     decode_ahead = False
+    ahead_window = False
     sparse = True
     fused = False
     nvtx = False
@@ -66,7 +67,8 @@ class _Flags:
     def read(cls) -> None:
         env = os.environ.get
         cls.prepared = env("DF11_PREPARED", "1") != "0"
-        cls.decode_ahead = env("DF11_DECODE_AHEAD", "0") == "1"
+        cls.decode_ahead = env("DF11_DECODE_AHEAD", "0") in ("1", "2")
+        cls.ahead_window = env("DF11_DECODE_AHEAD", "0") == "2"
         cls.sparse = env("DF11_SPARSE_EMBEDDING", "1") != "0"
         cls.fused = env("DF11_FUSED_GEMV", "0") == "1"
         cls.nvtx = env("DF11_NVTX", "0") == "1"
@@ -309,7 +311,8 @@ class _DecodeAhead:
         self.device = device
         self.stream = torch.cuda.Stream(device=device)
         self.prev: Optional[nn.Module] = None      # unit whose hook ran last in this forward
-        self.pending = None                        # (module, slot, done event, tensor)
+        self.pending = None                        # (module, slot, done event, tensor, elements decoded)
+        self.armed = None                          # windowed mode: (current unit, its successor), not yet launched
         self.slot = 0                              # slot that holds the weights of `prev`
         self.stats = dict(hits=0, misses=0, wasted=0, launched=0)
 
@@ -329,6 +332,7 @@ class _DecodeAhead:
                 ahead.pending = None
                 ahead.stats["wasted"] += 1
             ahead.prev = None
+            ahead.armed = None
 
     @staticmethod
     def eligible(unit: nn.Module, device: torch.device) -> bool:
@@ -340,22 +344,23 @@ class _DecodeAhead:
             return False
         return not (isinstance(unit, nn.Embedding) and _sparse_enabled())
 
-    def claim(self, module: nn.Module, n_elements: int) -> Optional[torch.Tensor]:
-        """The decoded weights of ``module`` if they were decoded ahead (valid for work queued on
-        the current stream after this call), else None."""
+    def claim(self, module: nn.Module, n_elements: int):
+        """``(tensor, n)``: the scratch tensor of ``module`` whose first ``n`` elements were decoded
+        ahead (valid for work queued on the current stream after this call), or ``(None, 0)``."""
         pending, self.pending = self.pending, None
+        self.armed = None
         if pending is None:
             self.stats["misses"] += 1
-            return None
-        unit, slot, done, tensor = pending
+            return None, 0
+        unit, slot, done, tensor, upto = pending
         torch.cuda.current_stream(self.device).wait_event(done)    # nobody writes a slot after this
         if unit is module and tensor.numel() == n_elements:
             self.stats["hits"] += 1
             self.slot = slot
-            return tensor
+            return tensor, upto
         self.stats["wasted"] += 1
         self.stats["misses"] += 1
-        return None
+        return None, 0
 
     def fresh_slot(self) -> int:
         self.slot ^= 1
@@ -371,9 +376,49 @@ class _DecodeAhead:
         if self.prev is not None and self.prev is not module:
             self.prev.__dict__["df11_next_unit"] = module
         self.prev = module
+        self.armed = None
         nxt = module.__dict__.get("df11_next_unit")
         if nxt is None or nxt is module or not self.eligible(nxt, self.device):
             return
+        if _Flags.current().ahead_window and not light:
+            # windowed: nothing yet; the first part of the next unit is decompressed when this
+            # unit's trigger layer has run (see `window`), the rest by the next unit's own hook
+            if self._window_hook(module):
+                self.armed = (module, nxt)
+            return
+        self._launch(module, nxt, light, None)
+
+    def _window_hook(self, unit: nn.Module) -> bool:
+        """Registers, once per unit, a forward hook on the layer after which the unit's forward
+        leaves most of the GPU idle for a while (``DF11_AHEAD_AFTER``, default ``v_proj``: rotary
+        embedding, cache update and attention follow).  False if the unit has no such layer."""
+        d = unit.__dict__
+        if "df11_window_hook" not in d:
+            name = os.environ.get("DF11_AHEAD_AFTER", "v_proj")
+            layer = next((m for n, m in unit.named_modules() if n.split(".")[-1] == name), None)
+            if layer is None:
+                d["df11_window_hook"] = None
+            else:
+                ref = weakref.ref(unit)
+                d["df11_window_hook"] = layer.register_forward_hook(
+                    lambda _m, _i, _o: _DecodeAhead.window(ref()))
+        return d["df11_window_hook"] is not None
+
+    @classmethod
+    def window(cls, unit: Optional[nn.Module]) -> None:
+        """The trigger layer of ``unit`` has run: start on its successor now."""
+        if unit is None or not _Flags.current().ahead_window:
+            return
+        for ahead in cls._by_device.values():
+            if ahead.armed is not None and ahead.armed[0] is unit:
+                (_, nxt), ahead.armed = ahead.armed, None
+                n = nxt.sign_mantissa.numel()
+                chunk = ops.chunk_elements()
+                part = int(n * float(os.environ.get("DF11_AHEAD_FRACTION", "0.4"))) // chunk * chunk
+                if part > 0:
+                    ahead._launch(unit, nxt, False, part)
+
+    def _launch(self, module: nn.Module, nxt: nn.Module, light: bool, part: Optional[int]) -> None:
         n_next = nxt.sign_mantissa.numel()
         n_this = module.sign_mantissa.numel() if not hasattr(module, "offloaded_tensors") else n_next
         ctas = int(os.environ.get("DF11_AHEAD_CTAS", "1"))
@@ -386,12 +431,16 @@ class _DecodeAhead:
         queued.record(main)                            # the slot's previous reader has been queued before this
         self.stream.wait_event(queued)
         with torch.cuda.stream(self.stream):
-            pos, gaps = _side_tensors(nxt, self.device)
-            ops.decode_prepared(nxt.luts, nxt.encoded_exponent, nxt.sign_mantissa, pos, gaps, nxt.df11_aux,
-                                out=tensor, ctas_per_sm=ctas, status=_status_word(self.device))
+            if part is None:
+                pos, gaps = _side_tensors(nxt, self.device)
+                ops.decode_prepared(nxt.luts, nxt.encoded_exponent, nxt.sign_mantissa, pos, gaps, nxt.df11_aux,
+                                    out=tensor, ctas_per_sm=ctas, status=_status_word(self.device))
+            else:
+                ops.decode_range_prepared(nxt.luts, nxt.encoded_exponent, nxt.sign_mantissa, nxt.df11_aux, 0, part,
+                                          out=tensor, ctas_per_sm=ctas, status=_status_word(self.device))
             done = torch.cuda.Event()
             done.record(self.stream)
-        self.pending = (nxt, slot, done, tensor)
+        self.pending = (nxt, slot, done, tensor, n_next if part is None else part)
         self.stats["launched"] += 1
 
 
@@ -743,6 +792,7 @@ def get_hook(threads_per_block, bytes_per_thread):
         offloaded = hasattr(module, "offloaded_tensors")
         d["df11_undecoded"] = False
         d.pop("df11_pending", None)
+        d.pop("df11_fast", None)          # whatever this pass injects replaces what the short path relied on
 
         if flags.prepared and offloaded and _sparse_embedding(module, inputs, module.offloaded_tensors[
                 "sign_mantissa"].numel()) and all(t.is_pinned() for t in module.offloaded_tensors.values()):
@@ -810,8 +860,14 @@ def get_hook(threads_per_block, bytes_per_thread):
             ahead = _DecodeAhead.get(device) if flags.decode_ahead else None
             if _sparse_embedding(module, inputs, n_elements):
                 return sparse_lookup(module, inputs, encoded_exponent, sign_mantissa, aux, device, status, stager, ahead)
-            reconstructed = ahead.claim(module, n_elements) if ahead is not None else None
+            reconstructed, upto = ahead.claim(module, n_elements) if ahead is not None else (None, 0)
             pos, gaps = _side_tensors(module, device)
+            if reconstructed is not None and upto < n_elements:
+                # the first part was decompressed beside the previous unit's forward; the rest now
+                ops.decode_range_prepared(module.luts, encoded_exponent, sign_mantissa, aux, upto, n_elements - upto,
+                                          out=reconstructed[upto:], status=status)
+                _counters["decodes"] += 1
+                _counters["decoded_elements"] += n_elements - upto
             if reconstructed is None:
                 slot = ahead.fresh_slot() if ahead is not None else 0
                 reconstructed = TensorManager.allocate_bfloat16(device, n_elements, slot=slot)

@@ -130,14 +130,21 @@ def chunk_elements() -> int:
 
 def decode_range_prepared(luts: torch.Tensor, encoded_exponent: torch.Tensor, sign_mantissa: torch.Tensor,
                           aux: torch.Tensor, first_element: int, range_elements: int, out: torch.Tensor,
-                          status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          status: Optional[torch.Tensor] = None, ctas_per_sm: int = 0) -> torch.Tensor:
     """Decompress elements ``[first_element, first_element + range_elements)`` of a prepared unit into
     ``out[:range_elements]``.  The range starts on a multiple of ``chunk_elements()`` and ends on one
-    or at the end of the unit."""
+    or at the end of the unit.  ``ctas_per_sm`` > 0 caps the CTAs per SM, as in ``decode_prepared``."""
     device = _require_cuda(luts=luts, encoded_exponent=encoded_exponent, sign_mantissa=sign_mantissa,
                            aux=aux, out=out, status=status)
     if out.dtype != torch.bfloat16 or out.numel() < range_elements:
         raise RuntimeError("`out` must be a bfloat16 tensor with at least range_elements elements")
+    if ctas_per_sm:
+        _lib.check(_lib.lib.df11_decode_range_prepared_shared(
+            luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(), aux.data_ptr(),
+            int(first_element), int(range_elements), out.data_ptr(), luts.shape[0], encoded_exponent.numel(),
+            sign_mantissa.numel(), int(ctas_per_sm), status.data_ptr() if status is not None else None,
+            device.index, _stream(device)))
+        return out[:range_elements]
     _lib.check(_lib.lib.df11_decode_range_prepared(
         luts.data_ptr(), encoded_exponent.data_ptr(), sign_mantissa.data_ptr(), aux.data_ptr(),
         int(first_element), int(range_elements), out.data_ptr(), luts.shape[0], encoded_exponent.numel(),

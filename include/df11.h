@@ -174,6 +174,15 @@ int df11_decode_range_prepared(const void *luts, const void *codes, const void *
                                void *status, int32_t device, void *stream);
 
 /*
+ * df11_decode_range_prepared with the cap on CTAs per SM of df11_decode_prepared_shared: for a
+ * part of a unit that is decompressed on a second stream beside the forward pass.
+ */
+int df11_decode_range_prepared_shared(const void *luts, const void *codes, const void *sign_mantissa,
+                                      const void *aux, int64_t first_element, int64_t range_elements,
+                                      void *out_bf16, int32_t n_luts, int64_t n_bytes, int64_t n_elements,
+                                      int32_t ctas_per_sm, void *status, int32_t device, void *stream);
+
+/*
  * Decode fused with a matrix-vector product: y[j][r] = sum_c W[r][c] * x[j][c] + bias[r] for
  * one [n_rows, in_features] matrix W that lies inside a prepared unit (its first weight is
  * element `first_element` of the unit) and m = 1..4 activation vectors, without writing W

@@ -295,7 +295,7 @@ def test_graphed_decoder_refuses_a_model_that_is_not_on_a_gpu():
 
 # ------------------------------------------------------------------ GPU
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["resident", "ahead", "ahead_3_ctas", "offload", "offload_some_ahead", "two_pass",
+@pytest.mark.parametrize("mode", ["resident", "ahead", "ahead_3_ctas", "ahead_window", "offload", "offload_some_ahead", "two_pass",
                                   "auto_map"])
 def test_logits_identical_to_bf16_model(saved, mode, monkeypatch):
     path, reference = saved
@@ -305,6 +305,8 @@ def test_logits_identical_to_bf16_model(saved, mode, monkeypatch):
         monkeypatch.setenv("DF11_DECODE_AHEAD", "1")             # next unit decoded on a second stream
     if mode == "ahead_3_ctas":
         monkeypatch.setenv("DF11_AHEAD_CTAS", "3")
+    if mode == "ahead_window":                                   # part of the next unit beside attention, the rest in its own hook
+        monkeypatch.setenv("DF11_DECODE_AHEAD", "2")
     if mode == "offload":
         kwargs["cpu_offload"] = True
     elif mode.startswith("offload_some"):
@@ -333,6 +335,26 @@ def test_logits_identical_to_bf16_model(saved, mode, monkeypatch):
         assert ahead is not None and ahead.stats["hits"] > 0 and ahead.pending is None
     else:
         assert ahead is None or ahead.stats["launched"] == 0
+
+
+@pytest.mark.gpu
+def test_switching_decode_ahead_off_again_keeps_the_weights_right(saved, monkeypatch):
+    """The short path of the hook keeps pointers and weight views from a unit's last call; a pass
+    in another mode (here: decode-ahead, whose units alternate between two scratch tensors)
+    re-injects the views, and the short path must not trust its old state afterwards."""
+    path, reference = saved
+    host._DecodeAhead._by_device.clear()
+    model = df11.DFloat11Model.from_pretrained(path, bfloat16_model=tiny_llama(seed=7), device="cuda:0")
+    ref = copy.deepcopy(reference).to("cuda:0")
+    ids = torch.randint(0, 1024, (2, 19), generator=torch.Generator().manual_seed(5)).to("cuda:0")
+    with torch.no_grad():
+        want = ref(input_ids=ids).logits
+        for setting in (None, None, "1", "1", None, None, "2", "2", None, None):
+            if setting is None:
+                monkeypatch.delenv("DF11_DECODE_AHEAD", raising=False)
+            else:
+                monkeypatch.setenv("DF11_DECODE_AHEAD", setting)
+            assert torch.equal(model(input_ids=ids).logits, want), setting
 
 
 @pytest.mark.gpu
