@@ -46,6 +46,7 @@ SIGNATURES = {
                                             c_void_p, c_int32, c_void_p]),
     "df11_decode_static": (c_int32, [c_void_p] * 6 + [c_int32, c_int64, c_int64, c_void_p, c_int32, c_void_p]),
     "df11_allreduce_flag_bytes": (c_int64, []),
+    "df11_allreduce_counter_bytes": (c_int64, []),
     "df11_allreduce_bf16": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int64, c_int64,
                                       c_int64, c_void_p, c_int32, c_void_p]),
     "df11_selftest_allreduce_one_gpu": (c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

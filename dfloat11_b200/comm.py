@@ -64,7 +64,7 @@ class PeerAllReduce:
         pointers = [int(p) for p in self.handle.buffer_ptrs]
         self._data = (ctypes.c_uint64 * 8)(*(pointers + [0] * (8 - len(pointers))))
         self._flags = (ctypes.c_uint64 * 8)(*([p + 2 * self.slot_bytes for p in pointers] + [0] * (8 - len(pointers))))
-        self.counters = torch.zeros(2, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(int(_lib.lib.df11_allreduce_counter_bytes()) // 4, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.calls = 0
         # nobody writes a flag before every rank's flag area is zero

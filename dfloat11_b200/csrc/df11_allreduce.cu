@@ -45,6 +45,12 @@ constexpr size_t kFlagBytes = (size_t)2 * kMaxCtas * kMaxRanks * sizeof(uint32_t
 constexpr int kLlThreads = 128;
 constexpr uint32_t kLlSlotVecs = 4096;                                   // 64 KB of data per rank and call
 constexpr size_t kLlHalfBytes = (size_t)kMaxRanks * kLlSlotVecs * 32;    // 1 MiB
+// counters of one rank: [0] call number of the flag form, [1] its CTAs done, [2 + c] the number of
+// pushed calls CTA c has taken part in (a cell is only ever touched by the CTA with its number,
+// so each CTA can keep its own count: no atomic, no fence at the end of the kernel)
+constexpr int kLlCtas = kLlSlotVecs / kLlThreads;
+constexpr int kCounterWords = 64;
+static_assert(2 + kLlCtas <= kCounterWords, "counter block too small");
 
 struct Peers {
     uint8_t *data[kMaxRanks];    // each rank's buffer: two halves of slot_bytes
@@ -183,7 +189,8 @@ __device__ __forceinline__ void pushed_form(const Peers &peers, const uint8_t *o
                                             const uint4 *in, uint4 *out, uint32_t n_vec, uint64_t wait_ns,
                                             int *status, uint32_t cta, uint32_t n_ctas)
 {
-    const uint32_t call = *reinterpret_cast<volatile uint32_t *>(counters);
+    uint32_t *sequence = counters + 2 + cta;  // pushed calls this CTA has seen: the same on every rank
+    const uint32_t call = *reinterpret_cast<volatile uint32_t *>(sequence);
     uint32_t tag = call + 1u;  // never 0: the buffers start zeroed
     if (tag == 0u) tag = 1u;   // (the neighbouring calls' tags in the same half are 0xFFFFFFFF and 2)
     const uint32_t v = cta * kLlThreads + threadIdx.x;
@@ -231,16 +238,12 @@ __device__ __forceinline__ void pushed_form(const Peers &peers, const uint8_t *o
                                 bf16x2_from_floats(acc[4], acc[5]), bf16x2_from_floats(acc[6], acc[7]));
         }
     }
-    const int all_ok = __syncthreads_and(ok ? 1 : 0);
+    const int all_ok = __syncthreads_and(ok ? 1 : 0);  // every thread has read the count by now
     if (threadIdx.x == 0) {
         if (!all_ok && status != nullptr) atomicOr(status, DF11_STATUS_TIMEOUT);
-        __threadfence();
-        if (atomicAdd(counters + 1, 1u) == n_ctas - 1u) {  // the last CTA advances the call number
-            counters[1] = 0u;
-            __threadfence();
-            *reinterpret_cast<volatile uint32_t *>(counters) = call + 1u;
-        }
+        *sequence = call + 1u;  // seen by the next launch on this stream
     }
+    (void)n_ctas;
 }
 
 template <int WORLD>
@@ -257,7 +260,7 @@ __global__ void __launch_bounds__(kLlThreads) df11_allreduce_ll_kernel(const Pee
 // `world` buffers, flag areas, counters, inputs and outputs laid out one after another.
 struct Emulated {
     uint8_t *data, *flags;       // [world] buffers of 2 * slot_bytes, [world] flag areas
-    uint32_t *counters;          // [world][2]
+    uint32_t *counters;          // [world][kCounterWords]
     const uint4 *in;             // [world][n_vec]
     uint4 *out;                  // [world][n_vec]
 };
@@ -273,7 +276,7 @@ __global__ void __launch_bounds__(PUSHED ? kLlThreads : kThreads) df11_allreduce
         peers.data[r] = e.data + (size_t)r * 2 * slot_bytes;
         peers.flags[r] = reinterpret_cast<uint32_t *>(e.flags + (size_t)r * (kFlagBytes + 2 * kLlHalfBytes));
     }
-    uint32_t *counters = e.counters + 2 * rank;
+    uint32_t *counters = e.counters + kCounterWords * rank;
     const uint4 *in = e.in + (size_t)rank * n_vec;
     uint4 *out = e.out + (size_t)rank * n_vec;
     if (PUSHED)
@@ -338,6 +341,7 @@ extern "C" int df11_selftest_allreduce_one_gpu(int32_t world, void *data, void *
 }
 
 extern "C" int64_t df11_allreduce_flag_bytes(void) { return (int64_t)(kFlagBytes + 2 * kLlHalfBytes); }
+extern "C" int64_t df11_allreduce_counter_bytes(void) { return (int64_t)kCounterWords * sizeof(uint32_t); }
 
 extern "C" int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *peer_flags, void *counters, int32_t rank,
                                    int32_t world, const void *in_bf16, void *out_bf16, int64_t n_elements,

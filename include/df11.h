@@ -268,7 +268,8 @@ int df11_decode_static(const void *luts, const void *codes, const void *sign_man
  *   peer_flags   HOST array [world]: rank r's flag area of df11_allreduce_flag_bytes() bytes
  *                (about 2 MiB: the flags, and the cells of the pushed form below), in the
  *                same kind of memory, zeroed once before the first call on any rank
- *   counters     device, this rank only: two uint32, zeroed once (call number, CTAs done)
+ *   counters     device, this rank only: df11_allreduce_counter_bytes() bytes (256), zeroed once;
+ *                the kernels keep their call numbers there
  *   in_bf16 / out_bf16   device, n_elements BF16 each (a multiple of 8; in == out is fine),
  *                16-byte aligned; n_elements * 2 <= slot_bytes
  *   wait_ms      how long a rank waits for its peers' data before it gives up and sets
@@ -279,11 +280,12 @@ int df11_decode_static(const void *luts, const void *codes, const void *sign_man
  * or barrier.  Anything else: slices into the own data buffer, one flag per rank and CTA,
  * peer loads.
  * The sum is taken in rank order in fp32 and rounded once: identical bits on every rank.
- * The call number is kept in `counters`, so a launch captured in a CUDA graph replays.
+ * The call numbers are kept in `counters`, so a launch captured in a CUDA graph replays.
  * No counterpart in the reference (its only multi-GPU form places whole layers on
  * different devices, dfloat11/dfloat11.py:455-460).
  */
 int64_t df11_allreduce_flag_bytes(void);
+int64_t df11_allreduce_counter_bytes(void);
 
 int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *peer_flags, void *counters,
                         int32_t rank, int32_t world, const void *in_bf16, void *out_bf16,
@@ -298,7 +300,7 @@ int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *peer_flags, v
  * a GPU; one cooperative launch may.)
  *   data      device, world buffers of 2 * slot_bytes bytes one after another
  *   flags     device, world flag areas of df11_allreduce_flag_bytes() bytes, zeroed once
- *   counters  device, world pairs of uint32, zeroed once
+ *   counters  device, world blocks of df11_allreduce_counter_bytes() bytes, zeroed once
  *   in_bf16 / out_bf16   device, [world][n_elements] BF16: rank r's input and result
  * Size limits, forms, summation order and time-out as for df11_allreduce_bf16 (wait_ms <= 0:
  * 200 ms).  No counterpart in the reference.

@@ -193,13 +193,14 @@ def _peer_worker(rank, world, port, q):
         torch.cuda.synchronize()
         dist.barrier(device_ids=[rank])
         inst.counters[0] = -3                                  # 0xFFFFFFFD, on every rank, nothing in flight
+        inst.counters[2:] = -3                                 # (the pushed form counts per CTA)
         torch.cuda.synchronize()
         dist.barrier(device_ids=[rank])
-        for k in range(6):
+        for k in range(8):
             x = torch.full((40000 if k % 2 else 16384,), float(rank + 1 + k), dtype=torch.bfloat16, device=dev)  # both forms
             assert inst.all_reduce_(x)
             ok &= bool((x == float(sum(r + 1 + k for r in range(world)))).all())
-        ok &= int(inst.counters[0].item()) == 3
+        ok &= inst.counters[:3].cpu().tolist() == [1, 0, 1]
         inst.check()
         q.put((rank, "ok" if ok else "wrong"))
     finally:
@@ -217,7 +218,8 @@ def test_all_reduce_kernels_with_all_ranks_on_one_gpu(world):
     flag_bytes = int(lib.df11_allreduce_flag_bytes())
     data = torch.zeros(world * 2 * slot, dtype=torch.uint8, device=dev)
     flags = torch.zeros(world * flag_bytes, dtype=torch.uint8, device=dev)
-    counters = torch.zeros(world, 2, dtype=torch.int32, device=dev)
+    words = int(lib.df11_allreduce_counter_bytes()) // 4
+    counters = torch.zeros(world, words, dtype=torch.int32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
 
@@ -236,14 +238,19 @@ def test_all_reduce_kernels_with_all_ranks_on_one_gpu(world):
             assert torch.equal(out[r].cpu(), want.to(torch.bfloat16)), (n, r)
 
     sizes = (8, 16384, 16384, 40000, 32768, 16 * 16384, 40000, 16384, 1000 * 8)   # pushed form up to 32768 elements
+    pushed = flagged = 0
     for k, n in enumerate(sizes):
         one_call(n, 17 * k + world)
-        assert counters.cpu().tolist() == [[k + 1, 0]] * world
+        pushed, flagged = pushed + (n <= 32768), flagged + (n > 32768)
+        # [0] calls of the flag form, [1] its CTAs done, [2 + c] pushed calls CTA c took part in
+        assert counters[:, :3].cpu().tolist() == [[flagged, 0, pushed]] * world
+    assert counters[:, 2 + 31].cpu().tolist() == [1] * world   # only the 32768-element call reached the last CTA
     counters[:, 0] = -3                                       # 0xFFFFFFFD: the tags pass 0xFFFFFFFF, skip 0
+    counters[:, 2:] = -3
     torch.cuda.synchronize()
-    for k in range(6):
+    for k in range(8):
         one_call(40000 if k % 2 else 16384, 900 + k)
-    assert counters.cpu().tolist() == [[3, 0]] * world
+    assert counters[:, :3].cpu().tolist() == [[1, 0, 1]] * world
     with pytest.raises(_lib.DF11Error):
         _lib.check(lib.df11_selftest_allreduce_one_gpu(3, data.data_ptr(), flags.data_ptr(), counters.data_ptr(),
                                                        data.data_ptr(), data.data_ptr(), 8, slot, 0, status.data_ptr(),
