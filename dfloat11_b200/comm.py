@@ -3,7 +3,7 @@
 After every row-parallel layer the ranks' partial outputs are summed: a ``[batch, hidden]`` BF16
 tensor, 32 KB at batch 1 for hidden 16384.  A library collective is pure latency at that size
 (19-22 microseconds each through NCCL at two and four ranks when nothing runs between them, two
-per transformer layer; this kernel: 5.8).
+per transformer layer; this kernel: 4.3).
 ``df11_allreduce_bf16`` (``csrc/df11_allreduce.cu``) does it in one launch with plain peer loads
 and stores on buffers that every rank can address (up to 64 KB: every rank pushes its slice to
 all ranks as tagged 8-byte pairs, one NVLink crossing); this module sets those buffers up with
