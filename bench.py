@@ -1240,8 +1240,8 @@ def run_tp_generation(args, cfg):
             "layers": layers, "layers_of_the_full_model": cfg["layers"], "batch": args.batch,
             "prompt_tokens": args.prompt_tokens, "new_tokens": args.new_tokens,
             "harness": "greedy, static KV cache, one CUDA graph per step with the collectives inside",
-            "activation_all_reduce": ("own kernel over NVLink peer memory (DF11_PEER_ALLREDUCE=1)"
-                                     if os.environ.get("DF11_PEER_ALLREDUCE", "0") == "1" else "NCCL"),
+            "activation_all_reduce": ("own kernel over NVLink peer memory"
+                                     if os.environ.get("DF11_PEER_ALLREDUCE", "1") != "0" else "NCCL (DF11_PEER_ALLREDUCE=0)"),
             "fused_gemv": os.environ.get("DF11_FUSED_GEMV", "0") == "1",
             "bf16_shards_tok_s": round(tokens / t_bf16, 2), "df11_shards_tok_s": round(tokens / t_df11, 2),
             "slowdown_vs_bf16_shards": round(t_df11 / t_bf16, 3), "ids_identical": bool(same.item()),

@@ -11,10 +11,11 @@ torch's symmetric memory and keeps one set per process group and device.  The re
 such mode at all (its only multi-GPU form places whole layers on different devices,
 dfloat11/dfloat11.py:455-460).
 
-Opt-in: ``DF11_PEER_ALLREDUCE=1`` (read when ``apply_tensor_parallel`` runs).  Whatever cannot
-go through the kernel -- another dtype, more than ``SLOT_BYTES``, a setup that failed -- goes
-through ``torch.distributed.all_reduce`` as before; compare models only with the same setting,
-the two ways of summing round differently.
+Used by the partitioned mode unless ``DF11_PEER_ALLREDUCE=0`` (read when ``apply_tensor_parallel``
+runs).  Whatever cannot go through the kernel -- another dtype, more than ``SLOT_BYTES``, a set-up
+that failed on any rank -- goes through ``torch.distributed.all_reduce``; compare models only with
+the same setting, the two ways of summing round differently.  A call that gives up waiting for a
+peer (two seconds) sets a status word: ``dfloat11_b200.check_status()`` raises on it.
 """
 from __future__ import annotations
 

@@ -18,8 +18,9 @@ sharded BEFORE compression, because a Huffman stream cannot be re-cut without de
 
 Decompression itself never communicates: the collectives are the activation all-reduce after
 each row-parallel layer (two per transformer block), the all-reduce of the embedding lookup and
-the all-gather of the logits -- NCCL's, or, with ``DF11_PEER_ALLREDUCE=1``, for the two
-all-reduces one kernel of this library over NVLink peer memory (``comm.py``).
+the all-gather of the logits.  The two all-reduces are one kernel of this library over NVLink peer
+memory (``comm.py``) wherever its buffers can be set up on every rank, and NCCL's otherwise or with
+``DF11_PEER_ALLREDUCE=0``; the all-gather is NCCL's.
 """
 from __future__ import annotations
 
@@ -147,7 +148,7 @@ def apply_tensor_parallel(model: nn.Module, pattern_dict: Dict[str, List[str]], 
     if tp_size == 1:
         return model
     import torch.distributed as dist
-    own_all_reduce = os.environ.get("DF11_PEER_ALLREDUCE", "0") == "1"
+    own_all_reduce = os.environ.get("DF11_PEER_ALLREDUCE", "1") != "0"
 
     peer = [None, False]          # the one-kernel all-reduce over NVLink peer memory, set up at its first use
 
