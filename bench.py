@@ -1005,7 +1005,9 @@ def tp_block(args, rank, world, device):
     out["parity"] = {"model": "3-layer Llama, hidden 1024, vocabulary 8192, sharded before compression",
                      "logits_identical_to_bf16_shards": bool(flag[0].item()),
                      "generated_ids_identical": bool(flag[1].item()),
-                     "vocabulary_parallel": model.lm_head.out_features == TOY_TP["vocab_size"] // world}
+                     "vocabulary_parallel": model.lm_head.out_features == TOY_TP["vocab_size"] // world,
+                     "all_reduces": ("own kernel over NVLink peer memory (NCCL where its buffers cannot be set up)"
+                                     if os.environ.get("DF11_PEER_ALLREDUCE", "1") != "0" else "NCCL")}
     del model, bf16
     TensorManager.release()
     torch.cuda.empty_cache()
@@ -1135,7 +1137,9 @@ def tp_block(args, rank, world, device):
         "us_per_all_reduce_in_step": round((ms_with - ms_without) * 1e3 / (2 * layers), 2),
         "bit_exact": bool(ok),
         "peer_all_reduce": peer_result,
-        "note": "one block-shard per rank compressed once and cloned per layer; NCCL all-reduce unless stated"}
+        "note": "one block-shard per rank compressed once and cloned per layer; the figures outside "
+                "`peer_all_reduce` use NCCL's all-reduce, those inside the library's own kernel (the default "
+                "of the partitioned mode)"}
     del units, first, scratch
     torch.cuda.empty_cache()
 
