@@ -15,7 +15,8 @@ Used by the partitioned mode unless ``DF11_PEER_ALLREDUCE=0`` (read when ``apply
 runs).  Whatever cannot go through the kernel -- another dtype, more than ``SLOT_BYTES``, a set-up
 that failed on any rank -- goes through ``torch.distributed.all_reduce``; compare models only with
 the same setting, the two ways of summing round differently.  A call that gives up waiting for a
-peer (two seconds) sets a status word: ``dfloat11_b200.check_status()`` raises on it.
+peer (``DF11_ALLREDUCE_WAIT_MS``, 30 s) sets a status word, after which further calls return at
+once; ``dfloat11_b200.check_status()`` raises on it.
 """
 from __future__ import annotations
 
@@ -67,6 +68,10 @@ class PeerAllReduce:
         self._flags = (ctypes.c_uint64 * 8)(*([p + 2 * self.slot_bytes for p in pointers] + [0] * (8 - len(pointers))))
         self.counters = torch.zeros(int(_lib.lib.df11_allreduce_counter_bytes()) // 4, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        # How long a rank waits for the others inside one call.  Ranks of a serving job run in step,
+        # but a host may stall one of them for seconds (a collection pause, a log write); a library
+        # collective would simply wait.  After the first call that gave up the others return at once.
+        self.wait_ms = int(os.environ.get("DF11_ALLREDUCE_WAIT_MS", "30000"))
         self.calls = 0
         # nobody writes a flag before every rank's flag area is zero
         dist.barrier(group=group, device_ids=[device.index])
@@ -100,7 +105,7 @@ class PeerAllReduce:
             return False
         _lib.check(_lib.lib.df11_allreduce_bf16(
             self._data, self._flags, self.counters.data_ptr(), self.rank, self.world, tensor.data_ptr(),
-            tensor.data_ptr(), tensor.numel(), self.slot_bytes, 0, self.status.data_ptr(), self.device.index,
+            tensor.data_ptr(), tensor.numel(), self.slot_bytes, self.wait_ms, self.status.data_ptr(), self.device.index,
             torch.cuda.current_stream(self.device).cuda_stream))
         self.calls += 1
         return True

@@ -38,7 +38,16 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxCtas = 32;
 constexpr int kThreads = 512;
 constexpr uint64_t kWaitNs = 2000ull * 1000 * 1000;  // a peer that has not shown up after two seconds is not coming
-constexpr uint32_t kWaitPolls = 1u << 24;
+// A wait ends when its time is up; and, whatever the clock says, after a number of polls that
+// grows with that time (a poll takes some hundred nanoseconds at the very least).  Once a call has
+// given up (DF11_STATUS_TIMEOUT in the caller's status word), the calls after it do not wait
+// again: a forward pass with hundreds of all-reduces then ends at once, with the status set,
+// instead of waiting that time hundreds of times.
+__device__ __forceinline__ uint64_t poll_limit(uint64_t wait_ns, const int *status)
+{
+    if (status != nullptr && (*reinterpret_cast<const volatile int *>(status) & DF11_STATUS_TIMEOUT)) return 1;
+    return wait_ns / 128u + 4096u;
+}
 constexpr size_t kFlagBytes = (size_t)2 * kMaxCtas * kMaxRanks * sizeof(uint32_t);
 // pushed form: after the flags, two halves (call parity) of [rank][vector] cells of 32 bytes
 // (16 bytes of data as four {data, tag} pairs)
@@ -108,6 +117,7 @@ __device__ __forceinline__ void flag_form(const Peers &peers, uint32_t *counters
     const uint32_t tid = threadIdx.x;
     const uint32_t call = *reinterpret_cast<volatile uint32_t *>(counters);  // advanced by the last CTA to finish
     const uint32_t tag = call + 1u != 0u ? call + 1u : 1u;  // never 0: the flag areas start zeroed
+    const uint64_t polls = poll_limit(wait_ns, status);     // read early: its latency hides behind the copy below
     const uint32_t half = call & 1u;
     const uint32_t v0 = cta * vec_per_cta, v1 = min(n_vec, v0 + vec_per_cta);
     const uint32_t flag_index = (half * kMaxCtas + cta) * kMaxRanks;
@@ -124,7 +134,7 @@ __device__ __forceinline__ void flag_form(const Peers &peers, uint32_t *counters
         const uint32_t *theirs = peers.flags[rank] + flag_index + tid;
         const uint64_t t0 = global_ns();
         ok = false;
-        for (uint32_t it = 0; it < kWaitPolls; ++it) {
+        for (uint64_t it = 0; it < polls; ++it) {
             if (ld_acquire_sys(theirs) == tag) {
                 ok = true;
                 break;
@@ -191,6 +201,7 @@ __device__ __forceinline__ void pushed_form(const Peers &peers, const uint8_t *o
 {
     uint32_t *sequence = counters + 2 + cta;  // pushed calls this CTA has seen: the same on every rank
     const uint32_t call = *reinterpret_cast<volatile uint32_t *>(sequence);
+    const uint64_t polls = poll_limit(wait_ns, status);  // read early: its latency hides behind the loads below
     uint32_t tag = call + 1u;  // never 0: the buffers start zeroed
     if (tag == 0u) tag = 1u;   // (the neighbouring calls' tags in the same half are 0xFFFFFFFF and 2)
     const uint32_t v = cta * kLlThreads + threadIdx.x;
@@ -209,7 +220,7 @@ __device__ __forceinline__ void pushed_form(const Peers &peers, const uint8_t *o
         uint4 a[WORLD], b[WORLD];
         const uint64_t t0 = global_ns();
         ok = false;
-        for (uint32_t it = 0; it < kWaitPolls; ++it) {
+        for (uint64_t it = 0; it < polls; ++it) {
             bool all = true;
 #pragma unroll
             for (int r = 0; r < WORLD; ++r) {

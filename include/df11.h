@@ -273,7 +273,9 @@ int df11_decode_static(const void *luts, const void *codes, const void *sign_man
  *   in_bf16 / out_bf16   device, n_elements BF16 each (a multiple of 8; in == out is fine),
  *                16-byte aligned; n_elements * 2 <= slot_bytes
  *   wait_ms      how long a rank waits for its peers' data before it gives up and sets
- *                DF11_STATUS_TIMEOUT in `status`; `out` is then undefined (<= 0: 2 s)
+ *                DF11_STATUS_TIMEOUT in `status`; `out` is then undefined (<= 0: 2 s).  While
+ *                that bit is set in `status`, later calls do not wait at all (they still keep
+ *                the ranks' call numbers in step): clear it after dealing with the failure
  * Two forms, chosen by size alone (so every rank chooses alike).  Up to 64 KB on 1, 2, 4 or 8
  * ranks: every rank pushes its slice into every rank's flag area as 8-byte {data, call tag}
  * pairs and sums what has arrived with this call's tag -- one NVLink crossing, no fence, flag

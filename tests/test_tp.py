@@ -258,6 +258,41 @@ def test_all_reduce_kernels_with_all_ranks_on_one_gpu(world):
 
 
 @pytest.mark.gpu
+def test_all_reduce_gives_up_when_a_peer_never_comes():
+    """Rank 0 of two on one GPU, the other rank's buffers standing by untouched: nothing ever sets
+    its tags or flags, so the wait (50 ms here) runs out, the status word says so and the kernel
+    returns; while the status is set the next call does not wait again.  Both forms."""
+    import ctypes
+    import time
+    from dfloat11_b200 import _lib
+    lib, dev, slot = _lib.lib, torch.device("cuda", 0), 1 << 20
+    flag_bytes = int(lib.df11_allreduce_flag_bytes())
+    buffers = [torch.zeros(2 * slot + flag_bytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    data = (ctypes.c_uint64 * 8)(*([b.data_ptr() for b in buffers] + [0] * 6))
+    flags = (ctypes.c_uint64 * 8)(*([b.data_ptr() + 2 * slot for b in buffers] + [0] * 6))
+    counters = torch.zeros(int(lib.df11_allreduce_counter_bytes()) // 4, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def call(x, wait_ms):
+        torch.cuda.synchronize()
+        t0 = time.time()
+        _lib.check(lib.df11_allreduce_bf16(data, flags, counters.data_ptr(), 0, 2, x.data_ptr(), x.data_ptr(),
+                                           x.numel(), slot, wait_ms, status.data_ptr(), 0, stream))
+        torch.cuda.synchronize()
+        return time.time() - t0
+
+    for n in (16384, 40000):                                   # pushed form, flag form
+        x = torch.ones(n, dtype=torch.bfloat16, device=dev)
+        waited = call(x, 50)
+        assert int(status.item()) & _lib.STATUS_TIMEOUT
+        assert 0.04 < waited < 5.0
+        assert call(x, 5000) < 1.0                             # gave up before: no second wait
+        status.zero_()
+    assert counters[:3].cpu().tolist() == [2, 0, 2]            # the call numbers went on all the same
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("world", [1, 2])
 def test_peer_all_reduce_kernel(world):
     if torch.cuda.device_count() < world:
