@@ -16,8 +16,8 @@
 // parity: a rank can only be one call ahead of a peer (it needs the peer's flag of call s to
 // finish call s), so the half written in call s + 2 is no longer being read.
 //
-// Tensors of up to 64 KB on 1, 2, 4 or 8 ranks take a second, faster form with no flags, fences
-// or barriers at all (`df11_allreduce_ll_kernel`): every rank PUSHES its slice into every rank's
+// Tensors of up to 64 KB on 1, 2, 4 or 8 ranks take a second, faster form with no flags and no
+// fences, and no barrier before the result is written (`df11_allreduce_ll_kernel`): every rank PUSHES its slice into every rank's
 // buffer as 8-byte pairs {4 bytes of data, call tag}; an 8-byte store arrives whole, so a pair
 // whose tag is this call's tag is this call's data.  A thread writes the pairs of its own 16
 // bytes to all ranks, polls the pairs of all ranks for the same 16 bytes in its own buffer
