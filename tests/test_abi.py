@@ -61,3 +61,17 @@ def test_argument_errors_do_not_need_a_gpu():
     assert L.df11_prepare(p, p, p, p, p, 16, 4, 10, 10, None, 0, None) == _lib.DF11_ERR_NOSPACE
     assert L.df11_decode_static(p, p, p, p, p, p, 4, 10, (1 << 25) + 1, None, 0, None) == _lib.DF11_ERR_NOSPACE
     assert L.df11_encode_size(None, 0, None) == _lib.DF11_ERR_BADARG
+    # the all-reduce entry points check their arguments before they touch the device
+    eight = (ctypes.c_uint64 * 8)(*([p] * 8))
+    assert L.df11_allreduce_flag_bytes() > 2 << 20 and L.df11_allreduce_counter_bytes() == 256
+    assert L.df11_allreduce_bf16(None, eight, p, 0, 2, p, p, 8, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
+    assert L.df11_allreduce_bf16(eight, eight, p, 0, 9, p, p, 8, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
+    assert b"ranks" in L.df11_last_error()
+    assert L.df11_allreduce_bf16(eight, eight, p, 2, 2, p, p, 8, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
+    assert L.df11_allreduce_bf16(eight, eight, p, 0, 2, p, p, 12, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
+    assert L.df11_allreduce_bf16(eight, eight, p, 0, 2, p, p, 1 << 20, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_NOSPACE
+    assert L.df11_allreduce_bf16(eight, eight, p, 0, 2, p, p, 0, 1 << 20, 0, None, 0, None) == _lib.DF11_OK   # nothing to sum
+    assert L.df11_selftest_allreduce_one_gpu(3, p, p, p, p, p, 8, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
+    assert L.df11_selftest_allreduce_one_gpu(2, p, p, p, p, p, 12, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
+    assert L.df11_decode_range_prepared_shared(p, p, p, p, 0, -1, p, 4, 10, 10, 1, None, 0, None) == _lib.DF11_ERR_BADARG
+    assert L.df11_decode_range_prepared_shared(p, p, p, p, 0, 512, p, 4, 10, 10, -1, None, 0, None) == _lib.DF11_ERR_BADARG
