@@ -290,19 +290,21 @@ __global__ void __launch_bounds__(PUSHED ? kLlThreads : kThreads) df11_allreduce
     uint32_t *counters = e.counters + kCounterWords * rank;
     const uint4 *in = e.in + (size_t)rank * n_vec;
     uint4 *out = e.out + (size_t)rank * n_vec;
+    // 2, 4 and 8 ranks: the specialised kernels of the real launch; any other number: the general one
+    constexpr int kSpecial = (WORLD == 2 || WORLD == 4 || WORLD == 8) ? WORLD : 0;
     if (PUSHED)
         pushed_form<WORLD>(peers, e.flags + (size_t)rank * (kFlagBytes + 2 * kLlHalfBytes), counters, rank, in, out,
                            n_vec, wait_ns, status, blockIdx.x, gridDim.x);
     else
-        flag_form<WORLD>(peers, counters, rank, WORLD, in, out, n_vec, vec_per_cta, slot_bytes, wait_ns, status,
-                         blockIdx.x, gridDim.x);
+        flag_form<kSpecial>(peers, counters, rank, WORLD, in, out, n_vec, vec_per_cta, slot_bytes, wait_ns, status,
+                            blockIdx.x, gridDim.x);
 }
 
 template <int WORLD>
 cudaError_t launch_emulated(const Emulated &e, uint32_t n_vec, uint32_t slot_bytes, uint64_t wait_ns, int *status,
                             cudaStream_t stream)
 {
-    const bool pushed = n_vec <= kLlSlotVecs;
+    const bool pushed = n_vec <= kLlSlotVecs && (WORLD == 2 || WORLD == 4 || WORLD == 8);  // as the real launch chooses
     uint32_t ctas, per = 0;
     if (pushed) {
         ctas = (n_vec + kLlThreads - 1) / kLlThreads;
@@ -326,7 +328,8 @@ extern "C" int df11_selftest_allreduce_one_gpu(int32_t world, void *data, void *
                                                void *stream)
 {
     if (!data || !flags || !counters || !in_bf16 || !out_bf16) return df11_fail(DF11_ERR_BADARG, "null pointer");
-    if (world != 2 && world != 4 && world != 8) return df11_fail(DF11_ERR_BADARG, "world must be 2, 4 or 8");
+    if (world != 2 && world != 3 && world != 4 && world != 8)
+        return df11_fail(DF11_ERR_BADARG, "world must be 2, 3, 4 or 8");
     if (n_elements <= 0 || n_elements % 8 || n_elements * 2 > slot_bytes || slot_bytes % 16 || slot_bytes > 0x7FFFFFFF)
         return df11_fail(DF11_ERR_BADARG, "n_elements must be a positive multiple of 8 that fits slot_bytes");
     if (((uintptr_t)data | (uintptr_t)flags | (uintptr_t)in_bf16 | (uintptr_t)out_bf16) & 15)
@@ -342,7 +345,8 @@ extern "C" int df11_selftest_allreduce_one_gpu(int32_t world, void *data, void *
         Emulated e = {(uint8_t *)data, (uint8_t *)flags, (uint32_t *)counters, (const uint4 *)in_bf16, (uint4 *)out_bf16};
         const uint32_t n_vec = (uint32_t)(n_elements / 8);
         const uint64_t wait_ns = wait_ms > 0 ? (uint64_t)wait_ms * 1000000ull : 200ull * 1000 * 1000;
-        err = world == 2 ? launch_emulated<2>(e, n_vec, (uint32_t)slot_bytes, wait_ns, (int *)status, (cudaStream_t)stream)
+        err = world == 3 ? launch_emulated<3>(e, n_vec, (uint32_t)slot_bytes, wait_ns, (int *)status, (cudaStream_t)stream)
+            : world == 2 ? launch_emulated<2>(e, n_vec, (uint32_t)slot_bytes, wait_ns, (int *)status, (cudaStream_t)stream)
             : world == 4 ? launch_emulated<4>(e, n_vec, (uint32_t)slot_bytes, wait_ns, (int *)status, (cudaStream_t)stream)
                          : launch_emulated<8>(e, n_vec, (uint32_t)slot_bytes, wait_ns, (int *)status, (cudaStream_t)stream);
     }

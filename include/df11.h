@@ -296,7 +296,7 @@ int df11_allreduce_bf16(const uint64_t *peer_data, const uint64_t *peer_flags, v
 
 /*
  * Self-test of df11_allreduce_bf16's kernels on ONE GPU: a single cooperative launch plays all
- * `world` ranks (2, 4 or 8) -- row r of the grid runs rank r's code on rank r's buffers -- so
+ * `world` ranks (2, 4 or 8: the specialised kernels; 3: the general one) -- row r of the grid runs rank r's code on rank r's buffers -- so
  * the exchange between ranks, the call tags and the alternating buffer halves are exercised
  * where only one GPU is at hand.  (Separate launches that wait for one another must never share
  * a GPU; one cooperative launch may.)

@@ -71,7 +71,7 @@ def test_argument_errors_do_not_need_a_gpu():
     assert L.df11_allreduce_bf16(eight, eight, p, 0, 2, p, p, 12, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
     assert L.df11_allreduce_bf16(eight, eight, p, 0, 2, p, p, 1 << 20, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_NOSPACE
     assert L.df11_allreduce_bf16(eight, eight, p, 0, 2, p, p, 0, 1 << 20, 0, None, 0, None) == _lib.DF11_OK   # nothing to sum
-    assert L.df11_selftest_allreduce_one_gpu(3, p, p, p, p, p, 8, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
+    assert L.df11_selftest_allreduce_one_gpu(5, p, p, p, p, p, 8, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
     assert L.df11_selftest_allreduce_one_gpu(2, p, p, p, p, p, 12, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
     assert L.df11_decode_range_prepared_shared(p, p, p, p, 0, -1, p, 4, 10, 10, 1, None, 0, None) == _lib.DF11_ERR_BADARG
     assert L.df11_decode_range_prepared_shared(p, p, p, p, 0, 512, p, 4, 10, 10, -1, None, 0, None) == _lib.DF11_ERR_BADARG

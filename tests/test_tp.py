@@ -208,7 +208,7 @@ def _peer_worker(rank, world, port, q):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
 def test_all_reduce_kernels_with_all_ranks_on_one_gpu(world):
     """Both forms of the all-reduce kernel with 2, 4 and 8 ranks played by one cooperative launch
     on one GPU: results against an fp32 sum in rank order, the call numbers, the alternating
@@ -241,18 +241,19 @@ def test_all_reduce_kernels_with_all_ranks_on_one_gpu(world):
     pushed = flagged = 0
     for k, n in enumerate(sizes):
         one_call(n, 17 * k + world)
-        pushed, flagged = pushed + (n <= 32768), flagged + (n > 32768)
+        takes_pushed = n <= 32768 and world != 3               # 3 ranks: the general kernel, flag form only
+        pushed, flagged = pushed + takes_pushed, flagged + (not takes_pushed)
         # [0] calls of the flag form, [1] its CTAs done, [2 + c] pushed calls CTA c took part in
         assert counters[:, :3].cpu().tolist() == [[flagged, 0, pushed]] * world
-    assert counters[:, 2 + 31].cpu().tolist() == [1] * world   # only the 32768-element call reached the last CTA
+    assert counters[:, 2 + 31].cpu().tolist() == [int(world != 3)] * world   # only the 32768-element call reached the last CTA
     counters[:, 0] = -3                                       # 0xFFFFFFFD: the tags pass 0xFFFFFFFF, skip 0
     counters[:, 2:] = -3
     torch.cuda.synchronize()
     for k in range(8):
         one_call(40000 if k % 2 else 16384, 900 + k)
-    assert counters[:, :3].cpu().tolist() == [[1, 0, 1]] * world
+    assert counters[:, :3].cpu().tolist() == ([[1, 0, 1]] if world != 3 else [[5, 0, -3]]) * world
     with pytest.raises(_lib.DF11Error):
-        _lib.check(lib.df11_selftest_allreduce_one_gpu(3, data.data_ptr(), flags.data_ptr(), counters.data_ptr(),
+        _lib.check(lib.df11_selftest_allreduce_one_gpu(5, data.data_ptr(), flags.data_ptr(), counters.data_ptr(),
                                                        data.data_ptr(), data.data_ptr(), 8, slot, 0, status.data_ptr(),
                                                        0, stream))
 
