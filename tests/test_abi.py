@@ -75,3 +75,15 @@ def test_argument_errors_do_not_need_a_gpu():
     assert L.df11_selftest_allreduce_one_gpu(2, p, p, p, p, p, 12, 1 << 20, 0, None, 0, None) == _lib.DF11_ERR_BADARG
     assert L.df11_decode_range_prepared_shared(p, p, p, p, 0, -1, p, 4, 10, 10, 1, None, 0, None) == _lib.DF11_ERR_BADARG
     assert L.df11_decode_range_prepared_shared(p, p, p, p, 0, 512, p, 4, 10, 10, -1, None, 0, None) == _lib.DF11_ERR_BADARG
+
+
+def test_header_is_plain_c():
+    """include/df11.h is what a foreign-function binding reads: it must compile as C99 and as C++."""
+    import shutil
+    import subprocess
+    header = os.path.join(ROOT, "include", "df11.h")
+    for compiler, language in (("gcc", ["-std=c99", "-x", "c"]), ("g++", ["-x", "c++"])):
+        if shutil.which(compiler) is None:
+            continue
+        done = subprocess.run([compiler, "-fsyntax-only", "-Wall"] + language + [header], capture_output=True, text=True)
+        assert done.returncode == 0, done.stderr
